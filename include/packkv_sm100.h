@@ -1,0 +1,77 @@
+/*
+ * C ABI of libpackkv_sm100.so -- the B200 (sm_100a) implementation of PackKV's compression
+ * hot path.  Plain pointers and sizes only; every pointer is a DEVICE pointer unless the
+ * parameter name ends in _host.  Every call is asynchronous on `cuda_stream` (a
+ * cudaStream_t passed as void*; NULL = the legacy default stream) and allocates nothing.
+ *
+ * Return value: PKV_OK, or a PKV_ERR_* code for arguments that can be rejected on the host.
+ * Conditions only the kernels can see (a block that does not fit the stream, a code that
+ * does not fit `bits`, a corrupt block_info entry) are OR-ed as PKV_FLAG_* bits into the
+ * caller's device word `dev_flags`, and the offending block is skipped; nothing aborts.
+ *
+ * Each declaration cites the reference interface it replaces (paths inside the PackKV
+ * repository).
+ */
+#ifndef PACKKV_SM100_H
+#define PACKKV_SM100_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PKV_OK 0
+#define PKV_ERR_BAD_ARGUMENT 1
+#define PKV_ERR_UNSUPPORTED 2   /* the reference raises RuntimeError("not supported") here */
+#define PKV_ERR_CUDA 3
+
+#define PKV_FLAG_STREAM_OVERFLOW 1u
+#define PKV_FLAG_CODE_RANGE 2u
+#define PKV_FLAG_BAD_STREAM 4u
+#define PKV_FLAG_TIMEOUT 8u
+
+/* Library / build identification: returns the ABI version (currently 1). */
+int32_t pkv_abi_version(void);
+
+/*
+ * Bit-pack encoders.  Replace k_encode_cpu_pyi (packkv_cuda_ext/src/k_encode_cpu.cpp:286-331)
+ * and v_encode_cpu_pyi (packkv_cuda_ext/src/v_encode_cpu.cpp:301-346); the byte stream and
+ * block_info are identical to theirs.
+ *
+ * `n_seq` independent sequences are encoded in one call.  Sequence s reads the uint8 code
+ * matrix (ctx_len, hidden) at codes + s*codes_seq_stride, appends its blocks to the stream at
+ * stream + s*stream_seq_stride (at most `capacity` bytes), and fills block_info rows
+ * [first_cb*(hidden/hb), ...) of its table at block_info + 2*s*info_seq_stride.
+ * stream_bytes[s] is the running stream length: read when first_cb > 0 (append), written
+ * always.  Block shapes: K hb=128, cb in {32,64,128}; V hb=64, cb in {32,64,128}; bits 2..4.
+ * codes must be 16-byte aligned, streams 2-byte aligned.
+ */
+int32_t pkv_k_encode(const uint8_t* codes, int64_t codes_seq_stride, uint8_t* stream, int64_t stream_seq_stride,
+                     int64_t capacity, uint32_t* block_info, int64_t info_seq_stride, uint32_t* stream_bytes,
+                     uint32_t* dev_flags, int32_t n_seq, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb,
+                     int32_t bits, int32_t first_cb, void* cuda_stream);
+int32_t pkv_v_encode(const uint8_t* codes, int64_t codes_seq_stride, uint8_t* stream, int64_t stream_seq_stride,
+                     int64_t capacity, uint32_t* block_info, int64_t info_seq_stride, uint32_t* stream_bytes,
+                     uint32_t* dev_flags, int32_t n_seq, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb,
+                     int32_t bits, int32_t first_cb, void* cuda_stream);
+
+/*
+ * Bit-pack decoders.  Replace k_decode_cpu_pyi (packkv_cuda_ext/src/k_decode_cpu.cpp:281-326)
+ * and v_decode_cpu_pyi (packkv_cuda_ext/src/v_decode_cpu.cpp:258-303).  `capacity` is the
+ * number of valid stream bytes per sequence; entries pointing outside it are skipped and
+ * flagged.
+ */
+int32_t pkv_k_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t capacity, const uint32_t* block_info,
+                     int64_t info_seq_stride, uint8_t* codes, int64_t codes_seq_stride, uint32_t* dev_flags,
+                     int32_t n_seq, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb, int32_t bits,
+                     int32_t first_cb, void* cuda_stream);
+int32_t pkv_v_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t capacity, const uint32_t* block_info,
+                     int64_t info_seq_stride, uint8_t* codes, int64_t codes_seq_stride, uint32_t* dev_flags,
+                     int32_t n_seq, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb, int32_t bits,
+                     int32_t first_cb, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PACKKV_SM100_H */

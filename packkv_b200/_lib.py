@@ -1,0 +1,61 @@
+"""ctypes binding of libpackkv_sm100.so (the C ABI in include/packkv_sm100.h).
+
+There is no fallback: if the shared library is missing the import of any compute entry point
+raises, telling the user to build it (``python -m packkv_b200.build``).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libpackkv_sm100.so")
+
+PKV_OK, PKV_ERR_BAD_ARGUMENT, PKV_ERR_UNSUPPORTED, PKV_ERR_CUDA = 0, 1, 2, 3
+FLAG_STREAM_OVERFLOW, FLAG_CODE_RANGE, FLAG_BAD_STREAM, FLAG_TIMEOUT = 1, 2, 4, 8
+
+_i32, _i64, _p, _f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
+
+_CODEC_ENC = [_p, _i64, _p, _i64, _i64, _p, _i64, _p, _p] + [_i32] * 7 + [_p]
+_CODEC_DEC = [_p, _i64, _i64, _p, _i64, _p, _i64, _p] + [_i32] * 7 + [_p]
+
+SIGNATURES = {
+    "pkv_abi_version": (_i32, []),
+    "pkv_k_encode": (_i32, _CODEC_ENC),
+    "pkv_v_encode": (_i32, _CODEC_ENC),
+    "pkv_k_decode": (_i32, _CODEC_DEC),
+    "pkv_v_decode": (_i32, _CODEC_DEC),
+}
+
+_lib = None
+
+
+class PackKVLibraryError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise PackKVLibraryError(
+                f"{LIB_PATH} is missing: build it with `python -m packkv_b200.build` "
+                "(nvcc, sm_100a). There is no CPU fallback."
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    """Maps a C-ABI status to the exceptions the reference's callers see."""
+    if status == PKV_OK:
+        return
+    if status == PKV_ERR_UNSUPPORTED:
+        raise RuntimeError("not supported")  # same text as the reference's dispatch failure
+    if status == PKV_ERR_BAD_ARGUMENT:
+        raise ValueError(f"{what}: bad argument")
+    raise RuntimeError(f"{what}: CUDA error")

@@ -1,0 +1,57 @@
+// extern "C" surface of libpackkv_sm100.so; declarations and contracts live in
+// include/packkv_sm100.h.
+#include "../../include/packkv_sm100.h"
+#include "common.cuh"
+#include "launch.h"
+
+using namespace pkv;
+
+extern "C" {
+
+int32_t pkv_abi_version(void) { return 1; }
+
+static int32_t codec_call(bool is_k, bool encode, const uint8_t* codes, int64_t codes_seq_stride, uint8_t* stream,
+                          int64_t stream_seq_stride, int64_t capacity, uint32_t* info, int64_t info_seq_stride,
+                          uint32_t* stream_bytes, uint32_t* flags, int32_t n_seq, int32_t ctx_len, int32_t hidden,
+                          int32_t cb, int32_t hb, int32_t bits, int32_t first_cb, void* cuda_stream) {
+    CodecShape sh{n_seq, ctx_len, hidden, cb, hb, bits, first_cb};
+    CodecBuffers b{codes, codes_seq_stride, stream, stream_seq_stride, capacity, info, info_seq_stride, stream_bytes, flags};
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    return encode ? launch_encode(is_k, sh, b, st) : launch_decode(is_k, sh, b, st);
+}
+
+int32_t pkv_k_encode(const uint8_t* codes, int64_t codes_seq_stride, uint8_t* stream, int64_t stream_seq_stride,
+                     int64_t capacity, uint32_t* block_info, int64_t info_seq_stride, uint32_t* stream_bytes,
+                     uint32_t* dev_flags, int32_t n_seq, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb,
+                     int32_t bits, int32_t first_cb, void* cuda_stream) {
+    return codec_call(true, true, codes, codes_seq_stride, stream, stream_seq_stride, capacity, block_info, info_seq_stride,
+                      stream_bytes, dev_flags, n_seq, ctx_len, hidden, cb, hb, bits, first_cb, cuda_stream);
+}
+
+int32_t pkv_v_encode(const uint8_t* codes, int64_t codes_seq_stride, uint8_t* stream, int64_t stream_seq_stride,
+                     int64_t capacity, uint32_t* block_info, int64_t info_seq_stride, uint32_t* stream_bytes,
+                     uint32_t* dev_flags, int32_t n_seq, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb,
+                     int32_t bits, int32_t first_cb, void* cuda_stream) {
+    return codec_call(false, true, codes, codes_seq_stride, stream, stream_seq_stride, capacity, block_info, info_seq_stride,
+                      stream_bytes, dev_flags, n_seq, ctx_len, hidden, cb, hb, bits, first_cb, cuda_stream);
+}
+
+int32_t pkv_k_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t capacity, const uint32_t* block_info,
+                     int64_t info_seq_stride, uint8_t* codes, int64_t codes_seq_stride, uint32_t* dev_flags,
+                     int32_t n_seq, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb, int32_t bits,
+                     int32_t first_cb, void* cuda_stream) {
+    return codec_call(true, false, codes, codes_seq_stride, const_cast<uint8_t*>(stream), stream_seq_stride, capacity,
+                      const_cast<uint32_t*>(block_info), info_seq_stride, nullptr, dev_flags, n_seq, ctx_len, hidden, cb, hb,
+                      bits, first_cb, cuda_stream);
+}
+
+int32_t pkv_v_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t capacity, const uint32_t* block_info,
+                     int64_t info_seq_stride, uint8_t* codes, int64_t codes_seq_stride, uint32_t* dev_flags,
+                     int32_t n_seq, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb, int32_t bits,
+                     int32_t first_cb, void* cuda_stream) {
+    return codec_call(false, false, codes, codes_seq_stride, const_cast<uint8_t*>(stream), stream_seq_stride, capacity,
+                      const_cast<uint32_t*>(block_info), info_seq_stride, nullptr, dev_flags, n_seq, ctx_len, hidden, cb, hb,
+                      bits, first_cb, cuda_stream);
+}
+
+}  // extern "C"

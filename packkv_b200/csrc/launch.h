@@ -1,0 +1,32 @@
+// Host-side launch interfaces shared between the kernel translation units and the C ABI.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace pkv {
+
+struct CodecShape {
+    int n_seq;       // independent sequences (each has its own stream and block_info rows)
+    int ctx_len;     // tokens in this call (multiple of cb)
+    int hidden;      // channels per token row (multiple of hb)
+    int cb, hb;      // block shape: tokens x channels (K: hb 128, V: hb 64)
+    int bits;        // 2, 3 or 4
+    int first_cb;    // index of the first token block of this call inside the sequence
+};
+
+struct CodecBuffers {
+    const uint8_t* codes;       // encode: input; decode: output (cast away const by the callee)
+    int64_t codes_seq_stride;   // bytes between sequences
+    uint8_t* stream;
+    int64_t stream_seq_stride;  // bytes between sequences
+    int64_t capacity;           // usable bytes of each sequence's stream
+    uint32_t* info;             // (offset, size) pairs; rows of sequence s start at s*info_seq_stride
+    int64_t info_seq_stride;    // in blocks
+    uint32_t* stream_bytes;     // per sequence: bytes used so far (encode: in/out)
+    unsigned* flags;            // device status word, OR-ed with DevFlag bits
+};
+
+int launch_encode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
+int launch_decode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
+
+}  // namespace pkv
