@@ -71,6 +71,51 @@ int32_t pkv_v_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t c
                      int32_t n_seq, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb, int32_t bits,
                      int32_t first_cb, void* cuda_stream);
 
+/*
+ * Fused decompress-attention decode: out = softmax(q K^T * scaling) V for ONE new query token
+ * per sequence over (compressed tokens + uncompressed residual tokens), reading the packed
+ * streams directly.  Replaces the chain kq_mat_vec_mul -> fused_kq -> torch softmax ->
+ * wv_mat_vec_mul -> fused_wv (packkv_cuda_ext/src/kernels.cu:611-630,842-859,
+ * src/fused_kernels.cu:171-185,355-369, evaluation/evaluation.py:1040-1049) and, for the
+ * model path, dequantise + eager attention (models/cache/packkv_quant.py:45-85,
+ * models/llama.py:177-212), whose rounding points it reproduces.
+ *
+ * Head dimension is 128.  group = q heads per KV head (1..8).  Element type fp16 or bf16.
+ * K quantisation: PKV_K_CHANNEL (scale/zero per (kv head, token block, channel), the
+ * reference's QuantMode.ChannelQuant; requires the scale block = cbk) or PKV_K_TOKEN (per
+ * token across all heads, QuantMode.TokenQuant).  V quantisation: per token.
+ * Streams and their per-sequence strides/capacities must be 16-byte aligned / multiples of
+ * 16; n_comp must be a multiple of 128 (64 when cbk = cbv = 64).
+ * One thread-block cluster works on each (sequence, KV head); no scratch memory is needed.
+ */
+#define PKV_K_CHANNEL 0
+#define PKV_K_TOKEN 1
+
+typedef struct pkv_attn_args {
+    const void* q;              /* (batch, kv_heads*group, 128) */
+    void* out;                  /* (batch, kv_heads*group, 128) */
+    const uint8_t* k_stream; int64_t k_seq_stride; int64_t k_capacity;
+    const uint32_t* k_info;  int64_t k_info_seq_stride;   /* block = ctx_blk*kv_heads + head */
+    const void* k_scale; const void* k_zero;              /* channel: (batch, kv_heads, n_comp/cbk, 128); token: (batch, n_comp) */
+    const uint8_t* v_stream; int64_t v_seq_stride; int64_t v_capacity;
+    const uint32_t* v_info;  int64_t v_info_seq_stride;   /* block = ctx_blk*2*kv_heads + 2*head + half */
+    const void* v_scale; const void* v_zero;              /* (batch, n_comp) */
+    const void* k_res; const void* v_res;                 /* (batch, kv_heads, res_capacity, 128); first n_res tokens valid */
+    int64_t res_seq_stride, res_head_stride;              /* in elements */
+    int32_t n_res;
+    int32_t batch, kv_heads, group;
+    int32_t n_comp;
+    int32_t cbk, cbv, bits_k, bits_v;
+    int32_t k_mode;
+    int32_t high_precision_zero;                          /* dequantise as code*scale + min (utils/compute.py:175) */
+    int32_t is_bf16;
+    float scaling;
+    uint32_t* flags;                                      /* device status word */
+} pkv_attn_args;
+
+/* `args` is a HOST pointer to the argument block (copied at call time). */
+int32_t pkv_decode_attention(const pkv_attn_args* args_host, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

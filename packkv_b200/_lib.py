@@ -19,7 +19,25 @@ _i32, _i64, _p, _f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c
 _CODEC_ENC = [_p, _i64, _p, _i64, _i64, _p, _i64, _p, _p] + [_i32] * 7 + [_p]
 _CODEC_DEC = [_p, _i64, _i64, _p, _i64, _p, _i64, _p] + [_i32] * 7 + [_p]
 
+
+
+class AttnArgs(ctypes.Structure):
+    """Mirror of pkv_attn_args (include/packkv_sm100.h)."""
+    _fields_ = [
+        ("q", _p), ("out", _p),
+        ("k_stream", _p), ("k_seq_stride", _i64), ("k_capacity", _i64), ("k_info", _p), ("k_info_seq_stride", _i64),
+        ("k_scale", _p), ("k_zero", _p),
+        ("v_stream", _p), ("v_seq_stride", _i64), ("v_capacity", _i64), ("v_info", _p), ("v_info_seq_stride", _i64),
+        ("v_scale", _p), ("v_zero", _p),
+        ("k_res", _p), ("v_res", _p), ("res_seq_stride", _i64), ("res_head_stride", _i64),
+        ("n_res", _i32), ("batch", _i32), ("kv_heads", _i32), ("group", _i32), ("n_comp", _i32),
+        ("cbk", _i32), ("cbv", _i32), ("bits_k", _i32), ("bits_v", _i32),
+        ("k_mode", _i32), ("high_precision_zero", _i32), ("is_bf16", _i32), ("scaling", _f32), ("flags", _p),
+    ]
+
+
 SIGNATURES = {
+    "pkv_decode_attention": (_i32, [ctypes.POINTER(AttnArgs), _p]),
     "pkv_abi_version": (_i32, []),
     "pkv_k_encode": (_i32, _CODEC_ENC),
     "pkv_v_encode": (_i32, _CODEC_ENC),

@@ -1,0 +1,773 @@
+// Fused decompress-attention decode for one query token per sequence.
+//
+// Replaces, in one launch over the packed streams, the reference's kq_mat_vec_mul + fused_kq
+// (packkv_cuda_ext/src/kernels.cu:426-535, fused_kernels.cu:13-76), torch softmax
+// (evaluation/evaluation.py:1040-1049), wv_mat_vec_mul + fused_wv (kernels.cu:632-765,
+// fused_kernels.cu:187-261) and, for numerics, the model path's dequantise-then-attend
+// (models/cache/packkv_quant.py:45-85 + models/llama.py:177-212).  Decompressed K/V never go
+// to HBM, and neither do scores or split-K partials.
+//
+// Numerics follow the reference's rounding points so the result can be compared with its
+// decompress-then-attend path: every K and V element is dequantised to the element type
+// exactly as (code + zero) * scale (two roundings, utils/compute.py:178); scores are rounded
+// to the element type after the dot product and again after * scaling (llama.py:200); the
+// softmax runs in fp32 over ALL tokens and its probabilities are rounded to the element type
+// before the second contraction (llama.py:208-210), which accumulates in fp32.
+//
+// Because the probabilities need the global max and sum before they can be rounded, the
+// sequence is split over a thread-block CLUSTER instead of over independent split-K CTAs:
+// grid = (cluster_size, kv_heads, batch), one cluster per (sequence, KV head).
+//   phase 1  every warp of the cluster walks its 128-token (or 64-token) tiles: K blocks are
+//            staged with cp.async, unpacked, dequantised and contracted with q on the tensor
+//            cores; scores stay in the warp's shared memory.  Residual (uncompressed) tokens
+//            are spread over the same warps.
+//   exchange per-CTA (max, sum) go through distributed shared memory, one cluster barrier.
+//   phase 2  scores -> probabilities in place, V blocks are unpacked and contracted.
+//   reduce   warps -> CTA in shared memory, CTAs -> rank 0 through distributed shared memory.
+//
+// Per warp, K: read the per-round headers, warp-scan the pack sizes into byte offsets, unpack
+// 4 channels x 16 tokens per lane with one rotate + one mask per code, exchange through a
+// swizzled 16x128-byte tile so that each lane holds the mma A fragment (tokens x channels),
+// dequantise two codes per instruction, mma.sync m16n8k16 against the q fragments (the 8
+// columns of the n-tile are the q heads of the group).  V: same unpack (1 channel x 64 tokens
+// per lane), 32x64-byte exchange tile, A = channels x tokens, B = probabilities.
+#include <cooperative_groups.h>
+
+#include "attn.cuh"
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace pkv {
+
+constexpr int kAW = 4;            // warps per CTA
+constexpr int kD = 128;           // head dimension
+
+// ---- element-type traits --------------------------------------------------------------------
+template <typename T> struct Tr;
+
+template <> struct Tr<__half> {
+    using T2 = __half2;
+    static constexpr unsigned kMagic = 0x64646464u;   // 0x6400 | b == 1024 + b, exact
+    static constexpr float kBias = 1024.f;
+    static __device__ __forceinline__ T2 bias2() { return __float2half2_rn(1024.f); }
+    static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    static __device__ __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
+    static __device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+    static __device__ __forceinline__ T2 dup(__half x) { return __half2half2(x); }
+    static __device__ __forceinline__ void mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+};
+
+template <> struct Tr<__nv_bfloat16> {
+    using T2 = __nv_bfloat162;
+    static constexpr unsigned kMagic = 0x43434343u;   // 0x4300 | b == 128 + b, exact
+    static constexpr float kBias = 128.f;
+    static __device__ __forceinline__ T2 bias2() { return __float2bfloat162_rn(128.f); }
+    static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
+    static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+    static __device__ __forceinline__ T2 dup(__nv_bfloat16 x) { return __bfloat162bfloat162(x); }
+    static __device__ __forceinline__ void mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+};
+
+template <typename T2> __device__ __forceinline__ unsigned as_u(T2 v) { return *reinterpret_cast<unsigned*>(&v); }
+template <typename T2> __device__ __forceinline__ T2 as_t2(unsigned v) { return *reinterpret_cast<T2*>(&v); }
+
+// two biased codes (bias + code, exact) -> two dequantised elements, rounded like the reference
+template <typename T, bool HP>
+__device__ __forceinline__ unsigned deq2(unsigned biased, typename Tr<T>::T2 z, typename Tr<T>::T2 s) {
+    using T2 = typename Tr<T>::T2;
+    T2 x = as_t2<T2>(biased);
+    if (!HP) return as_u(__hmul2(__hadd2(x, z), s));          // z = zero - bias
+    return as_u(__hadd2(__hmul2(__hsub2(x, Tr<T>::bias2()), s), z));   // z = min
+}
+
+__device__ __forceinline__ void cp_async16(uint8_t* smem_dst, const uint8_t* gsrc) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gsrc));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ float fast_exp(float x) { return exp2f(x * 1.4426950408889634f); }
+
+struct AttnDev {
+    AttnArgs a;
+    int cluster;         // CTAs per (sequence, kv head)
+    int tile;            // tokens per warp tile: 128 or 64
+    int tiles_total;     // n_comp / tile
+    int tpw;             // max tiles per warp
+    int rpw;             // max residual tokens per warp
+    int rows;            // score rows kept per tile (q heads of the group, rounded up to even)
+    int slot;            // bytes of one staging slot
+    int prow;            // bytes of one row of the score / probability tile
+    int warp_smem;       // bytes of per-warp shared memory
+    int cta_off;         // byte offset of the CTA-shared block
+};
+
+// CTA-shared block (cluster-visible)
+struct CtaShared {
+    float cl_m[8];       // this CTA's max per head
+    float cl_l[8];       // this CTA's sum of exp(s - cl_m) per head
+    float wm[kAW][8];    // per-warp scratch
+    float gM[8], gInvL[8];
+    float out[8][kD];    // this CTA's accumulators
+};
+
+// =================================================================================================
+template <typename T, int KMODE, bool HP>
+__global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) {
+    using T2 = typename Tr<T>::T2;
+    extern __shared__ __align__(16) uint8_t smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const AttnArgs& a = P.a;
+    const int lane = lane_id(), wic = threadIdx.x >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    const int rank = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int G = a.group;
+    const int q_heads = a.kv_heads * G;
+    const int n_warps = kAW * P.cluster;
+    const int gw = rank * kAW + wic;                   // warp index inside the cluster
+
+    uint8_t* wbase = smem + wic * P.warp_smem;
+    uint8_t* xch = wbase + 2 * P.slot;                 // 2048 B exchange tile
+    T* vsz = reinterpret_cast<T*>(xch + 2048);         // [tile] V scale, [tile] V zero(-bias)
+    T* ksz = vsz + 2 * P.tile;                         // token mode: [tile] K scale, [tile] K zero(-bias)
+    uint8_t* stile = reinterpret_cast<uint8_t*>(ksz + 2 * P.tile);   // [tpw][rows][prow] scores -> probabilities
+    float* rsc = reinterpret_cast<float*>(stile + P.tpw * P.rows * P.prow);   // [rpw][8] residual scores
+    CtaShared* cs = reinterpret_cast<CtaShared*>(smem + P.cta_off);
+
+    const int my_tiles = gw < P.tiles_total ? (P.tiles_total - gw + n_warps - 1) / n_warps : 0;
+    const int my_res = gw < a.n_res ? (a.n_res - gw + n_warps - 1) / n_warps : 0;
+    const int nkb = P.tile / max(a.cbk, 1), nvb = P.tile / max(a.cbv, 1);
+    const int k_items = my_tiles * nkb, v_items = my_tiles * 2 * nvb;
+    const int total_items = k_items + v_items;
+    const int k_rounds = a.cbk / 16;
+    const int lbk = len_field_bits(a.bits_k), lbv = len_field_bits(a.bits_v);
+    const uint8_t* kbase = a.k_stream + (int64_t)b * a.k_seq_stride;
+    const uint8_t* vbase = a.v_stream + (int64_t)b * a.v_seq_stride;
+    const uint32_t* kinfo = a.k_info + (int64_t)b * a.k_info_seq_stride * 2;
+    const uint32_t* vinfo = a.v_info + (int64_t)b * a.v_info_seq_stride * 2;
+    const T2 bias2 = Tr<T>::bias2();
+    const bool col_live = 2 * c < P.rows;              // this lane's score columns (heads 2c, 2c+1) are kept
+
+    // ---- stream-block fetch ---------------------------------------------------------------------
+    // item n < k_items: K block (n % nkb) of local tile n / nkb; else V block of local tile
+    auto issue = [&](int n, int& phase_out, int& size_out) {
+        const uint8_t* base;
+        const uint32_t* info;
+        int64_t cap;
+        int bound;
+        if (n < k_items) {
+            const int tl = n / nkb, i = n - tl * nkb;
+            const int t0 = (gw + tl * n_warps) * P.tile;
+            info = kinfo + ((int64_t)(t0 / a.cbk + i) * a.kv_heads + h) * 2;
+            base = kbase; cap = a.k_capacity;
+            bound = 2 * k_rounds + k_rounds * (16 * a.bits_k + 16 * lbk + 256 * a.bits_k);
+        } else {
+            const int m = n - k_items;
+            const int tl = m / (2 * nvb), vi = m - tl * 2 * nvb;
+            const int t0 = (gw + tl * n_warps) * P.tile;
+            info = vinfo + ((int64_t)(t0 / a.cbv + (vi >> 1)) * (2 * a.kv_heads) + 2 * h + (vi & 1)) * 2;
+            base = vbase; cap = a.v_capacity;
+            const int nseg = a.cbv == 128 ? 4 : 2;
+            bound = 2 * nseg + nseg * (16 * a.bits_v + 16 * lbv + 256 * a.bits_v);
+        }
+        const unsigned off = __ldg(info), size = __ldg(info + 1);
+        uint8_t* dst = wbase + (n & 1) * P.slot;
+        if ((int64_t)off + size > cap || (int)size > bound || size < 4) {
+            if (lane == 0) atomicOr(a.flags, kFlagBadStream);
+            phase_out = 0; size_out = 0;
+        } else {
+            const uint8_t* src = base + off;
+            const int phase = (int)(reinterpret_cast<uintptr_t>(src) & 15);
+            const int total = (phase + (int)size + 15) & ~15;
+            for (int j = lane * 16; j < total; j += 512) cp_async16(dst + j, src - phase + j);
+            phase_out = phase; size_out = (int)size;
+        }
+        cp_async_commit();
+    };
+
+    int cur_phase = 0, cur_size = 0, nxt_phase = 0, nxt_size = 0;
+    if (total_items > 0) issue(0, nxt_phase, nxt_size);
+
+    // q fragments: column g of the n-tile is q head g
+    unsigned qf[8][2];
+    {
+        const uint4* qp = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const T*>(a.q) + ((int64_t)(b * q_heads + h * G + min(g, G - 1))) * kD + 32 * c);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint4 v = g < G ? __ldg(qp + i) : make_uint4(0, 0, 0, 0);
+            qf[2 * i][0] = v.x; qf[2 * i][1] = v.y; qf[2 * i + 1][0] = v.z; qf[2 * i + 1][1] = v.w;
+        }
+    }
+
+    float mloc0 = -INFINITY, mloc1 = -INFINITY;       // running max of this lane's scores, heads 2c and 2c+1
+
+    // ============================================================================ phase 1: K tiles
+    for (int n = 0; n < k_items; n++) {
+        cur_phase = nxt_phase; cur_size = nxt_size;
+        if (n + 1 < total_items) issue(n + 1, nxt_phase, nxt_size); else cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const uint8_t* blk = wbase + (n & 1) * P.slot + cur_phase;
+        const int tl = n / nkb, i = n - tl * nkb;
+        const int t0 = (gw + tl * n_warps) * P.tile;
+        uint8_t* st = stile + tl * P.rows * P.prow;
+
+        if (KMODE == kKToken && i == 0) {
+            const T* ks = reinterpret_cast<const T*>(a.k_scale) + (int64_t)b * a.n_comp + t0;
+            const T* kz = reinterpret_cast<const T*>(a.k_zero) + (int64_t)b * a.n_comp + t0;
+            for (int t = lane; t < P.tile; t += 32) {
+                ksz[t] = ks[t];
+                ksz[P.tile + t] = HP ? kz[t] : Tr<T>::from_float(Tr<T>::to_float(kz[t]) - Tr<T>::kBias);
+            }
+            __syncwarp();
+        }
+        if (cur_size > 0) {
+            // channel mode: per-(block, channel) scale and zero for this lane's 32 channels
+            T2 ksc[8][2], kzb[8][2];
+            if (KMODE == kKChannel) {
+                const int64_t row = ((int64_t)(b * a.kv_heads + h) * (a.n_comp / a.cbk) + (t0 / a.cbk + i)) * kD + 32 * c;
+                const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_scale) + row);
+                const uint4* zp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_zero) + row);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) {
+                    uint4 sv = __ldg(sp + q4), zv = __ldg(zp + q4);
+                    ksc[2 * q4][0] = as_t2<T2>(sv.x); ksc[2 * q4][1] = as_t2<T2>(sv.y);
+                    ksc[2 * q4 + 1][0] = as_t2<T2>(sv.z); ksc[2 * q4 + 1][1] = as_t2<T2>(sv.w);
+                    kzb[2 * q4][0] = as_t2<T2>(zv.x); kzb[2 * q4][1] = as_t2<T2>(zv.y);
+                    kzb[2 * q4 + 1][0] = as_t2<T2>(zv.z); kzb[2 * q4 + 1][1] = as_t2<T2>(zv.w);
+                }
+                if (!HP) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) { kzb[j][0] = __hsub2(kzb[j][0], bias2); kzb[j][1] = __hsub2(kzb[j][1], bias2); }
+                }
+            }
+            int pos = 2 * k_rounds;
+            for (int r = 0; r < k_rounds; r++) {
+                const uint8_t* hdr = blk + pos;
+                const unsigned minword = load_lane_field(hdr, lane, 4 * a.bits_k);
+                const unsigned lenword = load_lane_field(hdr + 16 * a.bits_k, lane, 4 * lbk);
+                unsigned lens4 = 0, mins4 = 0;
+                int len[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    len[j] = min((int)((lenword >> (j * lbk)) & ((1u << lbk) - 1u)), 4);
+                    lens4 |= (unsigned)len[j] << (8 * j);
+                    mins4 |= ((minword >> (j * a.bits_k)) & ((1u << a.bits_k) - 1u)) << (8 * j);
+                }
+                const unsigned inc = warp_inclusive_sum(lens4);
+                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+                const unsigned exc = inc - lens4;
+                const uint8_t* packs = hdr + 16 * a.bits_k + 16 * lbk;
+                unsigned before = 0;
+                unsigned top[4], bot[4], msk[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint64_t w = load_u64_align2(packs + 2 * (before + ((exc >> (8 * j)) & 0xFFu)));
+                    before += (tot >> (8 * j)) & 0xFFu;
+                    const unsigned lo = (unsigned)w, hi = (unsigned)(w >> 32);
+                    // tokens 0..7 live in bits [8*len, 16*len): bring them to the low word
+                    const unsigned tp = __funnelshift_rc(lo, hi, 8 * len[j]);
+                    // rotate so that token 0 (bit offset 7*len) sits at byte j
+                    const int rot = (8 * j - 7 * len[j]) & 31;
+                    top[j] = __funnelshift_l(tp, tp, rot);
+                    bot[j] = __funnelshift_l(lo, lo, rot);
+                    msk[j] = ((1u << len[j]) - 1u) << (8 * j);
+                }
+                // 16 tokens: one u32 (4 channel bytes) each, stored to the exchange tile
+#pragma unroll
+                for (int t = 0; t < 16; t++) {
+                    unsigned u;
+                    if (t < 8) {
+                        u = (top[0] & msk[0]) | (top[1] & msk[1]) | (top[2] & msk[2]) | (top[3] & msk[3]);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) top[j] = __funnelshift_l(top[j], top[j], len[j]);
+                    } else {
+                        u = (bot[0] & msk[0]) | (bot[1] & msk[1]) | (bot[2] & msk[2]) | (bot[3] & msk[3]);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) bot[j] = __funnelshift_l(bot[j], bot[j], len[j]);
+                    }
+                    u += mins4;
+                    *reinterpret_cast<unsigned*>(xch + t * 128 + ((((lane >> 2) ^ (t & 1)) << 4) | ((lane & 3) << 2))) = u;
+                }
+                __syncwarp();
+                // A fragments: rows g and g+8, this lane's 32 channels (two 16-byte chunks each)
+                uint4 ra0 = *reinterpret_cast<const uint4*>(xch + g * 128 + (((2 * c) ^ (g & 1)) << 4));
+                uint4 ra1 = *reinterpret_cast<const uint4*>(xch + g * 128 + (((2 * c + 1) ^ (g & 1)) << 4));
+                uint4 rb0 = *reinterpret_cast<const uint4*>(xch + (g + 8) * 128 + (((2 * c) ^ (g & 1)) << 4));
+                uint4 rb1 = *reinterpret_cast<const uint4*>(xch + (g + 8) * 128 + (((2 * c + 1) ^ (g & 1)) << 4));
+                __syncwarp();
+                const unsigned ua[8] = {ra0.x, ra0.y, ra0.z, ra0.w, ra1.x, ra1.y, ra1.z, ra1.w};
+                const unsigned ub[8] = {rb0.x, rb0.y, rb0.z, rb0.w, rb1.x, rb1.y, rb1.z, rb1.w};
+                const int tk = i * a.cbk + r * 16 + g;       // token (in the tile) of row g
+                T2 sg, zg, sg8, zg8;                         // token mode: per-row scale / zero
+                if (KMODE == kKToken) {
+                    sg = Tr<T>::dup(ksz[tk]); zg = Tr<T>::dup(ksz[P.tile + tk]);
+                    sg8 = Tr<T>::dup(ksz[tk + 8]); zg8 = Tr<T>::dup(ksz[P.tile + tk + 8]);
+                }
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    unsigned af[4];
+                    const unsigned a_lo = __byte_perm(ua[j], Tr<T>::kMagic, 0x4140), a_hi = __byte_perm(ua[j], Tr<T>::kMagic, 0x4342);
+                    const unsigned b_lo = __byte_perm(ub[j], Tr<T>::kMagic, 0x4140), b_hi = __byte_perm(ub[j], Tr<T>::kMagic, 0x4342);
+                    if (KMODE == kKChannel) {
+                        af[0] = deq2<T, HP>(a_lo, kzb[j][0], ksc[j][0]);
+                        af[1] = deq2<T, HP>(b_lo, kzb[j][0], ksc[j][0]);
+                        af[2] = deq2<T, HP>(a_hi, kzb[j][1], ksc[j][1]);
+                        af[3] = deq2<T, HP>(b_hi, kzb[j][1], ksc[j][1]);
+                    } else {
+                        af[0] = deq2<T, HP>(a_lo, zg, sg);
+                        af[1] = deq2<T, HP>(b_lo, zg8, sg8);
+                        af[2] = deq2<T, HP>(a_hi, zg, sg);
+                        af[3] = deq2<T, HP>(b_hi, zg8, sg8);
+                    }
+                    Tr<T>::mma(acc, af, qf[j][0], qf[j][1]);
+                }
+                // scores rounded like the reference: matmul output, then * scaling
+                if (col_live) {
+                    T* row0 = reinterpret_cast<T*>(st + (2 * c) * P.prow);
+                    T* row1 = reinterpret_cast<T*>(st + (2 * c + 1) * P.prow);
+                    const T s00 = Tr<T>::from_float(Tr<T>::round(acc[0]) * a.scaling), s01 = Tr<T>::from_float(Tr<T>::round(acc[1]) * a.scaling);
+                    const T s10 = Tr<T>::from_float(Tr<T>::round(acc[2]) * a.scaling), s11 = Tr<T>::from_float(Tr<T>::round(acc[3]) * a.scaling);
+                    row0[tk] = s00; row1[tk] = s01; row0[tk + 8] = s10; row1[tk + 8] = s11;
+                    mloc0 = fmaxf(mloc0, fmaxf(Tr<T>::to_float(s00), Tr<T>::to_float(s10)));
+                    mloc1 = fmaxf(mloc1, fmaxf(Tr<T>::to_float(s01), Tr<T>::to_float(s11)));
+                }
+                pos += 16 * a.bits_k + 16 * lbk + 2 * (int)before;
+            }
+        }
+        __syncwarp();
+    }
+
+    // ---- residual tokens, phase 1: scores ------------------------------------------------------
+    // token r = gw + k*n_warps; lane owns channels 4*lane .. 4*lane+3
+    const T* kr = reinterpret_cast<const T*>(a.k_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride + 4 * lane;
+    const T* vr = reinterpret_cast<const T*>(a.v_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride + 4 * lane;
+    float mres[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) mres[i] = -INFINITY;
+    if (my_res > 0) {
+        float qv[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const T* qp = reinterpret_cast<const T*>(a.q) + ((int64_t)(b * q_heads + h * G + min(i, G - 1))) * kD + 4 * lane;
+            const uint2 qq = *reinterpret_cast<const uint2*>(qp);
+            const T* qt = reinterpret_cast<const T*>(&qq);
+#pragma unroll
+            for (int j = 0; j < 4; j++) qv[i][j] = i < G ? Tr<T>::to_float(qt[j]) : 0.f;
+        }
+        for (int k = 0; k < my_res; k++) {
+            const int r = gw + k * n_warps;
+            const uint2 kk = *reinterpret_cast<const uint2*>(kr + (int64_t)r * kD);
+            const T* kt = reinterpret_cast<const T*>(&kk);
+            float kf[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) kf[j] = Tr<T>::to_float(kt[j]);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if (i < G) {
+                    float d = qv[i][0] * kf[0] + qv[i][1] * kf[1] + qv[i][2] * kf[2] + qv[i][3] * kf[3];
+#pragma unroll
+                    for (int s = 16; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
+                    const float sc = Tr<T>::round(Tr<T>::round(d) * a.scaling);
+                    mres[i] = fmaxf(mres[i], sc);
+                    if (lane == 0) rsc[k * 8 + i] = sc;
+                }
+            }
+        }
+    }
+
+    // ---- warp max -> CTA max --------------------------------------------------------------------
+#pragma unroll
+    for (int d = 4; d < 32; d <<= 1) {
+        mloc0 = fmaxf(mloc0, __shfl_xor_sync(0xffffffffu, mloc0, d));
+        mloc1 = fmaxf(mloc1, __shfl_xor_sync(0xffffffffu, mloc1, d));
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) cs->wm[wic][i] = mres[i];
+    }
+    __syncwarp();
+    if (g == 0 && col_live) {
+        cs->wm[wic][2 * c] = fmaxf(cs->wm[wic][2 * c], mloc0);
+        cs->wm[wic][2 * c + 1] = fmaxf(cs->wm[wic][2 * c + 1], mloc1);
+    }
+    __syncthreads();
+    if (threadIdx.x < 8) {
+        float m = cs->wm[0][threadIdx.x];
+#pragma unroll
+        for (int w = 1; w < kAW; w++) m = fmaxf(m, cs->wm[w][threadIdx.x]);
+        cs->cl_m[threadIdx.x] = m;
+    }
+    __syncthreads();
+    // ---- sums relative to the CTA max ---------------------------------------------------------
+    {
+        float l0 = 0.f, l1 = 0.f;
+        if (col_live) {
+            const float m0 = cs->cl_m[2 * c], m1 = cs->cl_m[2 * c + 1];
+            for (int tl = 0; tl < my_tiles; tl++) {
+                const T* row0 = reinterpret_cast<const T*>(stile + tl * P.rows * P.prow + (2 * c) * P.prow);
+                const T* row1 = reinterpret_cast<const T*>(stile + tl * P.rows * P.prow + (2 * c + 1) * P.prow);
+                for (int t = g; t < P.tile; t += 8) {
+                    l0 += fast_exp(Tr<T>::to_float(row0[t]) - m0);
+                    l1 += fast_exp(Tr<T>::to_float(row1[t]) - m1);
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 4; d < 32; d <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, d);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, d);
+        }
+        // residual scores: lanes 0..7 take head = lane
+        float lr = 0.f;
+        if (lane < G) {
+            const float m = cs->cl_m[lane];
+            for (int k = 0; k < my_res; k++) lr += fast_exp(rsc[k * 8 + lane] - m);
+        }
+        if (lane < 8) cs->wm[wic][lane] = lr;           // wm's maxima were consumed before the barrier above
+        __syncwarp();
+        if (g == 0 && col_live) {
+            cs->wm[wic][2 * c] += l0;
+            cs->wm[wic][2 * c + 1] += l1;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 8) {
+        float l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAW; w++) l += cs->wm[w][threadIdx.x];
+        cs->cl_l[threadIdx.x] = l;
+    }
+    // ---- cluster exchange: global max and sum ---------------------------------------------------
+    cluster.sync();
+    if (threadIdx.x < 8) {
+        float M = -INFINITY;
+        for (int r = 0; r < P.cluster; r++) M = fmaxf(M, cluster.map_shared_rank(cs, r)->cl_m[threadIdx.x]);
+        float L = 0.f;
+        for (int r = 0; r < P.cluster; r++) {
+            const CtaShared* o = cluster.map_shared_rank(cs, r);
+            const float mr = o->cl_m[threadIdx.x];
+            if (mr != -INFINITY) L += o->cl_l[threadIdx.x] * fast_exp(mr - M);
+        }
+        cs->gM[threadIdx.x] = M;
+        cs->gInvL[threadIdx.x] = L > 0.f ? 1.f / L : 0.f;
+    }
+    __syncthreads();
+
+    // ============================================================================ phase 2: V tiles
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) o[i][j] = 0.f;
+
+    for (int n = k_items; n < total_items; n++) {
+        cur_phase = nxt_phase; cur_size = nxt_size;
+        if (n + 1 < total_items) issue(n + 1, nxt_phase, nxt_size); else cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const uint8_t* blk = wbase + (n & 1) * P.slot + cur_phase;
+        const int m = n - k_items;
+        const int tl = m / (2 * nvb), vi = m - tl * 2 * nvb;
+        const int t0 = (gw + tl * n_warps) * P.tile;
+        uint8_t* st = stile + tl * P.rows * P.prow;
+
+        if (vi == 0) {
+            // scores -> probabilities rounded to the element type, in place; V scale / zero of the tile
+            if (col_live) {
+                T* row0 = reinterpret_cast<T*>(st + (2 * c) * P.prow);
+                T* row1 = reinterpret_cast<T*>(st + (2 * c + 1) * P.prow);
+                const float M0 = cs->gM[2 * c], M1 = cs->gM[2 * c + 1], I0 = cs->gInvL[2 * c], I1 = cs->gInvL[2 * c + 1];
+                for (int t = g; t < P.tile; t += 8) {
+                    row0[t] = Tr<T>::from_float(fast_exp(Tr<T>::to_float(row0[t]) - M0) * I0);
+                    row1[t] = Tr<T>::from_float(fast_exp(Tr<T>::to_float(row1[t]) - M1) * I1);
+                }
+            }
+            const T* vs = reinterpret_cast<const T*>(a.v_scale) + (int64_t)b * a.n_comp + t0;
+            const T* vz = reinterpret_cast<const T*>(a.v_zero) + (int64_t)b * a.n_comp + t0;
+            for (int t = lane; t < P.tile; t += 32) {
+                vsz[t] = vs[t];
+                vsz[P.tile + t] = HP ? vz[t] : Tr<T>::from_float(Tr<T>::to_float(vz[t]) - Tr<T>::kBias);
+            }
+            __syncwarp();
+        }
+        if (cur_size > 0) {
+            const int hh = vi & 1;                         // which 64-channel half of the head
+            const int tok_blk = (vi >> 1) * a.cbv;         // token offset of the block in the tile
+            const int rpw = a.cbv == 128 ? 2 : 1;
+            const int nseg = 2 * rpw;
+            int pos = 2 * nseg;
+            for (int sgi = 0; sgi < nseg; sgi++) {
+                const int w = sgi / rpw, rr = sgi - w * rpw;
+                const int tok_seg = tok_blk + rr * 64;     // first token (in the tile) of the segment
+                const uint8_t* hdr = blk + pos;
+                const unsigned minword = load_lane_field(hdr, lane, 4 * a.bits_v);
+                const unsigned lenword = load_lane_field(hdr + 16 * a.bits_v, lane, 4 * lbv);
+                unsigned lens4 = 0;
+                int len[4];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) {
+                    len[q4] = min((int)((lenword >> (q4 * lbv)) & ((1u << lbv) - 1u)), 4);
+                    lens4 |= (unsigned)len[q4] << (8 * q4);
+                }
+                const unsigned inc = warp_inclusive_sum(lens4);
+                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+                const unsigned exc = inc - lens4;
+                const uint8_t* packs = hdr + 16 * a.bits_v + 16 * lbv;
+                unsigned before = 0;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) {
+                    const uint64_t wd = load_u64_align2(packs + 2 * (before + ((exc >> (8 * q4)) & 0xFFu)));
+                    before += (tot >> (8 * q4)) & 0xFFu;
+                    const unsigned lo = (unsigned)wd, hi = (unsigned)(wd >> 32);
+                    const int ln = len[q4];
+                    const unsigned tp = __funnelshift_rc(lo, hi, 8 * ln);
+                    const unsigned mn4 = ((minword >> (q4 * a.bits_v)) & ((1u << a.bits_v) - 1u)) * 0x01010101u;
+                    const unsigned m1 = (1u << ln) - 1u;
+                    const unsigned m0 = m1, m8 = m1 << 8, m16 = m1 << 16, m24 = m1 << 24;
+                    // token i' of a word sits at bit len*(7-i'); its byte target is 8*(i'&3):
+                    // start with token 0 at byte 0, then rotate left by 8+len per token
+                    unsigned y = __funnelshift_l(tp, tp, (32 - 7 * ln) & 31);
+                    unsigned z = __funnelshift_l(lo, lo, (32 - 7 * ln) & 31);
+                    unsigned u[4];
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        unsigned v0 = y & m0; y = __funnelshift_l(y, y, 8 + ln);
+                        v0 |= y & m8; y = __funnelshift_l(y, y, 8 + ln);
+                        v0 |= y & m16; y = __funnelshift_l(y, y, 8 + ln);
+                        v0 |= y & m24; y = __funnelshift_l(y, y, 8 + ln);
+                        u[k] = v0 + mn4;
+                        unsigned v1 = z & m0; z = __funnelshift_l(z, z, 8 + ln);
+                        v1 |= z & m8; z = __funnelshift_l(z, z, 8 + ln);
+                        v1 |= z & m16; z = __funnelshift_l(z, z, 8 + ln);
+                        v1 |= z & m24; z = __funnelshift_l(z, z, 8 + ln);
+                        u[2 + k] = v1 + mn4;
+                    }
+                    // row = lane (channel), logical 16-byte chunk q4, swizzled
+                    *reinterpret_cast<uint4*>(xch + lane * 64 + ((q4 ^ ((lane >> 1) & 3)) << 4)) = make_uint4(u[0], u[1], u[2], u[3]);
+                }
+                __syncwarp();
+                // per-token scale / zero pairs and probabilities for tokens tok_seg + 16c .. +15
+                const uint4 s0 = *reinterpret_cast<const uint4*>(vsz + tok_seg + 16 * c);
+                const uint4 s1 = *reinterpret_cast<const uint4*>(vsz + tok_seg + 16 * c + 8);
+                const uint4 z0 = *reinterpret_cast<const uint4*>(vsz + P.tile + tok_seg + 16 * c);
+                const uint4 z1 = *reinterpret_cast<const uint4*>(vsz + P.tile + tok_seg + 16 * c + 8);
+                uint4 p0 = make_uint4(0, 0, 0, 0), p1 = make_uint4(0, 0, 0, 0);
+                if (g < P.rows) {
+                    p0 = *reinterpret_cast<const uint4*>(st + g * P.prow + 2 * (tok_seg + 16 * c));
+                    p1 = *reinterpret_cast<const uint4*>(st + g * P.prow + 2 * (tok_seg + 16 * c) + 16);
+                }
+                const unsigned vS[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                const unsigned vZ[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+                const unsigned pf[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                // A fragments for both 16-channel row tiles, then the contraction into the
+                // accumulator group of this (64-channel half, warp half): static register
+                // indices, so the select is unrolled
+                unsigned afr[2][4][4];
+#pragma unroll
+                for (int mt = 0; mt < 2; mt++) {
+                    const int ra = 16 * mt + g, rb = ra + 8;
+                    const uint4 xa = *reinterpret_cast<const uint4*>(xch + ra * 64 + ((c ^ ((ra >> 1) & 3)) << 4));
+                    const uint4 xb = *reinterpret_cast<const uint4*>(xch + rb * 64 + ((c ^ ((rb >> 1) & 3)) << 4));
+                    const unsigned ua[4] = {xa.x, xa.y, xa.z, xa.w};
+                    const unsigned ub[4] = {xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        afr[mt][j][0] = deq2<T, HP>(__byte_perm(ua[j], Tr<T>::kMagic, 0x4140), as_t2<T2>(vZ[2 * j]), as_t2<T2>(vS[2 * j]));
+                        afr[mt][j][1] = deq2<T, HP>(__byte_perm(ub[j], Tr<T>::kMagic, 0x4140), as_t2<T2>(vZ[2 * j]), as_t2<T2>(vS[2 * j]));
+                        afr[mt][j][2] = deq2<T, HP>(__byte_perm(ua[j], Tr<T>::kMagic, 0x4342), as_t2<T2>(vZ[2 * j + 1]), as_t2<T2>(vS[2 * j + 1]));
+                        afr[mt][j][3] = deq2<T, HP>(__byte_perm(ub[j], Tr<T>::kMagic, 0x4342), as_t2<T2>(vZ[2 * j + 1]), as_t2<T2>(vS[2 * j + 1]));
+                    }
+                }
+                const int sel = 2 * hh + w;
+#pragma unroll
+                for (int idx = 0; idx < 4; idx++) {
+                    if (idx == sel) {
+#pragma unroll
+                        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                            for (int j = 0; j < 4; j++) Tr<T>::mma(o[2 * idx + mt], afr[mt][j], pf[2 * j], pf[2 * j + 1]);
+                    }
+                }
+                __syncwarp();
+                pos += 16 * a.bits_v + 16 * lbv + 2 * (int)before;
+            }
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+    __syncwarp();
+
+    // ---- residual tokens, phase 2: probabilities x V (lane owns channels 4*lane..+3) ----------
+    // (done before the accumulators are parked in shared memory: that region may overlap rsc)
+    float racc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) racc[i][j] = 0.f;
+    for (int k = 0; k < my_res; k++) {
+        const int r = gw + k * n_warps;
+        const uint2 vv = *reinterpret_cast<const uint2*>(vr + (int64_t)r * kD);
+        const T* vt = reinterpret_cast<const T*>(&vv);
+        float vf[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) vf[j] = Tr<T>::to_float(vt[j]);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            if (i < G) {
+                const float p = Tr<T>::round(fast_exp(rsc[k * 8 + i] - cs->gM[i]) * cs->gInvL[i]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) racc[i][j] += p * vf[j];
+            }
+        }
+    }
+    __syncwarp();
+    // ---- warp accumulators -> this warp's shared region: red[head][channel] --------------------
+    float* red = reinterpret_cast<float*>(wbase);
+#pragma unroll
+    for (int mt = 0; mt < 8; mt++) {
+        red[(2 * c) * kD + 16 * mt + g] = o[mt][0];
+        red[(2 * c + 1) * kD + 16 * mt + g] = o[mt][1];
+        red[(2 * c) * kD + 16 * mt + g + 8] = o[mt][2];
+        red[(2 * c + 1) * kD + 16 * mt + g + 8] = o[mt][3];
+    }
+    __syncwarp();
+    if (my_res > 0) {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            if (i < G) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) red[i * kD + 4 * lane + j] += racc[i][j];
+            }
+    }
+    __syncthreads();
+    // ---- CTA reduce, then cluster reduce on rank 0 ---------------------------------------------
+    {
+        const int d = threadIdx.x;
+        for (int hd = 0; hd < G; hd++) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < kAW; w++) v += reinterpret_cast<const float*>(smem + w * P.warp_smem)[hd * kD + d];
+            cs->out[hd][d] = v;
+        }
+    }
+    cluster.sync();
+    if (rank == 0) {
+        const int d = threadIdx.x;
+        for (int hd = 0; hd < G; hd++) {
+            float v = 0.f;
+            for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cs, r)->out[hd][d];
+            reinterpret_cast<T*>(a.out)[((int64_t)(b * q_heads + h * G + hd)) * kD + d] = Tr<T>::from_float(v);
+        }
+    }
+    cluster.sync();   // keep every CTA's shared memory alive until rank 0 has read it
+}
+
+// =================================================================================================
+static int k_bound(int cb, int bits) { int r = cb / 16; return 2 * r + r * (16 * bits + 16 * len_field_bits(bits) + 256 * bits); }
+static int v_bound(int cb, int bits) { int n = cb == 128 ? 4 : 2; return 2 * n + n * (16 * bits + 16 * len_field_bits(bits) + 256 * bits); }
+
+template <typename T, int KM, bool HPV>
+static int launch_one(const AttnDev& P, dim3 grid, int smem, cudaStream_t st) {
+    auto kern = attn_decode_kernel<T, KM, HPV>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kCudaError;
+    if (P.cluster > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) return kCudaError;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kAW * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = P.cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, P) == cudaSuccess ? kOk : kCudaError;
+}
+
+template <typename T>
+static int launch_typed(const AttnDev& P, dim3 grid, int smem, cudaStream_t st) {
+    const AttnArgs& a = P.a;
+    if (a.k_mode == kKChannel) return a.high_precision_zero ? launch_one<T, kKChannel, true>(P, grid, smem, st) : launch_one<T, kKChannel, false>(P, grid, smem, st);
+    return a.high_precision_zero ? launch_one<T, kKToken, true>(P, grid, smem, st) : launch_one<T, kKToken, false>(P, grid, smem, st);
+}
+
+int launch_attention(const AttnArgs& a, cudaStream_t st) {
+    if (a.batch <= 0 || a.kv_heads <= 0 || a.group < 1 || a.group > 8) return a.group > 8 ? kUnsupported : kBadArgument;
+    if (a.n_comp < 0 || a.n_res < 0 || a.n_comp + a.n_res == 0) return kBadArgument;
+    if (!a.q || !a.out || !a.flags) return kBadArgument;
+    if (a.n_comp > 0) {
+        if ((a.cbk != 64 && a.cbk != 128) || (a.cbv != 64 && a.cbv != 128)) return kUnsupported;
+        if (a.bits_k < 2 || a.bits_k > 4 || a.bits_v < 2 || a.bits_v > 4) return kUnsupported;
+        if (a.k_mode != kKChannel && a.k_mode != kKToken) return kUnsupported;
+        const int tile = (a.cbk == 128 || a.cbv == 128) ? 128 : 64;
+        if (a.n_comp % tile) return kBadArgument;
+        if (!a.k_stream || !a.k_info || !a.k_scale || !a.k_zero || !a.v_stream || !a.v_info || !a.v_scale || !a.v_zero) return kBadArgument;
+        if ((reinterpret_cast<uintptr_t>(a.k_stream) & 15) || (a.k_seq_stride & 15) || (reinterpret_cast<uintptr_t>(a.v_stream) & 15) ||
+            (a.v_seq_stride & 15) || (a.k_capacity & 15) || (a.v_capacity & 15))
+            return kBadArgument;
+        if ((reinterpret_cast<uintptr_t>(a.k_scale) & 15) || (reinterpret_cast<uintptr_t>(a.k_zero) & 15)) return kBadArgument;
+    }
+    if (a.n_res > 0) {
+        if (!a.k_res || !a.v_res) return kBadArgument;
+        if ((reinterpret_cast<uintptr_t>(a.k_res) & 7) || (reinterpret_cast<uintptr_t>(a.v_res) & 7) || (a.res_seq_stride & 3) || (a.res_head_stride & 3))
+            return kBadArgument;
+    }
+    if (reinterpret_cast<uintptr_t>(a.q) & 15) return kBadArgument;
+
+    AttnDev P{};
+    P.a = a;
+    P.tile = (a.n_comp > 0 && (a.cbk == 128 || a.cbv == 128)) ? 128 : 64;
+    P.tiles_total = a.n_comp / P.tile;
+    // cluster size: enough CTAs for ~2 waves of the 148 SMs (3 CTAs each), but at least one
+    // tile per warp; a long sequence must also fit its scores in shared memory
+    const long pairs = (long)a.batch * a.kv_heads;
+    const int units = P.tiles_total + (a.n_res + 15) / 16;
+    int cl = 1;
+    while (cl < 8 && pairs * cl < 2L * 148 * 3 && units > kAW * cl) cl *= 2;
+    P.rows = (a.group + 1) & ~1;
+    P.prow = 2 * P.tile + 16;
+    int slot = 0;
+    if (a.n_comp > 0) {
+        const int kb = k_bound(a.cbk, a.bits_k), vb = v_bound(a.cbv, a.bits_v);
+        slot = ((kb > vb ? kb : vb) + 48 + 15) & ~15;
+    }
+    P.slot = slot;
+    int smem = 0;
+    for (;;) {
+        P.cluster = cl;
+        const int n_warps = kAW * cl;
+        P.tpw = (P.tiles_total + n_warps - 1) / n_warps;
+        P.rpw = (a.n_res + n_warps - 1) / n_warps;
+        int warp_smem = 2 * slot + 2048 + 8 * P.tile + P.tpw * P.rows * P.prow + P.rpw * 8 * 4;
+        const int red_need = 8 * kD * 4;
+        if (warp_smem < red_need) warp_smem = red_need;
+        P.warp_smem = (warp_smem + 15) & ~15;
+        P.cta_off = kAW * P.warp_smem;
+        smem = P.cta_off + (int)sizeof(CtaShared);
+        if (smem <= 200 * 1024 || cl >= 16) break;
+        cl *= 2;                                          // long sequence: spread the scores over more CTAs
+    }
+    if (smem > 227 * 1024) return kUnsupported;
+    dim3 grid(P.cluster, a.kv_heads, a.batch);
+    return a.is_bf16 ? launch_typed<__nv_bfloat16>(P, grid, smem, st) : launch_typed<__half>(P, grid, smem, st);
+}
+
+}  // namespace pkv

@@ -1,0 +1,15 @@
+// Host-side interface of the fused decompress-attention decode kernel.  The argument block
+// is the C ABI's pkv_attn_args (include/packkv_sm100.h); all pointers are device pointers.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+#include "../../include/packkv_sm100.h"
+
+namespace pkv {
+
+enum KMode : int { kKChannel = PKV_K_CHANNEL, kKToken = PKV_K_TOKEN };
+using AttnArgs = pkv_attn_args;
+
+int launch_attention(const AttnArgs& a, cudaStream_t st);
+
+}  // namespace pkv

@@ -3,6 +3,7 @@
 #include "../../include/packkv_sm100.h"
 #include "common.cuh"
 #include "launch.h"
+#include "attn.cuh"
 
 using namespace pkv;
 
@@ -52,6 +53,11 @@ int32_t pkv_v_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t c
     return codec_call(false, false, codes, codes_seq_stride, const_cast<uint8_t*>(stream), stream_seq_stride, capacity,
                       const_cast<uint32_t*>(block_info), info_seq_stride, nullptr, dev_flags, n_seq, ctx_len, hidden, cb, hb,
                       bits, first_cb, cuda_stream);
+}
+
+int32_t pkv_decode_attention(const pkv_attn_args* args_host, void* cuda_stream) {
+    if (!args_host) return kBadArgument;
+    return launch_attention(*args_host, static_cast<cudaStream_t>(cuda_stream));
 }
 
 }  // extern "C"

@@ -6,6 +6,8 @@ libpackkv_sm100.so.
 """
 from __future__ import annotations
 
+import ctypes
+from dataclasses import dataclass
 from typing import Optional, Tuple
 
 import torch
@@ -105,3 +107,96 @@ def decode_codes(which: str, stream: torch.Tensor, info: torch.Tensor, ctx: int,
             n_seq, ctx, hidden, cb, hb, bits, first_cb, _stream_ptr())
     _lib.check(st, f"{which}_decode")
     return out, flags
+
+
+K_CHANNEL, K_TOKEN = 0, 1
+
+
+@dataclass
+class CompressedLayer:
+    """Device-resident compressed KV of one layer: per-sequence K and V streams with their
+    block tables and quantisation parameters (layouts: include/packkv_sm100.h)."""
+    k_stream: torch.Tensor      # (B, capacity) u8
+    k_info: torch.Tensor        # (B, n_k_blocks, 2) i32 (u32 values)
+    k_bytes: torch.Tensor       # (B,) i32
+    k_scale: torch.Tensor       # channel: (B, Hkv, n_comp/cbk, 128); token: (B, n_comp)
+    k_zero: torch.Tensor
+    v_stream: torch.Tensor
+    v_info: torch.Tensor
+    v_bytes: torch.Tensor
+    v_scale: torch.Tensor       # (B, n_comp)
+    v_zero: torch.Tensor
+    n_comp: int
+    kv_heads: int
+    cbk: int
+    cbv: int
+    bits_k: int
+    bits_v: int
+    k_mode: int
+    high_precision_zero: bool = False
+
+    def stream_bytes(self) -> int:
+        """Compressed payload actually read by a decode step (streams + block tables + scales)."""
+        n = int(self.k_bytes.sum().item()) + int(self.v_bytes.sum().item())
+        n += self.k_info.numel() * 4 + self.v_info.numel() * 4
+        for t in (self.k_scale, self.k_zero, self.v_scale, self.v_zero):
+            n += t.numel() * t.element_size()
+        return n
+
+
+def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: Optional[torch.Tensor],
+                     v_res: Optional[torch.Tensor], n_res: int, *, scaling: Optional[float] = None,
+                     out: Optional[torch.Tensor] = None,
+                     flags: Optional[torch.Tensor] = None, kv_heads: Optional[int] = None) -> torch.Tensor:
+    """softmax(q K^T * scaling) V for one query token per sequence.
+
+    q: (B, Hq, 128) fp16/bf16 (post-RoPE).  `layer` holds the compressed tokens, k_res/v_res
+    (B, Hkv, R_cap, 128) the uncompressed residual whose first n_res tokens are valid.
+    Returns out (B, Hq, 128) in q's dtype; asynchronous on the current stream.
+    """
+    _require_cuda(q, k_res, v_res, out, flags)
+    if q.dim() != 3 or q.shape[2] != 128 or not q.is_contiguous():
+        raise ValueError("q must be a contiguous (B, Hq, 128) tensor")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("q must be fp16 or bf16")
+    B, Hq, D = q.shape
+    if layer is not None:
+        kv_heads = layer.kv_heads
+    elif kv_heads is None:
+        kv_heads = k_res.shape[1]
+    if Hq % kv_heads:
+        raise ValueError("q heads must be a multiple of kv heads")
+    if out is None:
+        out = torch.empty_like(q)
+    if flags is None:
+        flags = new_flags(q.device)
+    a = _lib.AttnArgs()
+    a.q, a.out = q.data_ptr(), out.data_ptr()
+    n_comp = 0 if layer is None else layer.n_comp
+    if n_comp > 0:
+        L = layer
+        for t in (L.k_scale, L.k_zero, L.v_scale, L.v_zero):
+            if t.dtype != q.dtype or not t.is_contiguous():
+                raise ValueError("scale / zero tensors must be contiguous and of q's dtype")
+        a.k_stream, a.k_seq_stride, a.k_capacity = L.k_stream.data_ptr(), L.k_stream.stride(0), L.k_stream.shape[1] & ~15
+        a.k_info, a.k_info_seq_stride = L.k_info.data_ptr(), L.k_info.shape[1]
+        a.k_scale, a.k_zero = L.k_scale.data_ptr(), L.k_zero.data_ptr()
+        a.v_stream, a.v_seq_stride, a.v_capacity = L.v_stream.data_ptr(), L.v_stream.stride(0), L.v_stream.shape[1] & ~15
+        a.v_info, a.v_info_seq_stride = L.v_info.data_ptr(), L.v_info.shape[1]
+        a.v_scale, a.v_zero = L.v_scale.data_ptr(), L.v_zero.data_ptr()
+        a.cbk, a.cbv, a.bits_k, a.bits_v = L.cbk, L.cbv, L.bits_k, L.bits_v
+        a.k_mode, a.high_precision_zero = L.k_mode, int(L.high_precision_zero)
+    if n_res > 0:
+        if k_res.dtype != q.dtype or v_res.dtype != q.dtype or k_res.stride(3) != 1 or k_res.stride(2) != 128:
+            raise ValueError("residual tensors must be (B, Hkv, R, 128) with contiguous rows, in q's dtype")
+        if k_res.stride() != v_res.stride():
+            raise ValueError("k_res and v_res must share strides")
+        a.k_res, a.v_res = k_res.data_ptr(), v_res.data_ptr()
+        a.res_seq_stride, a.res_head_stride = k_res.stride(0), k_res.stride(1)
+    a.n_res, a.batch, a.kv_heads, a.group, a.n_comp = n_res, B, kv_heads, Hq // kv_heads, n_comp
+    a.is_bf16 = int(q.dtype == torch.bfloat16)
+    a.scaling = float(D ** -0.5 if scaling is None else scaling)
+    a.flags = flags.data_ptr()
+    st = _lib.lib().pkv_decode_attention(ctypes.byref(a), _stream_ptr())
+    _lib.check(st, "decode_attention")
+    return out

@@ -1,0 +1,95 @@
+"""GPU: fused decompress-attention decode (C ABI pkv_decode_attention) against the
+reference's decompress-then-attend path restated on CPU (oracle/quant.py): quantise ->
+dequantise in the tensor dtype -> eager attention with fp32 softmax.
+
+Tolerance: 2e-3 max-abs error relative to max|reference| (the bar of the task), both dtypes.
+"""
+import pytest
+import torch
+
+from oracle import quant as Q
+from packkv_b200 import ops, synth
+from tests.helpers import layer_from_oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def _run_case(dev, dtype, B, Hkv, G, n_comp, n_res, *, block, cbk, cbv, bits_k, bits_v, k_mode, seed, hp=False, rope=True):
+    S = n_comp + n_res
+    k, v = synth.synth_kv(B, Hkv, S, 128, seed=seed, dtype=dtype, apply_rope=rope)
+    q = synth.synth_q(B, Hkv * G, 128, seed=seed, dtype=dtype)
+    layer = kd = vd = None
+    if n_comp:
+        layer, kd, vd = layer_from_oracle(k[:, :, :n_comp], v[:, :, :n_comp], block=block, bits_k=bits_k, bits_v=bits_v,
+                                          k_mode=k_mode, cbk=cbk, cbv=cbv, rel_k=synth.rel_for_bits(bits_k),
+                                          rel_v=synth.rel_for_bits(bits_v), device=dev, hp=hp)
+    K = k[:, :, n_comp:] if kd is None else torch.cat([kd, k[:, :, n_comp:]], 2)
+    V = v[:, :, n_comp:] if vd is None else torch.cat([vd, v[:, :, n_comp:]], 2)
+    ref = Q.eager_attention(q, K, V)[:, 0].float()           # (B, Hq, D)
+    k_res = k[:, :, n_comp:].contiguous().to(dev) if n_res else None
+    v_res = v[:, :, n_comp:].contiguous().to(dev) if n_res else None
+    flags = ops.new_flags(dev)
+    out = ops.decode_attention(q[:, :, 0].contiguous().to(dev), layer, k_res, v_res, n_res, flags=flags, kv_heads=Hkv)
+    torch.cuda.synchronize()
+    assert int(flags.item()) == 0
+    err = ((out.float().cpu() - ref).abs().max() / ref.abs().max()).item()
+    return err
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k_mode", ["channel", "token"])
+def test_gqa_4bit_block64(cuda_device, dtype, k_mode):
+    err = _run_case(cuda_device, dtype, 2, 2, 4, 512, 128, block=64, cbk=64, cbv=64, bits_k=4, bits_v=4, k_mode=k_mode, seed=1)
+    assert err <= TOL, err
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_v_block_128_reference_layout(cuda_device, dtype):
+    err = _run_case(cuda_device, dtype, 1, 8, 4, 1024 - 128, 128, block=64, cbk=64, cbv=128, bits_k=4, bits_v=4, k_mode="channel", seed=0, rope=False)
+    assert err <= TOL, err
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_long_context_2bit_k_block128(cuda_device, dtype):
+    err = _run_case(cuda_device, dtype, 1, 2, 4, 2048, 160, block=128, cbk=128, cbv=128, bits_k=2, bits_v=4, k_mode="channel", seed=2)
+    assert err <= TOL, err
+
+
+@pytest.mark.parametrize("G", [1, 2, 8])
+def test_group_sizes(cuda_device, G):
+    err = _run_case(cuda_device, torch.float16, 2, 2, G, 256, 130, block=64, cbk=64, cbv=64, bits_k=3, bits_v=3, k_mode="token", seed=3)
+    assert err <= TOL, err
+
+
+def test_residual_only_and_compressed_only(cuda_device):
+    err = _run_case(cuda_device, torch.float16, 2, 2, 4, 0, 191, block=64, cbk=64, cbv=64, bits_k=4, bits_v=4, k_mode="channel", seed=4)
+    assert err <= TOL, err
+    err = _run_case(cuda_device, torch.bfloat16, 1, 2, 4, 384, 0, block=64, cbk=64, cbv=64, bits_k=4, bits_v=4, k_mode="channel", seed=5)
+    assert err <= TOL, err
+
+
+def test_high_precision_zero_point(cuda_device):
+    err = _run_case(cuda_device, torch.float16, 1, 2, 4, 256, 128, block=64, cbk=64, cbv=64, bits_k=4, bits_v=4, k_mode="channel", seed=6, hp=True)
+    assert err <= TOL, err
+
+
+def test_permutation_invariance(cuda_device):
+    """Attention over the compressed tokens does not depend on the token order inside a
+    block, the property the reorder step relies on (models/cache/unorder_cache.py:11-20)."""
+    dev, dtype = cuda_device, torch.float16
+    B, H, G, S = 1, 2, 4, 256
+    k, v = synth.synth_kv(B, H, S, 128, seed=9, dtype=dtype)
+    q = synth.synth_q(B, H * G, 128, seed=9, dtype=dtype)[:, :, 0].contiguous().to(dev)
+    outs = []
+    g = torch.Generator().manual_seed(0)
+    for shuffle in (False, True):
+        kk, vv = k, v
+        if shuffle:   # K token-mode and V token-mode parameters travel with their token
+            perm = torch.cat([torch.randperm(64, generator=g) + 64 * i for i in range(S // 64)])
+            kk, vv = k[:, :, perm], v[:, :, perm]
+        layer, _, _ = layer_from_oracle(kk, vv, block=64, bits_k=4, bits_v=4, k_mode="token", cbk=64, cbv=64,
+                                        rel_k=1 / 14, rel_v=1 / 14, device=dev)
+        outs.append(ops.decode_attention(q, layer, None, None, 0).float().cpu())
+    torch.cuda.synchronize()
+    assert ((outs[0] - outs[1]).abs().max() / outs[0].abs().max()).item() <= TOL
