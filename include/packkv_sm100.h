@@ -31,6 +31,10 @@ extern "C" {
 #define PKV_FLAG_BAD_STREAM 4u
 #define PKV_FLAG_TIMEOUT 8u
 
+/* quantisation modes (the reference's QuantMode.ChannelQuant / QuantMode.TokenQuant) */
+#define PKV_K_CHANNEL 0
+#define PKV_K_TOKEN 1
+
 /* Library / build identification: returns the ABI version (currently 1). */
 int32_t pkv_abi_version(void);
 
@@ -72,6 +76,22 @@ int32_t pkv_v_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t c
                      int32_t first_cb, void* cuda_stream);
 
 /*
+ * Block quantiser: fp16/bf16 K or V (batch, heads, tokens, 128) -> uint8 codes laid out as the
+ * encoders' input (batch, tokens, heads*128), plus scale and zero-point in the element type.
+ * Replaces quant_ints (utils/compute.py:84-112) bit for bit, including the rounding to the
+ * element type after every op.  mode PKV_K_CHANNEL: parameters per (sequence, head, token
+ * block, channel), written to (batch, heads, param_blocks, 128) starting at block first_block;
+ * mode PKV_K_TOKEN: per (sequence, token) across all heads, written to (batch, param_tokens)
+ * starting at token first_token.  x strides are in elements; rows of 128 channels are
+ * contiguous and 8-byte aligned.  bits > 0 enables the range check (PKV_FLAG_CODE_RANGE).
+ */
+int32_t pkv_quantize(const void* x, int64_t stride_b, int64_t stride_h, int64_t stride_s, uint8_t* codes,
+                     int64_t codes_seq_stride, void* scale, void* zero, int32_t param_blocks, int32_t first_block,
+                     int32_t param_tokens, int32_t first_token, int32_t batch, int32_t heads, int32_t tokens,
+                     int32_t block, float rel, int32_t bits, int32_t mode, int32_t high_precision_zero,
+                     int32_t is_bf16, uint32_t* dev_flags, void* cuda_stream);
+
+/*
  * Fused decompress-attention decode: out = softmax(q K^T * scaling) V for ONE new query token
  * per sequence over (compressed tokens + uncompressed residual tokens), reading the packed
  * streams directly.  Replaces the chain kq_mat_vec_mul -> fused_kq -> torch softmax ->
@@ -88,9 +108,6 @@ int32_t pkv_v_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t c
  * 16; n_comp must be a multiple of 128 (64 when cbk = cbv = 64).
  * One thread-block cluster works on each (sequence, KV head); no scratch memory is needed.
  */
-#define PKV_K_CHANNEL 0
-#define PKV_K_TOKEN 1
-
 typedef struct pkv_attn_args {
     const void* q;              /* (batch, kv_heads*group, 128) */
     void* out;                  /* (batch, kv_heads*group, 128) */

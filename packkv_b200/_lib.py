@@ -37,6 +37,7 @@ class AttnArgs(ctypes.Structure):
 
 
 SIGNATURES = {
+    "pkv_quantize": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _p] + [_i32] * 8 + [_f32] + [_i32] * 4 + [_p, _p]),
     "pkv_decode_attention": (_i32, [ctypes.POINTER(AttnArgs), _p]),
     "pkv_abi_version": (_i32, []),
     "pkv_k_encode": (_i32, _CODEC_ENC),

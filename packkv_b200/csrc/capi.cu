@@ -55,6 +55,16 @@ int32_t pkv_v_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t c
                       bits, first_cb, cuda_stream);
 }
 
+int32_t pkv_quantize(const void* x, int64_t stride_b, int64_t stride_h, int64_t stride_s, uint8_t* codes,
+                     int64_t codes_seq_stride, void* scale, void* zero, int32_t param_blocks, int32_t first_block,
+                     int32_t param_tokens, int32_t first_token, int32_t batch, int32_t heads, int32_t tokens,
+                     int32_t block, float rel, int32_t bits, int32_t mode, int32_t high_precision_zero,
+                     int32_t is_bf16, uint32_t* dev_flags, void* cuda_stream) {
+    QuantArgs q{x, stride_b, stride_h, stride_s, codes, codes_seq_stride, scale, zero, param_blocks, first_block,
+                param_tokens, first_token, batch, heads, tokens, block, rel, bits, mode, high_precision_zero, is_bf16, dev_flags};
+    return launch_quantize(q, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int32_t pkv_decode_attention(const pkv_attn_args* args_host, void* cuda_stream) {
     if (!args_host) return kBadArgument;
     return launch_attention(*args_host, static_cast<cudaStream_t>(cuda_stream));

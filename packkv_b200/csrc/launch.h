@@ -26,6 +26,24 @@ struct CodecBuffers {
     unsigned* flags;            // device status word, OR-ed with DevFlag bits
 };
 
+struct QuantArgs {
+    const void* x;               // (B, H, S, 128) elements; strides in elements, channels contiguous
+    int64_t stride_b, stride_h, stride_s;
+    uint8_t* codes;              // (B, S, H*128) uint8
+    int64_t codes_seq_stride;    // bytes between sequences
+    void* scale; void* zero;     // channel: (B, H, param_blocks, 128); token: (B, param_tokens)
+    int param_blocks, first_block;   // channel mode: capacity in blocks, index of this call's first block
+    int param_tokens, first_token;   // token mode: capacity in tokens, index of this call's first token
+    int batch, heads, tokens, block;
+    float rel;
+    int bits;                    // 0 = do not range-check the codes
+    int mode;                    // 0 = channel, 1 = token
+    int high_precision_zero;
+    int is_bf16;
+    unsigned* flags;
+};
+
+int launch_quantize(const QuantArgs& q, cudaStream_t st);
 int launch_encode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
 int launch_decode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
 

@@ -1,0 +1,58 @@
+"""KV encoder front end: fp16/bf16 K and V -> device-resident compressed layer.
+
+quantise (per-channel or per-token K, per-token V)  ->  optional in-block token reorder  ->
+bit-pack into per-sequence streams.  All arithmetic runs in libpackkv_sm100.so.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import ops
+from .config import QuantMode
+
+
+def _pad16(n: int) -> int:
+    return (n + 15) // 16 * 16
+
+
+def stream_capacity(which: str, n_tokens: int, kv_heads: int, cb: int, bits: int) -> int:
+    """Worst-case bytes of one sequence's stream for n_tokens tokens (16-byte multiple)."""
+    nhid = kv_heads * (128 // ops.HB[which])
+    return _pad16((n_tokens // cb) * nhid * ops.block_bound(which, cb, bits)) + 16
+
+
+def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bits_v: int,
+                k_rel: float, v_rel: float, k_mode: QuantMode = QuantMode.ChannelQuant,
+                cbk: Optional[int] = None, cbv: Optional[int] = None, high_precision_zero: bool = False,
+                capacity_tokens: Optional[int] = None, flags: Optional[torch.Tensor] = None) -> ops.CompressedLayer:
+    """Compresses K, V of shape (B, Hkv, S, 128) (S a multiple of the block sizes).
+
+    `capacity_tokens` reserves stream and table room for later appends.
+    """
+    if k.shape != v.shape or k.dim() != 4 or k.shape[3] != 128:
+        raise ValueError("k and v must both be (B, Hkv, S, 128)")
+    B, H, S, D = k.shape
+    cbk = block if cbk is None else cbk
+    cbv = block if cbv is None else cbv
+    cap_tok = max(S, capacity_tokens or 0)
+    dev = k.device
+    if flags is None:
+        flags = ops.new_flags(dev)
+    kq = ops.quantize(k, block, k_rel, k_mode, bits=bits_k, high_precision_zero=high_precision_zero, flags=flags,
+                      capacity_tokens=cap_tok)
+    vq = ops.quantize(v, block, v_rel, QuantMode.TokenQuant, bits=bits_v, high_precision_zero=high_precision_zero,
+                      flags=flags, capacity_tokens=cap_tok)
+    k_stream = torch.zeros(B, stream_capacity("k", cap_tok, H, cbk, bits_k), dtype=torch.uint8, device=dev)
+    v_stream = torch.zeros(B, stream_capacity("v", cap_tok, H, cbv, bits_v), dtype=torch.uint8, device=dev)
+    k_info = torch.zeros(B, (cap_tok // cbk) * H, 2, dtype=torch.int32, device=dev)
+    v_info = torch.zeros(B, (cap_tok // cbv) * 2 * H, 2, dtype=torch.int32, device=dev)
+    _, _, k_bytes, _ = ops.encode_codes("k", kq.codes, cbk, bits_k, stream=k_stream, info=k_info, flags=flags)
+    _, _, v_bytes, _ = ops.encode_codes("v", vq.codes, cbv, bits_v, stream=v_stream, info=v_info, flags=flags)
+    return ops.CompressedLayer(
+        k_stream=k_stream, k_info=k_info, k_bytes=k_bytes, k_scale=kq.scale, k_zero=kq.zero,
+        v_stream=v_stream, v_info=v_info, v_bytes=v_bytes, v_scale=vq.scale, v_zero=vq.zero,
+        n_comp=S, kv_heads=H, cbk=cbk, cbv=cbv, bits_k=bits_k, bits_v=bits_v,
+        k_mode=ops.K_CHANNEL if k_mode == QuantMode.ChannelQuant else ops.K_TOKEN,
+        high_precision_zero=high_precision_zero)

@@ -113,6 +113,52 @@ K_CHANNEL, K_TOKEN = 0, 1
 
 
 @dataclass
+class Quantised:
+    codes: torch.Tensor     # (B, S, H*128) uint8, the encoders' input layout
+    scale: torch.Tensor     # channel: (B, H, capacity_blocks, 128); token: (B, capacity_tokens)
+    zero: torch.Tensor
+
+
+def quantize(x: torch.Tensor, block: int, rel: float, mode, *, bits: int = 0, high_precision_zero: bool = False,
+             flags: Optional[torch.Tensor] = None, capacity_tokens: Optional[int] = None,
+             scale: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None, first_token: int = 0
+             ) -> Quantised:
+    """Block-quantises x (B, H, S, 128) fp16/bf16 like the reference's quant_ints.
+
+    `mode` is a QuantMode (ChannelQuant or TokenQuant) or the integers K_CHANNEL / K_TOKEN.
+    Passing existing scale/zero tensors with first_token > 0 writes the new parameters behind
+    the ones already there (append path).
+    """
+    _require_cuda(x, flags, scale, zero)
+    if x.dim() != 4 or x.shape[3] != 128 or x.stride(3) != 1 or x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("x must be (B, H, S, 128) fp16/bf16 with contiguous channels")
+    m = getattr(mode, "value", mode)
+    m = {"ChannelQuant": K_CHANNEL, "TokenQuant": K_TOKEN}.get(m, m)
+    if m not in (K_CHANNEL, K_TOKEN):
+        raise RuntimeError("not supported")
+    B, H, S, D = x.shape
+    if S % block:
+        raise ValueError("Tensor shape is not divisible by block size")
+    cap = max(S + first_token, capacity_tokens or 0)
+    dev = x.device
+    if flags is None:
+        flags = new_flags(dev)
+    codes = torch.empty(B, S, H * D, dtype=torch.uint8, device=dev)
+    if scale is None:
+        shape = (B, H, cap // block, D) if m == K_CHANNEL else (B, cap)
+        scale = torch.zeros(shape, dtype=x.dtype, device=dev)
+        zero = torch.zeros(shape, dtype=x.dtype, device=dev)
+    pb = scale.shape[2] if m == K_CHANNEL else 0
+    pt = scale.shape[1] if m == K_TOKEN else 0
+    st = _lib.lib().pkv_quantize(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2), codes.data_ptr(), codes.stride(0),
+                                 scale.data_ptr(), zero.data_ptr(), pb, first_token // block, pt, first_token,
+                                 B, H, S, block, float(rel), bits, m, int(high_precision_zero),
+                                 int(x.dtype == torch.bfloat16), flags.data_ptr(), _stream_ptr())
+    _lib.check(st, "quantize")
+    return Quantised(codes, scale, zero)
+
+
+@dataclass
 class CompressedLayer:
     """Device-resident compressed KV of one layer: per-sequence K and V streams with their
     block tables and quantisation parameters (layouts: include/packkv_sm100.h)."""
