@@ -1,0 +1,325 @@
+"""Headline benchmark: fused decompress-attention decode over a compressed KV cache.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload llama8b]
+
+Workload (default, N=1): Llama-3.1-8B-shaped decode attention -- 32 layers, 32 q heads / 8 KV
+heads, head_dim 128, bf16, batch 16, context 8192 (8064 compressed tokens + 128 uncompressed
+residual tokens per the cache's cut rule), K per-channel 4 bit, V per-token 4 bit, block 64.
+Synthetic KV (packkv_b200.synth) stands in for real-model caches.  One STEP = one decode step's
+attention for all layers = 32 launches of the fused kernel producing `batch` tokens.
+
+Multi-GPU (torchrun, one rank per GPU): sequences are independent, so the batch is sharded with
+no data-path collective; every rank holds a full `batch` of sequences (weak scaling) and the
+reported value is (all ranks' tokens) / (max over ranks of the device time).
+
+JSON line: metric decode tok/s; `value` with q/out resident in HBM; `e2e` through the public
+API with q in pinned host memory and the output read back every layer; `roofline` on the
+algorithmic compressed bytes of the fused kernel; `cpu_baseline` = the reference's own CPU path
+(C++ bit-unpack + torch dequantise + eager attention) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: layers, batch, q_heads, kv_heads, ctx, dtype, bits_k, bits_v, block, cbk, cbv
+    "llama8b": dict(layers=32, batch=16, q_heads=32, kv_heads=8, ctx=8192, dtype="bf16", bits_k=4, bits_v=4,
+                    block=64, cbk=64, cbv=64, name="llama-3.1-8b-shaped decode attention, batch 16, ctx 8192, 4-bit K/V, block 64"),
+    "qwen8b-long": dict(layers=36, batch=8, q_heads=32, kv_heads=8, ctx=32768, dtype="bf16", bits_k=2, bits_v=4,
+                        block=128, cbk=128, cbv=128, name="qwen3-8b-shaped decode attention, batch 8, ctx 32768, 2-bit K / 4-bit V, block 128"),
+    "llama8b-2l": dict(layers=2, batch=16, q_heads=32, kv_heads=8, ctx=8192, dtype="bf16", bits_k=4, bits_v=4,
+                       block=64, cbk=64, cbv=64, name="2 layers of the llama-3.1-8b-shaped workload (profiling case)"),
+    "tiny": dict(layers=2, batch=2, q_heads=8, kv_heads=2, ctx=1024, dtype="bf16", bits_k=4, bits_v=4,
+                 block=64, cbk=64, cbv=64, name="tiny smoke workload"),
+}
+RECENT = 192   # buffer_size of every reference script (128 + 64)
+
+
+def split_context(ctx: int, block: int, recent: int = RECENT):
+    n_blocks = max(0, (ctx + block - ctx % block - recent) // block)
+    return n_blocks * block, ctx - n_blocks * block
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.stop_flag = index, [], False
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def start(self):
+        self.thread.start()
+
+    def stop(self):
+        self.stop_flag = True
+        self.thread.join(timeout=6)
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+def build_layers(w, device, dtype):
+    from packkv_b200 import encode, synth
+    from packkv_b200.config import QuantMode
+    n_comp, n_res = split_context(w["ctx"], w["block"])
+    layers = []
+    for li in range(w["layers"]):
+        k, v = synth.synth_kv(w["batch"], w["kv_heads"], w["ctx"], 128, seed=1000 + li, dtype=dtype, device=device, apply_rope=True)
+        layer = encode.compress_kv(k[:, :, :n_comp], v[:, :, :n_comp], block=w["block"], bits_k=w["bits_k"], bits_v=w["bits_v"],
+                                   k_rel=synth.rel_for_bits(w["bits_k"]), v_rel=synth.rel_for_bits(w["bits_v"]),
+                                   k_mode=QuantMode.ChannelQuant, cbk=w["cbk"], cbv=w["cbv"])
+        # trim the streams to what is used (setup only), keeping 16-byte multiples
+        kb = (int(layer.k_bytes.max().item()) + 31) // 16 * 16
+        vb = (int(layer.v_bytes.max().item()) + 31) // 16 * 16
+        layer.k_stream = layer.k_stream[:, :kb].contiguous()
+        layer.v_stream = layer.v_stream[:, :vb].contiguous()
+        k_res = k[:, :, n_comp:].contiguous()
+        v_res = v[:, :, n_comp:].contiguous()
+        layers.append((layer, k_res, v_res))
+        del k, v
+    return layers, n_comp, n_res
+
+
+def layer_bytes(layer, k_res, v_res, n_res, batch, q_heads):
+    """Algorithmic HBM bytes of one fused launch: streams (headers included) + block tables +
+    scales/zeros + residual K/V + q + out."""
+    n = layer.stream_bytes()
+    n += 2 * batch * layer.kv_heads * n_res * 128 * k_res.element_size()
+    n += 2 * batch * q_heads * 128 * 2
+    return n
+
+
+def run_ours(args, w, rank, world, device):
+    from packkv_b200 import ops
+    dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
+    layers, n_comp, n_res = build_layers(w, device, dtype)
+    B, Hq = w["batch"], w["q_heads"]
+    g = torch.Generator(device=device).manual_seed(77 + rank)
+    q_dev = [torch.randn(B, Hq, 128, generator=g, device=device, dtype=torch.float32).to(dtype) for _ in layers]
+    out_dev = [torch.empty_like(q) for q in q_dev]
+    flags = ops.new_flags(device)
+    alg_bytes = sum(layer_bytes(L, kr, vr, n_res, B, Hq) for L, kr, vr in layers)
+
+    def step_resident():
+        for (L, kr, vr), q, o in zip(layers, q_dev, out_dev):
+            ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags)
+
+    q_host = [q.cpu().pin_memory() for q in q_dev]
+    out_host = [torch.empty(B, Hq, 128, dtype=dtype).pin_memory() for _ in layers]
+    q_stage = torch.empty(B, Hq, 128, dtype=dtype, device=device)
+
+    def step_e2e():
+        for (L, kr, vr), qh, oh, o in zip(layers, q_host, out_host, out_dev):
+            q_stage.copy_(qh, non_blocking=True)
+            ops.decode_attention(q_stage, L, kr, vr, n_res, out=o, flags=flags)
+            oh.copy_(o, non_blocking=True)
+
+    def timed(fn, steps):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    ms = timed(step_resident, args.steps)
+    clocks = sampler.stop()
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    torch.cuda.synchronize()
+    if int(flags.item()) != 0:
+        raise RuntimeError(f"device flags set: {int(flags.item())}")
+
+    if rank != 0:
+        return None
+    ms_per_step = ms / args.steps
+    tokens = B * world
+    peak, peak_kind = measured_peak_gbs()
+    per_launch_ms = ms_per_step / len(layers)
+    achieved = (alg_bytes / len(layers)) / (per_launch_ms * 1e-3) / 1e9
+    line = {
+        "metric": "fused decompress-attention decode throughput", "value": tokens / (ms_per_step * 1e-3), "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": w["name"], "layers": w["layers"], "batch_per_gpu": B, "context": w["ctx"],
+                   "compressed_tokens": n_comp, "residual_tokens": n_res, "k_quant": "channel", "v_quant": "token",
+                   "l2": f"working set {alg_bytes / 1e9:.2f} GB per step >> 126 MB L2 (no flush needed)",
+                   "sharding": "batch (independent sequences, no collective)"},
+        "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tok/s",
+                "h2d_bytes_per_step": len(layers) * B * Hq * 128 * 2, "d2h_bytes_per_step": len(layers) * B * Hq * 128 * 2},
+        "gpu_launches": len(layers) * args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": peak_kind, "traffic": None,
+                     "algorithmic_bytes_per_launch": alg_bytes // len(layers), "kernel": "attn_decode_kernel",
+                     "avg_launch_ms": per_launch_ms},
+        "compressed_kv_gbs": achieved,
+        "clocks": clocks,
+    }
+    return line
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_path(w, sample_batch: int, repeats: int, threads: int):
+    """The reference's CPU path for one layer of `sample_batch` sequences: bit-unpack with its
+    C++ codec (single-threaded by construction), dequantise and eager attention in torch."""
+    import numpy as np
+    from oracle import codec
+    from oracle import quant as Q
+    from packkv_b200 import synth
+    torch.set_num_threads(threads)
+    dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
+    n_comp, n_res = split_context(w["ctx"], w["block"])
+    k, v = synth.synth_kv(sample_batch, w["kv_heads"], w["ctx"], 128, seed=1000, dtype=dtype, apply_rope=True)
+    q = synth.synth_q(sample_batch, w["q_heads"], 128, seed=1000, dtype=dtype)
+    kc, kz, ks = Q.quant_ints(k[:, :, :n_comp], w["block"], synth.rel_for_bits(w["bits_k"]), "channel")
+    vc, vz, vs = Q.quant_ints(v[:, :, :n_comp], w["block"], synth.rel_for_bits(w["bits_v"]), "token")
+    refc = codec.reference()
+    impl = refc if refc is not None and refc.supports("k", w["kv_heads"] * 128, w["cbk"], w["bits_k"]) else codec.restated()
+    kind = "reference" if impl is refc else "port"
+    vcb = 128 if kind == "reference" else w["cbv"]
+
+    def seq_codes(c5, s):
+        return c5[s].flatten(1, 2).permute(1, 0, 2).flatten(1, 2).contiguous().to(torch.uint8).numpy()
+
+    packed = []
+    for s in range(sample_batch):
+        kk, vv = seq_codes(kc, s), seq_codes(vc, s)
+        if vv.shape[0] % vcb:
+            vv = np.concatenate([vv, np.zeros((vcb - vv.shape[0] % vcb, vv.shape[1]), np.uint8)])
+        packed.append((impl.encode("k", kk, w["cbk"], w["bits_k"]), impl.encode("v", vv, vcb, w["bits_v"]), kk.shape, vv.shape))
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        kd_list, vd_list = [], []
+        for (ke, ve, kshape, vshape) in packed:
+            kcodes = impl.decode("k", ke[0], ke[1], kshape[0], kshape[1], w["cbk"], w["bits_k"])
+            vcodes = impl.decode("v", ve[0], ve[1], vshape[0], vshape[1], vcb, w["bits_v"])[:n_comp]
+            kd_list.append(torch.from_numpy(kcodes).view(n_comp, w["kv_heads"], 128).permute(1, 0, 2))
+            vd_list.append(torch.from_numpy(vcodes).view(n_comp, w["kv_heads"], 128).permute(1, 0, 2))
+        kq = torch.stack(kd_list).to(dtype).reshape(sample_batch, w["kv_heads"], -1, w["block"], 128)
+        vq = torch.stack(vd_list).to(dtype).reshape(sample_batch, w["kv_heads"], -1, w["block"], 128)
+        K = torch.cat([Q.dequant(kq, kz, ks), k[:, :, n_comp:]], 2)
+        V = torch.cat([Q.dequant(vq, vz, vs), v[:, :, n_comp:]], 2)
+        out = Q.eager_attention(q, K, V)
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    t_layer = times[len(times) // 2]
+    tok_s = sample_batch / (t_layer * w["layers"])
+    return tok_s, kind, t_layer, float(out.float().abs().max())
+
+
+def run_reference(args, w):
+    threads = os.cpu_count() or 1
+    sample_batch = 2 if w["ctx"] <= 8192 else 1
+    tok_s, kind, t_layer, _ = cpu_reference_path(w, sample_batch, repeats=max(1, min(args.steps, 3)), threads=threads)
+    n_comp, n_res = split_context(w["ctx"], w["block"])
+    sample = (f"1 layer x {sample_batch} sequences of the workload per step (median {t_layer * 1e3:.0f} ms): C++ bit-unpack "
+              f"(1 thread) + torch dequantise + eager attention ({threads} threads); tok/s = sequences / (layer time x {w['layers']} layers)")
+    return {
+        "impl": "reference", "metric": "fused decompress-attention decode throughput", "value": tok_s, "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_layer * w["layers"] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": w["name"], "layers": w["layers"], "batch_per_gpu": w["batch"], "context": w["ctx"],
+                   "compressed_tokens": n_comp, "residual_tokens": n_res, "k_quant": "channel", "v_quant": "token"},
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args, w)), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=device)
+    line = run_ours(args, w, rank, world, device)
+    if rank == 0:
+        if not args.no_cpu_baseline:
+            t0 = time.perf_counter()
+            tok_s, kind, t_layer, _ = cpu_reference_path(w, 1, repeats=1, threads=os.cpu_count() or 1)
+            line["cpu_baseline"] = {
+                "value": tok_s, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": kind,
+                "sample": f"1 layer x 1 sequence ({t_layer * 1e3:.0f} ms, setup {time.perf_counter() - t0:.0f} s): C++ bit-unpack (1 thread) + "
+                          f"torch dequantise + eager attention (all threads); scaled by {w['layers']} layers"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
