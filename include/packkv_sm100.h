@@ -76,6 +76,34 @@ int32_t pkv_v_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t c
                      int32_t first_cb, void* cuda_stream);
 
 /*
+ * The reference's two-step GPU API, kept for its callers (evaluation/evaluation.py:398-715).
+ * pkv_kq_mat_vec_mul replaces kq_mat_vec_mul (packkv_cuda_ext/src/kernels.cu:611-630):
+ *   kq_out[h, n] = sum_d q[h, d] * code[n, h*128 + d], q given in the reference's lane-permuted
+ *   order (evaluation.py:465-468), kq_out (hidden/128, ctx_len) in the element type.
+ * pkv_wv_mat_vec_mul replaces wv_mat_vec_mul (kernels.cu:842-859):
+ *   wv_out[c] += sum_n w[c/128, n] * code[n, c], wv_out (hidden) float32, accumulated into.
+ * One sequence per call; `stream_bytes` = valid bytes of the stream (16-byte aligned base).
+ * Unlike the reference these do not synchronise or time themselves.
+ */
+int32_t pkv_kq_mat_vec_mul(const uint8_t* stream, int64_t stream_bytes, const uint32_t* block_info, const void* q,
+                           void* kq_out, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb, int32_t bits,
+                           int32_t is_bf16, uint32_t* dev_flags, void* cuda_stream);
+int32_t pkv_wv_mat_vec_mul(const uint8_t* stream, int64_t stream_bytes, const uint32_t* block_info, const void* w,
+                           float* wv_out, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb, int32_t bits,
+                           int32_t is_bf16, uint32_t* dev_flags, void* cuda_stream);
+/*
+ * pkv_fused_kq replaces fused_kq_launcher (packkv_cuda_ext/src/fused_kernels.cu:171-185):
+ *   our_kq[m, n] = (sum_d q[m, d] * zero[n] + t[m, n]) * scale[n];  q (M, K), t and our_kq (M, N).
+ * pkv_fused_wv replaces fused_wv_launcher (fused_kernels.cu:355-369):
+ *   our_wv[m, d] = sum_n w[m, n] * zero[n] * scale[n] + term1[m, d];  w (M, N), term1 and our_wv (M, D).
+ * Any M, N, K, D (the reference accepts only M in {8, 40} and K = D = 128).
+ */
+int32_t pkv_fused_kq(void* our_kq, const void* q, const void* zero, const void* scale, const void* t, int32_t M,
+                     int32_t N, int32_t K, int32_t is_bf16, void* cuda_stream);
+int32_t pkv_fused_wv(void* our_wv, const void* w, const void* zero, const void* scale, const void* term1, int32_t M,
+                     int32_t N, int32_t D, int32_t is_bf16, void* cuda_stream);
+
+/*
  * Block quantiser: fp16/bf16 K or V (batch, heads, tokens, 128) -> uint8 codes laid out as the
  * encoders' input (batch, tokens, heads*128), plus scale and zero-point in the element type.
  * Replaces quant_ints (utils/compute.py:84-112) bit for bit, including the rounding to the

@@ -37,6 +37,10 @@ class AttnArgs(ctypes.Structure):
 
 
 SIGNATURES = {
+    "pkv_kq_mat_vec_mul": (_i32, [_p, _i64, _p, _p, _p] + [_i32] * 6 + [_p, _p]),
+    "pkv_wv_mat_vec_mul": (_i32, [_p, _i64, _p, _p, _p] + [_i32] * 6 + [_p, _p]),
+    "pkv_fused_kq": (_i32, [_p] * 5 + [_i32] * 4 + [_p]),
+    "pkv_fused_wv": (_i32, [_p] * 5 + [_i32] * 4 + [_p]),
     "pkv_quantize": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _p] + [_i32] * 8 + [_f32] + [_i32] * 4 + [_p, _p]),
     "pkv_decode_attention": (_i32, [ctypes.POINTER(AttnArgs), _p]),
     "pkv_abi_version": (_i32, []),

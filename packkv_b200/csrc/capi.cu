@@ -55,6 +55,30 @@ int32_t pkv_v_decode(const uint8_t* stream, int64_t stream_seq_stride, int64_t c
                       bits, first_cb, cuda_stream);
 }
 
+int32_t pkv_kq_mat_vec_mul(const uint8_t* stream, int64_t stream_bytes, const uint32_t* block_info, const void* q,
+                           void* kq_out, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb, int32_t bits,
+                           int32_t is_bf16, uint32_t* dev_flags, void* cuda_stream) {
+    LegacyArgs a{stream, stream_bytes, block_info, q, kq_out, ctx_len, hidden, cb, hb, bits, is_bf16, dev_flags};
+    return launch_legacy_matvec(true, a, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_wv_mat_vec_mul(const uint8_t* stream, int64_t stream_bytes, const uint32_t* block_info, const void* w,
+                           float* wv_out, int32_t ctx_len, int32_t hidden, int32_t cb, int32_t hb, int32_t bits,
+                           int32_t is_bf16, uint32_t* dev_flags, void* cuda_stream) {
+    LegacyArgs a{stream, stream_bytes, block_info, w, wv_out, ctx_len, hidden, cb, hb, bits, is_bf16, dev_flags};
+    return launch_legacy_matvec(false, a, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_fused_kq(void* our_kq, const void* q, const void* zero, const void* scale, const void* t, int32_t M,
+                     int32_t N, int32_t K, int32_t is_bf16, void* cuda_stream) {
+    return launch_fused_epilogue(true, our_kq, q, zero, scale, t, M, N, K, is_bf16, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_fused_wv(void* our_wv, const void* w, const void* zero, const void* scale, const void* term1, int32_t M,
+                     int32_t N, int32_t D, int32_t is_bf16, void* cuda_stream) {
+    return launch_fused_epilogue(false, our_wv, w, zero, scale, term1, M, N, D, is_bf16, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int32_t pkv_quantize(const void* x, int64_t stride_b, int64_t stride_h, int64_t stride_s, uint8_t* codes,
                      int64_t codes_seq_stride, void* scale, void* zero, int32_t param_blocks, int32_t first_block,
                      int32_t param_tokens, int32_t first_token, int32_t batch, int32_t heads, int32_t tokens,

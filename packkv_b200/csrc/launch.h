@@ -43,6 +43,18 @@ struct QuantArgs {
     unsigned* flags;
 };
 
+struct LegacyArgs {
+    const uint8_t* stream; int64_t stream_bytes;   // one sequence; valid bytes
+    const uint32_t* info;
+    const void* vec;      // kq: q (hidden/128, 128) lane-permuted; wv: w (hidden/128, ctx_len)
+    void* out;            // kq: (hidden/128, ctx_len) element type; wv: (hidden) float, accumulated into
+    int ctx_len, hidden, cb, hb, bits, is_bf16;
+    unsigned* flags;
+};
+
+int launch_legacy_matvec(bool is_k, const LegacyArgs& a, cudaStream_t st);
+int launch_fused_epilogue(bool is_kq, void* out, const void* a, const void* zero, const void* scale, const void* t,
+                          int M, int N, int K, int is_bf16, cudaStream_t st);
 int launch_quantize(const QuantArgs& q, cudaStream_t st);
 int launch_encode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
 int launch_decode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
