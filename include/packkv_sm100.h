@@ -120,6 +120,28 @@ int32_t pkv_quantize(const void* x, int64_t stride_b, int64_t stride_h, int64_t 
                      int32_t is_bf16, uint32_t* dev_flags, void* cuda_stream);
 
 /*
+ * Rotary embedding of new K tokens inside the cache; replaces apply_rotary_pos_emb_single
+ * (utils/compute.py:32-43) bit for bit.  x/out (batch, heads, tokens, dim <= 128), cos/sin
+ * (batch or 1, tokens, dim) with cs_stride_b = 0 to broadcast; strides in elements.
+ */
+int32_t pkv_rope(const void* x, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, const void* cos,
+                 const void* sin, int64_t cs_stride_b, void* out, int64_t o_stride_b, int64_t o_stride_h,
+                 int64_t o_stride_s, int32_t batch, int32_t heads, int32_t tokens, int32_t dim, int32_t is_bf16,
+                 void* cuda_stream);
+
+/*
+ * Dense reconstruction of quantised tokens, (code + zero) * scale or code * scale + min with the
+ * reference's roundings (utils/compute.py:173-178).  codes (batch, tokens, heads*128) as written
+ * by pkv_quantize / pkv_{k,v}_decode; scale/zero laid out as in pkv_quantize, the first token of
+ * `codes` being token `first_token` of the sequence.  out (batch, heads, tokens, 128).
+ */
+int32_t pkv_dequantize(const uint8_t* codes, int64_t codes_seq_stride, const void* scale, const void* zero,
+                       int32_t param_blocks, int32_t param_tokens, int32_t first_token, void* out,
+                       int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int32_t batch, int32_t heads,
+                       int32_t tokens, int32_t block, int32_t mode, int32_t high_precision_zero, int32_t is_bf16,
+                       void* cuda_stream);
+
+/*
  * Fused decompress-attention decode: out = softmax(q K^T * scaling) V for ONE new query token
  * per sequence over (compressed tokens + uncompressed residual tokens), reading the packed
  * streams directly.  Replaces the chain kq_mat_vec_mul -> fused_kq -> torch softmax ->
@@ -141,10 +163,11 @@ typedef struct pkv_attn_args {
     void* out;                  /* (batch, kv_heads*group, 128) */
     const uint8_t* k_stream; int64_t k_seq_stride; int64_t k_capacity;
     const uint32_t* k_info;  int64_t k_info_seq_stride;   /* block = ctx_blk*kv_heads + head */
-    const void* k_scale; const void* k_zero;              /* channel: (batch, kv_heads, n_comp/cbk, 128); token: (batch, n_comp) */
+    const void* k_scale; const void* k_zero;              /* channel: (batch, kv_heads, param_blocks, 128); token: (batch, param_tokens) */
     const uint8_t* v_stream; int64_t v_seq_stride; int64_t v_capacity;
     const uint32_t* v_info;  int64_t v_info_seq_stride;   /* block = ctx_blk*2*kv_heads + 2*head + half */
-    const void* v_scale; const void* v_zero;              /* (batch, n_comp) */
+    const void* v_scale; const void* v_zero;              /* (batch, param_tokens) */
+    int32_t param_blocks, param_tokens;                   /* row lengths of the parameter arrays (>= n_comp/cbk, >= n_comp) */
     const void* k_res; const void* v_res;                 /* (batch, kv_heads, res_capacity, 128); first n_res tokens valid */
     int64_t res_seq_stride, res_head_stride;              /* in elements */
     int32_t n_res;

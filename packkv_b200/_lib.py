@@ -28,7 +28,7 @@ class AttnArgs(ctypes.Structure):
         ("k_stream", _p), ("k_seq_stride", _i64), ("k_capacity", _i64), ("k_info", _p), ("k_info_seq_stride", _i64),
         ("k_scale", _p), ("k_zero", _p),
         ("v_stream", _p), ("v_seq_stride", _i64), ("v_capacity", _i64), ("v_info", _p), ("v_info_seq_stride", _i64),
-        ("v_scale", _p), ("v_zero", _p),
+        ("v_scale", _p), ("v_zero", _p), ("param_blocks", _i32), ("param_tokens", _i32),
         ("k_res", _p), ("v_res", _p), ("res_seq_stride", _i64), ("res_head_stride", _i64),
         ("n_res", _i32), ("batch", _i32), ("kv_heads", _i32), ("group", _i32), ("n_comp", _i32),
         ("cbk", _i32), ("cbv", _i32), ("bits_k", _i32), ("bits_v", _i32),
@@ -41,6 +41,8 @@ SIGNATURES = {
     "pkv_wv_mat_vec_mul": (_i32, [_p, _i64, _p, _p, _p] + [_i32] * 6 + [_p, _p]),
     "pkv_fused_kq": (_i32, [_p] * 5 + [_i32] * 4 + [_p]),
     "pkv_fused_wv": (_i32, [_p] * 5 + [_i32] * 4 + [_p]),
+    "pkv_rope": (_i32, [_p, _i64, _i64, _i64, _p, _p, _i64, _p, _i64, _i64, _i64] + [_i32] * 5 + [_p]),
+    "pkv_dequantize": (_i32, [_p, _i64, _p, _p, _i32, _i32, _i32, _p, _i64, _i64, _i64] + [_i32] * 7 + [_p]),
     "pkv_quantize": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _p] + [_i32] * 8 + [_f32] + [_i32] * 4 + [_p, _p]),
     "pkv_decode_attention": (_i32, [ctypes.POINTER(AttnArgs), _p]),
     "pkv_abi_version": (_i32, []),

@@ -81,7 +81,7 @@ class PackKVCacheConfig:
     def from_str(text: str) -> "PackKVCacheConfig":
         """Inverse of str().  The reference evaluates the string as Python; here only
         literals and the enum constructors that str() emits are accepted."""
-        tree = ast.parse(text.strip(), mode="eval")
+        import re
 
         def ev(node):
             if isinstance(node, ast.Dict):
@@ -90,15 +90,12 @@ class PackKVCacheConfig:
                 return tuple(ev(e) for e in node.elts)
             if isinstance(node, ast.Constant):
                 return node.value
-            if isinstance(node, ast.Compare) and len(node.ops) == 1 and isinstance(node.ops[0], ast.Lt):
-                # "<QuantMode.ChannelQuant: 'ChannelQuant'>" is not valid Python; see below
-                raise ValueError("unparseable enum repr")
             raise ValueError("unsupported expression in config string")
 
-        # enum members inside tuples print as <QuantMode.X: 'X'>; rewrite them to their values
-        import re
+        # enum members inside the quant_method tuple print as <QuantMode.X: 'X'>, which is not
+        # Python; rewrite them to their string values before parsing
         cleaned = re.sub(r"<QuantMode\.\w+: '(\w+)'>", r"'\1'", text.strip())
-        d = ev(ast.parse(cleaned, mode="eval").body) if cleaned != text.strip() else ev(tree.body)
+        d = ev(ast.parse(cleaned, mode="eval").body)
         if d["enable_quant"]:
             qm = d["quant_method"]
             names = tuple(m if isinstance(m, str) else m.value for m in qm)

@@ -227,8 +227,8 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
         uint8_t* st = stile + tl * P.rows * P.prow;
 
         if (KMODE == kKToken && i == 0) {
-            const T* ks = reinterpret_cast<const T*>(a.k_scale) + (int64_t)b * a.n_comp + t0;
-            const T* kz = reinterpret_cast<const T*>(a.k_zero) + (int64_t)b * a.n_comp + t0;
+            const T* ks = reinterpret_cast<const T*>(a.k_scale) + (int64_t)b * a.param_tokens + t0;
+            const T* kz = reinterpret_cast<const T*>(a.k_zero) + (int64_t)b * a.param_tokens + t0;
             for (int t = lane; t < P.tile; t += 32) {
                 ksz[t] = ks[t];
                 ksz[P.tile + t] = HP ? kz[t] : Tr<T>::from_float(Tr<T>::to_float(kz[t]) - Tr<T>::kBias);
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
             // channel mode: per-(block, channel) scale and zero for this lane's 32 channels
             T2 ksc[8][2], kzb[8][2];
             if (KMODE == kKChannel) {
-                const int64_t row = ((int64_t)(b * a.kv_heads + h) * (a.n_comp / a.cbk) + (t0 / a.cbk + i)) * kD + 32 * c;
+                const int64_t row = ((int64_t)(b * a.kv_heads + h) * a.param_blocks + (t0 / a.cbk + i)) * kD + 32 * c;
                 const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_scale) + row);
                 const uint4* zp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_zero) + row);
 #pragma unroll
@@ -498,8 +498,8 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
                     row1[t] = Tr<T>::from_float(fast_exp(Tr<T>::to_float(row1[t]) - M1) * I1);
                 }
             }
-            const T* vs = reinterpret_cast<const T*>(a.v_scale) + (int64_t)b * a.n_comp + t0;
-            const T* vz = reinterpret_cast<const T*>(a.v_zero) + (int64_t)b * a.n_comp + t0;
+            const T* vs = reinterpret_cast<const T*>(a.v_scale) + (int64_t)b * a.param_tokens + t0;
+            const T* vz = reinterpret_cast<const T*>(a.v_zero) + (int64_t)b * a.param_tokens + t0;
             for (int t = lane; t < P.tile; t += 32) {
                 vsz[t] = vs[t];
                 vsz[P.tile + t] = HP ? vz[t] : Tr<T>::from_float(Tr<T>::to_float(vz[t]) - Tr<T>::kBias);
@@ -719,6 +719,7 @@ int launch_attention(const AttnArgs& a, cudaStream_t st) {
         if (a.k_mode != kKChannel && a.k_mode != kKToken) return kUnsupported;
         const int tile = (a.cbk == 128 || a.cbv == 128) ? 128 : 64;
         if (a.n_comp % tile) return kBadArgument;
+        if (a.param_tokens < a.n_comp || (a.k_mode == kKChannel && a.param_blocks < a.n_comp / a.cbk)) return kBadArgument;
         if (!a.k_stream || !a.k_info || !a.k_scale || !a.k_zero || !a.v_stream || !a.v_info || !a.v_scale || !a.v_zero) return kBadArgument;
         if ((reinterpret_cast<uintptr_t>(a.k_stream) & 15) || (a.k_seq_stride & 15) || (reinterpret_cast<uintptr_t>(a.v_stream) & 15) ||
             (a.v_seq_stride & 15) || (a.k_capacity & 15) || (a.v_capacity & 15))

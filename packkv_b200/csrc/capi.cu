@@ -89,6 +89,25 @@ int32_t pkv_quantize(const void* x, int64_t stride_b, int64_t stride_h, int64_t 
     return launch_quantize(q, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int32_t pkv_rope(const void* x, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, const void* cos,
+                 const void* sin, int64_t cs_stride_b, void* out, int64_t o_stride_b, int64_t o_stride_h,
+                 int64_t o_stride_s, int32_t batch, int32_t heads, int32_t tokens, int32_t dim, int32_t is_bf16,
+                 void* cuda_stream) {
+    RopeArgs r{x, x_stride_b, x_stride_h, x_stride_s, cos, sin, cs_stride_b, out, o_stride_b, o_stride_h, o_stride_s,
+               batch, heads, tokens, dim, is_bf16};
+    return launch_rope(r, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_dequantize(const uint8_t* codes, int64_t codes_seq_stride, const void* scale, const void* zero,
+                       int32_t param_blocks, int32_t param_tokens, int32_t first_token, void* out,
+                       int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int32_t batch, int32_t heads,
+                       int32_t tokens, int32_t block, int32_t mode, int32_t high_precision_zero, int32_t is_bf16,
+                       void* cuda_stream) {
+    DequantArgs q{codes, codes_seq_stride, scale, zero, param_blocks, param_tokens, first_token, out, o_stride_b,
+                  o_stride_h, o_stride_s, batch, heads, tokens, block, mode, high_precision_zero, is_bf16};
+    return launch_dequantize(q, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int32_t pkv_decode_attention(const pkv_attn_args* args_host, void* cuda_stream) {
     if (!args_host) return kBadArgument;
     return launch_attention(*args_host, static_cast<cudaStream_t>(cuda_stream));

@@ -55,6 +55,21 @@ struct LegacyArgs {
 int launch_legacy_matvec(bool is_k, const LegacyArgs& a, cudaStream_t st);
 int launch_fused_epilogue(bool is_kq, void* out, const void* a, const void* zero, const void* scale, const void* t,
                           int M, int N, int K, int is_bf16, cudaStream_t st);
+struct RopeArgs {
+    const void* x; int64_t x_stride_b, x_stride_h, x_stride_s;   // (B, H, T, dim), strides in elements
+    const void* cos; const void* sin; int64_t cs_stride_b;       // (B or 1, T, dim); cs_stride_b = 0 broadcasts
+    void* out; int64_t o_stride_b, o_stride_h, o_stride_s;
+    int batch, heads, tokens, dim, is_bf16;
+};
+struct DequantArgs {
+    const uint8_t* codes; int64_t codes_seq_stride;               // (B, T, H*128)
+    const void* scale; const void* zero;
+    int param_blocks, param_tokens, first_token;                  // layout of scale/zero as in QuantArgs
+    void* out; int64_t o_stride_b, o_stride_h, o_stride_s;         // (B, H, T, 128), strides in elements
+    int batch, heads, tokens, block, mode, high_precision_zero, is_bf16;
+};
+int launch_rope(const RopeArgs& r, cudaStream_t st);
+int launch_dequantize(const DequantArgs& q, cudaStream_t st);
 int launch_quantize(const QuantArgs& q, cudaStream_t st);
 int launch_encode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
 int launch_decode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);

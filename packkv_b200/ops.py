@@ -230,6 +230,10 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
         a.v_stream, a.v_seq_stride, a.v_capacity = L.v_stream.data_ptr(), L.v_stream.stride(0), L.v_stream.shape[1] & ~15
         a.v_info, a.v_info_seq_stride = L.v_info.data_ptr(), L.v_info.shape[1]
         a.v_scale, a.v_zero = L.v_scale.data_ptr(), L.v_zero.data_ptr()
+        a.param_tokens = L.v_scale.shape[1]
+        a.param_blocks = L.k_scale.shape[2] if L.k_mode == K_CHANNEL else 0
+        if L.k_mode == K_TOKEN and L.k_scale.shape[1] != L.v_scale.shape[1]:
+            raise ValueError("token-mode K and V parameter arrays must have the same row length")
         a.cbk, a.cbv, a.bits_k, a.bits_v = L.cbk, L.cbv, L.bits_k, L.bits_v
         a.k_mode, a.high_precision_zero = L.k_mode, int(L.high_precision_zero)
     if n_res > 0:
@@ -245,4 +249,40 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
     a.flags = flags.data_ptr()
     st = _lib.lib().pkv_decode_attention(ctypes.byref(a), _stream_ptr())
     _lib.check(st, "decode_attention")
+    return out
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(x * cos) + (rotate_half(x) * sin) with the reference's per-op rounding.
+    x (B, H, T, D) with contiguous channels; cos/sin (B or 1, T, D)."""
+    _require_cuda(x, cos, sin, out)
+    if x.dim() != 4 or x.stride(3) != 1 or x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("x must be (B, H, T, D) fp16/bf16 with contiguous channels")
+    B, H, T, D = x.shape
+    cos, sin = cos.to(x.dtype).contiguous(), sin.to(x.dtype).contiguous()
+    if cos.shape[-2:] != (T, D) or sin.shape != cos.shape:
+        raise ValueError("cos/sin must be (B or 1, T, D)")
+    if out is None:
+        out = torch.empty(B, H, T, D, dtype=x.dtype, device=x.device)
+    cs_stride = 0 if cos.shape[0] == 1 else T * D
+    st = _lib.lib().pkv_rope(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2), cos.data_ptr(), sin.data_ptr(), cs_stride,
+                             out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), B, H, T, D,
+                             int(x.dtype == torch.bfloat16), _stream_ptr())
+    _lib.check(st, "rope")
+    return out
+
+
+def dequantize(codes: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, heads: int, block: int, mode: int, *,
+               first_token: int = 0, high_precision_zero: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """codes (B, T, heads*128) uint8 + scale/zero -> dense (B, heads, T, 128) in scale's dtype."""
+    _require_cuda(codes, scale, zero, out)
+    B, T, _ = codes.shape
+    if out is None:
+        out = torch.empty(B, heads, T, 128, dtype=scale.dtype, device=codes.device)
+    pb = scale.shape[2] if mode == K_CHANNEL else 0
+    pt = scale.shape[1] if mode == K_TOKEN else 0
+    st = _lib.lib().pkv_dequantize(codes.data_ptr(), codes.stride(0), scale.data_ptr(), zero.data_ptr(), pb, pt, first_token,
+                                   out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), B, heads, T, block, mode,
+                                   int(high_precision_zero), int(scale.dtype == torch.bfloat16), _stream_ptr())
+    _lib.check(st, "dequantize")
     return out
