@@ -113,6 +113,9 @@ struct AttnDev {
     int prow;            // bytes of one row of the score / probability tile
     int warp_smem;       // bytes of per-warp shared memory
     int cta_off;         // byte offset of the CTA-shared block
+    int out_off;         // byte offset, inside a warp's region, of its rows of the CTA's reduced output
+    int tile_shift, cbk_shift, cbv_shift;   // log2 of tile, cbk, cbv
+    int nkb_shift, nvi_shift;               // log2 of K blocks per tile and of V blocks (2 halves x token blocks) per tile
 };
 
 // CTA-shared block (cluster-visible)
@@ -121,12 +124,17 @@ struct CtaShared {
     float cl_l[8];       // this CTA's sum of exp(s - cl_m) per head
     float wm[kAW][8];    // per-warp scratch
     float gM[8], gInvL[8];
-    float out[8][kD];    // this CTA's accumulators
 };
+// The CTA's reduced accumulators out[head][channel] (read by rank 0 through distributed shared
+// memory) live in the warps' exchange tiles, which are idle by then: head hd -> warp hd & 3,
+// float offset (hd >> 2) * kD.
+__device__ __forceinline__ float* cta_out_row(uint8_t* smem, int warp_smem, int out_off, int hd) {
+    return reinterpret_cast<float*>(smem + (hd & 3) * warp_smem + out_off) + (hd >> 2) * kD;
+}
 
 // =================================================================================================
 template <typename T, int KMODE, bool HP>
-__global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) {
+__global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev P) {
     using T2 = typename Tr<T>::T2;
     extern __shared__ __align__(16) uint8_t smem[];
     cg::cluster_group cluster = cg::this_cluster();
@@ -146,13 +154,21 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
     uint8_t* stile = reinterpret_cast<uint8_t*>(ksz + 2 * P.tile);   // [tpw][rows][prow] scores -> probabilities
     float* rsc = reinterpret_cast<float*>(stile + P.tpw * P.rows * P.prow);   // [rpw][8] residual scores
     CtaShared* cs = reinterpret_cast<CtaShared*>(smem + P.cta_off);
+    // 32-bit shared-window addresses for the hot loops
+    const unsigned wbase_a = smem_addr(wbase), xch_a = smem_addr(xch), vsz_a = smem_addr(vsz), stile_a = smem_addr(stile);
+    // K exchange: store address of this lane's 4 channel bytes for even / odd tokens; fragment rows g and g+8
+    const unsigned kst_even = xch_a + (((lane >> 2) << 4) | ((lane & 3) << 2)), kst_odd = xch_a + ((((lane >> 2) ^ 1) << 4) | ((lane & 3) << 2));
+    const unsigned kld0 = xch_a + g * 128 + (((2 * c) ^ (g & 1)) << 4), kld1 = xch_a + g * 128 + (((2 * c + 1) ^ (g & 1)) << 4);
+    // V exchange: row = lane (channel), chunk swizzle by (row >> 1) & 3; fragment rows g, g+8, g+16, g+24 share that swizzle
+    const unsigned vst = xch_a + lane * 64, vsw = ((lane >> 1) & 3) << 4;
+    const unsigned vld = xch_a + g * 64 + ((c ^ ((g >> 1) & 3)) << 4);
 
     const int my_tiles = gw < P.tiles_total ? (P.tiles_total - gw + n_warps - 1) / n_warps : 0;
     const int my_res = gw < a.n_res ? (a.n_res - gw + n_warps - 1) / n_warps : 0;
-    const int nkb = P.tile / max(a.cbk, 1), nvb = P.tile / max(a.cbv, 1);
-    const int k_items = my_tiles * nkb, v_items = my_tiles * 2 * nvb;
+    const int nkb = 1 << P.nkb_shift, nvi = 1 << P.nvi_shift;   // K blocks / V blocks per tile
+    const int k_items = my_tiles << P.nkb_shift, v_items = my_tiles << P.nvi_shift;
     const int total_items = k_items + v_items;
-    const int k_rounds = a.cbk / 16;
+    const int k_rounds = a.cbk >> 4;
     const int lbk = len_field_bits(a.bits_k), lbv = len_field_bits(a.bits_v);
     const uint8_t* kbase = a.k_stream + (int64_t)b * a.k_seq_stride;
     const uint8_t* vbase = a.v_stream + (int64_t)b * a.v_seq_stride;
@@ -169,16 +185,16 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
         int64_t cap;
         int bound;
         if (n < k_items) {
-            const int tl = n / nkb, i = n - tl * nkb;
-            const int t0 = (gw + tl * n_warps) * P.tile;
-            info = kinfo + ((int64_t)(t0 / a.cbk + i) * a.kv_heads + h) * 2;
+            const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
+            const int t0 = (gw + tl * n_warps) << P.tile_shift;
+            info = kinfo + ((int64_t)((t0 >> P.cbk_shift) + i) * a.kv_heads + h) * 2;
             base = kbase; cap = a.k_capacity;
             bound = 2 * k_rounds + k_rounds * (16 * a.bits_k + 16 * lbk + 256 * a.bits_k);
         } else {
             const int m = n - k_items;
-            const int tl = m / (2 * nvb), vi = m - tl * 2 * nvb;
-            const int t0 = (gw + tl * n_warps) * P.tile;
-            info = vinfo + ((int64_t)(t0 / a.cbv + (vi >> 1)) * (2 * a.kv_heads) + 2 * h + (vi & 1)) * 2;
+            const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
+            const int t0 = (gw + tl * n_warps) << P.tile_shift;
+            info = vinfo + ((int64_t)((t0 >> P.cbv_shift) + (vi >> 1)) * (2 * a.kv_heads) + 2 * h + (vi & 1)) * 2;
             base = vbase; cap = a.v_capacity;
             const int nseg = a.cbv == 128 ? 4 : 2;
             bound = 2 * nseg + nseg * (16 * a.bits_v + 16 * lbv + 256 * a.bits_v);
@@ -221,10 +237,10 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
         if (n + 1 < total_items) issue(n + 1, nxt_phase, nxt_size); else cp_async_commit();
         cp_async_wait<1>();
         __syncwarp();
-        const uint8_t* blk = wbase + (n & 1) * P.slot + cur_phase;
-        const int tl = n / nkb, i = n - tl * nkb;
-        const int t0 = (gw + tl * n_warps) * P.tile;
-        uint8_t* st = stile + tl * P.rows * P.prow;
+        const unsigned blk = wbase_a + (n & 1) * P.slot + cur_phase;
+        const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
+        const int t0 = (gw + tl * n_warps) << P.tile_shift;
+        const unsigned st = stile_a + tl * P.rows * P.prow;
 
         if (KMODE == kKToken && i == 0) {
             const T* ks = reinterpret_cast<const T*>(a.k_scale) + (int64_t)b * a.param_tokens + t0;
@@ -239,7 +255,7 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
             // channel mode: per-(block, channel) scale and zero for this lane's 32 channels
             T2 ksc[8][2], kzb[8][2];
             if (KMODE == kKChannel) {
-                const int64_t row = ((int64_t)(b * a.kv_heads + h) * a.param_blocks + (t0 / a.cbk + i)) * kD + 32 * c;
+                const int64_t row = ((int64_t)(b * a.kv_heads + h) * a.param_blocks + ((t0 >> P.cbk_shift) + i)) * kD + 32 * c;
                 const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_scale) + row);
                 const uint4* zp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_zero) + row);
 #pragma unroll
@@ -255,30 +271,31 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
                     for (int j = 0; j < 8; j++) { kzb[j][0] = __hsub2(kzb[j][0], bias2); kzb[j][1] = __hsub2(kzb[j][1], bias2); }
                 }
             }
+            const int bits_k = a.bits_k;
             int pos = 2 * k_rounds;
             for (int r = 0; r < k_rounds; r++) {
-                const uint8_t* hdr = blk + pos;
-                const unsigned minword = load_lane_field(hdr, lane, 4 * a.bits_k);
-                const unsigned lenword = load_lane_field(hdr + 16 * a.bits_k, lane, 4 * lbk);
+                const unsigned hdr = blk + pos;
+                const unsigned minword = lds_lane_field(hdr, lane, 4 * bits_k);
+                const unsigned lenword = lds_lane_field(hdr + 16 * bits_k, lane, 4 * lbk);
                 unsigned lens4 = 0, mins4 = 0;
                 int len[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     len[j] = min((int)((lenword >> (j * lbk)) & ((1u << lbk) - 1u)), 4);
                     lens4 |= (unsigned)len[j] << (8 * j);
-                    mins4 |= ((minword >> (j * a.bits_k)) & ((1u << a.bits_k) - 1u)) << (8 * j);
+                    mins4 |= ((minword >> (j * bits_k)) & ((1u << bits_k) - 1u)) << (8 * j);
                 }
                 const unsigned inc = warp_inclusive_sum(lens4);
                 const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
                 const unsigned exc = inc - lens4;
-                const uint8_t* packs = hdr + 16 * a.bits_k + 16 * lbk;
+                const unsigned packs = hdr + 16 * bits_k + 16 * lbk;
                 unsigned before = 0;
                 unsigned top[4], bot[4], msk[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const uint64_t w = load_u64_align2(packs + 2 * (before + ((exc >> (8 * j)) & 0xFFu)));
+                    unsigned lo, hi;
+                    lds_u64_align2(packs + 2 * (before + ((exc >> (8 * j)) & 0xFFu)), lo, hi);
                     before += (tot >> (8 * j)) & 0xFFu;
-                    const unsigned lo = (unsigned)w, hi = (unsigned)(w >> 32);
                     // tokens 0..7 live in bits [8*len, 16*len): bring them to the low word
                     const unsigned tp = __funnelshift_rc(lo, hi, 8 * len[j]);
                     // rotate so that token 0 (bit offset 7*len) sits at byte j
@@ -301,14 +318,11 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
                         for (int j = 0; j < 4; j++) bot[j] = __funnelshift_l(bot[j], bot[j], len[j]);
                     }
                     u += mins4;
-                    *reinterpret_cast<unsigned*>(xch + t * 128 + ((((lane >> 2) ^ (t & 1)) << 4) | ((lane & 3) << 2))) = u;
+                    sts32(((t & 1) ? kst_odd : kst_even) + t * 128, u);
                 }
                 __syncwarp();
                 // A fragments: rows g and g+8, this lane's 32 channels (two 16-byte chunks each)
-                uint4 ra0 = *reinterpret_cast<const uint4*>(xch + g * 128 + (((2 * c) ^ (g & 1)) << 4));
-                uint4 ra1 = *reinterpret_cast<const uint4*>(xch + g * 128 + (((2 * c + 1) ^ (g & 1)) << 4));
-                uint4 rb0 = *reinterpret_cast<const uint4*>(xch + (g + 8) * 128 + (((2 * c) ^ (g & 1)) << 4));
-                uint4 rb1 = *reinterpret_cast<const uint4*>(xch + (g + 8) * 128 + (((2 * c + 1) ^ (g & 1)) << 4));
+                const uint4 ra0 = lds128(kld0), ra1 = lds128(kld1), rb0 = lds128(kld0 + 8 * 128), rb1 = lds128(kld1 + 8 * 128);
                 __syncwarp();
                 const unsigned ua[8] = {ra0.x, ra0.y, ra0.z, ra0.w, ra1.x, ra1.y, ra1.z, ra1.w};
                 const unsigned ub[8] = {rb0.x, rb0.y, rb0.z, rb0.w, rb1.x, rb1.y, rb1.z, rb1.w};
@@ -318,7 +332,7 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
                     sg = Tr<T>::dup(ksz[tk]); zg = Tr<T>::dup(ksz[P.tile + tk]);
                     sg8 = Tr<T>::dup(ksz[tk + 8]); zg8 = Tr<T>::dup(ksz[P.tile + tk + 8]);
                 }
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                float accs[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // two chains hide the mma latency
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     unsigned af[4];
@@ -335,19 +349,20 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
                         af[2] = deq2<T, HP>(a_hi, zg, sg);
                         af[3] = deq2<T, HP>(b_hi, zg8, sg8);
                     }
-                    Tr<T>::mma(acc, af, qf[j][0], qf[j][1]);
+                    Tr<T>::mma(accs[j & 1], af, qf[j][0], qf[j][1]);
                 }
+                const float acc[4] = {accs[0][0] + accs[1][0], accs[0][1] + accs[1][1], accs[0][2] + accs[1][2], accs[0][3] + accs[1][3]};
                 // scores rounded like the reference: matmul output, then * scaling
                 if (col_live) {
-                    T* row0 = reinterpret_cast<T*>(st + (2 * c) * P.prow);
-                    T* row1 = reinterpret_cast<T*>(st + (2 * c + 1) * P.prow);
+                    const unsigned row0 = st + (2 * c) * P.prow + 2 * tk, row1 = row0 + P.prow;
                     const T s00 = Tr<T>::from_float(Tr<T>::round(acc[0]) * a.scaling), s01 = Tr<T>::from_float(Tr<T>::round(acc[1]) * a.scaling);
                     const T s10 = Tr<T>::from_float(Tr<T>::round(acc[2]) * a.scaling), s11 = Tr<T>::from_float(Tr<T>::round(acc[3]) * a.scaling);
-                    row0[tk] = s00; row1[tk] = s01; row0[tk + 8] = s10; row1[tk + 8] = s11;
+                    sts16(row0, *reinterpret_cast<const unsigned short*>(&s00)); sts16(row1, *reinterpret_cast<const unsigned short*>(&s01));
+                    sts16(row0 + 16, *reinterpret_cast<const unsigned short*>(&s10)); sts16(row1 + 16, *reinterpret_cast<const unsigned short*>(&s11));
                     mloc0 = fmaxf(mloc0, fmaxf(Tr<T>::to_float(s00), Tr<T>::to_float(s10)));
                     mloc1 = fmaxf(mloc1, fmaxf(Tr<T>::to_float(s01), Tr<T>::to_float(s11)));
                 }
-                pos += 16 * a.bits_k + 16 * lbk + 2 * (int)before;
+                pos += 16 * bits_k + 16 * lbk + 2 * (int)before;
             }
         }
         __syncwarp();
@@ -481,11 +496,12 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
         if (n + 1 < total_items) issue(n + 1, nxt_phase, nxt_size); else cp_async_commit();
         cp_async_wait<1>();
         __syncwarp();
-        const uint8_t* blk = wbase + (n & 1) * P.slot + cur_phase;
+        const unsigned blk = wbase_a + (n & 1) * P.slot + cur_phase;
         const int m = n - k_items;
-        const int tl = m / (2 * nvb), vi = m - tl * 2 * nvb;
-        const int t0 = (gw + tl * n_warps) * P.tile;
+        const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
+        const int t0 = (gw + tl * n_warps) << P.tile_shift;
         uint8_t* st = stile + tl * P.rows * P.prow;
+        const unsigned st_a = stile_a + tl * P.rows * P.prow;
 
         if (vi == 0) {
             // scores -> probabilities rounded to the element type, in place; V scale / zero of the tile
@@ -508,16 +524,17 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
         }
         if (cur_size > 0) {
             const int hh = vi & 1;                         // which 64-channel half of the head
-            const int tok_blk = (vi >> 1) * a.cbv;         // token offset of the block in the tile
-            const int rpw = a.cbv == 128 ? 2 : 1;
-            const int nseg = 2 * rpw;
+            const int tok_blk = (vi >> 1) << P.cbv_shift;  // token offset of the block in the tile
+            const int rpw_shift = a.cbv == 128 ? 1 : 0;
+            const int nseg = 2 << rpw_shift;
+            const int bits_v = a.bits_v;
             int pos = 2 * nseg;
             for (int sgi = 0; sgi < nseg; sgi++) {
-                const int w = sgi / rpw, rr = sgi - w * rpw;
+                const int w = sgi >> rpw_shift, rr = sgi & ((1 << rpw_shift) - 1);
                 const int tok_seg = tok_blk + rr * 64;     // first token (in the tile) of the segment
-                const uint8_t* hdr = blk + pos;
-                const unsigned minword = load_lane_field(hdr, lane, 4 * a.bits_v);
-                const unsigned lenword = load_lane_field(hdr + 16 * a.bits_v, lane, 4 * lbv);
+                const unsigned hdr = blk + pos;
+                const unsigned minword = lds_lane_field(hdr, lane, 4 * bits_v);
+                const unsigned lenword = lds_lane_field(hdr + 16 * bits_v, lane, 4 * lbv);
                 unsigned lens4 = 0;
                 int len[4];
 #pragma unroll
@@ -528,16 +545,16 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
                 const unsigned inc = warp_inclusive_sum(lens4);
                 const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
                 const unsigned exc = inc - lens4;
-                const uint8_t* packs = hdr + 16 * a.bits_v + 16 * lbv;
+                const unsigned packs = hdr + 16 * bits_v + 16 * lbv;
                 unsigned before = 0;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; q4++) {
-                    const uint64_t wd = load_u64_align2(packs + 2 * (before + ((exc >> (8 * q4)) & 0xFFu)));
+                    unsigned lo, hi;
+                    lds_u64_align2(packs + 2 * (before + ((exc >> (8 * q4)) & 0xFFu)), lo, hi);
                     before += (tot >> (8 * q4)) & 0xFFu;
-                    const unsigned lo = (unsigned)wd, hi = (unsigned)(wd >> 32);
                     const int ln = len[q4];
                     const unsigned tp = __funnelshift_rc(lo, hi, 8 * ln);
-                    const unsigned mn4 = ((minword >> (q4 * a.bits_v)) & ((1u << a.bits_v) - 1u)) * 0x01010101u;
+                    const unsigned mn4 = ((minword >> (q4 * bits_v)) & ((1u << bits_v) - 1u)) * 0x01010101u;
                     const unsigned m1 = (1u << ln) - 1u;
                     const unsigned m0 = m1, m8 = m1 << 8, m16 = m1 << 16, m24 = m1 << 24;
                     // token i' of a word sits at bit len*(7-i'); its byte target is 8*(i'&3):
@@ -559,18 +576,17 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
                         u[2 + k] = v1 + mn4;
                     }
                     // row = lane (channel), logical 16-byte chunk q4, swizzled
-                    *reinterpret_cast<uint4*>(xch + lane * 64 + ((q4 ^ ((lane >> 1) & 3)) << 4)) = make_uint4(u[0], u[1], u[2], u[3]);
+                    sts128(vst + ((q4 << 4) ^ vsw), make_uint4(u[0], u[1], u[2], u[3]));
                 }
                 __syncwarp();
                 // per-token scale / zero pairs and probabilities for tokens tok_seg + 16c .. +15
-                const uint4 s0 = *reinterpret_cast<const uint4*>(vsz + tok_seg + 16 * c);
-                const uint4 s1 = *reinterpret_cast<const uint4*>(vsz + tok_seg + 16 * c + 8);
-                const uint4 z0 = *reinterpret_cast<const uint4*>(vsz + P.tile + tok_seg + 16 * c);
-                const uint4 z1 = *reinterpret_cast<const uint4*>(vsz + P.tile + tok_seg + 16 * c + 8);
+                const unsigned tok2 = 2 * (tok_seg + 16 * c);      // byte offset of this lane's 16 tokens in a row of halves
+                const uint4 s0 = lds128(vsz_a + tok2), s1 = lds128(vsz_a + tok2 + 16);
+                const uint4 z0 = lds128(vsz_a + 2 * P.tile + tok2), z1 = lds128(vsz_a + 2 * P.tile + tok2 + 16);
                 uint4 p0 = make_uint4(0, 0, 0, 0), p1 = make_uint4(0, 0, 0, 0);
                 if (g < P.rows) {
-                    p0 = *reinterpret_cast<const uint4*>(st + g * P.prow + 2 * (tok_seg + 16 * c));
-                    p1 = *reinterpret_cast<const uint4*>(st + g * P.prow + 2 * (tok_seg + 16 * c) + 16);
+                    p0 = lds128(st_a + g * P.prow + tok2);
+                    p1 = lds128(st_a + g * P.prow + tok2 + 16);
                 }
                 const unsigned vS[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
                 const unsigned vZ[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
@@ -581,9 +597,7 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
                 unsigned afr[2][4][4];
 #pragma unroll
                 for (int mt = 0; mt < 2; mt++) {
-                    const int ra = 16 * mt + g, rb = ra + 8;
-                    const uint4 xa = *reinterpret_cast<const uint4*>(xch + ra * 64 + ((c ^ ((ra >> 1) & 3)) << 4));
-                    const uint4 xb = *reinterpret_cast<const uint4*>(xch + rb * 64 + ((c ^ ((rb >> 1) & 3)) << 4));
+                    const uint4 xa = lds128(vld + (16 * mt) * 64), xb = lds128(vld + (16 * mt + 8) * 64);
                     const unsigned ua[4] = {xa.x, xa.y, xa.z, xa.w};
                     const unsigned ub[4] = {xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
@@ -605,7 +619,7 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
                     }
                 }
                 __syncwarp();
-                pos += 16 * a.bits_v + 16 * lbv + 2 * (int)before;
+                pos += 16 * bits_v + 16 * lbv + 2 * (int)before;
             }
         }
         __syncwarp();
@@ -663,7 +677,7 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
             float v = 0.f;
 #pragma unroll
             for (int w = 0; w < kAW; w++) v += reinterpret_cast<const float*>(smem + w * P.warp_smem)[hd * kD + d];
-            cs->out[hd][d] = v;
+            cta_out_row(smem, P.warp_smem, P.out_off, hd)[d] = v;
         }
     }
     cluster.sync();
@@ -671,7 +685,7 @@ __global__ void __launch_bounds__(kAW * 32) attn_decode_kernel(const AttnDev P) 
         const int d = threadIdx.x;
         for (int hd = 0; hd < G; hd++) {
             float v = 0.f;
-            for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cs, r)->out[hd][d];
+            for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
             reinterpret_cast<T*>(a.out)[((int64_t)(b * q_heads + h * G + hd)) * kD + d] = Tr<T>::from_float(v);
         }
     }
@@ -737,6 +751,12 @@ int launch_attention(const AttnArgs& a, cudaStream_t st) {
     P.a = a;
     P.tile = (a.n_comp > 0 && (a.cbk == 128 || a.cbv == 128)) ? 128 : 64;
     P.tiles_total = a.n_comp / P.tile;
+    auto lg2 = [](int v) { int s = 0; while ((1 << s) < v) s++; return s; };
+    P.tile_shift = lg2(P.tile);
+    P.cbk_shift = a.n_comp > 0 ? lg2(a.cbk) : 6;
+    P.cbv_shift = a.n_comp > 0 ? lg2(a.cbv) : 6;
+    P.nkb_shift = P.tile_shift - P.cbk_shift;
+    P.nvi_shift = P.tile_shift - P.cbv_shift + 1;
     // cluster size: enough CTAs for ~2 waves of the 148 SMs (3 CTAs each), but at least one
     // tile per warp; a long sequence must also fit its scores in shared memory
     const long pairs = (long)a.batch * a.kv_heads;
@@ -758,7 +778,8 @@ int launch_attention(const AttnArgs& a, cudaStream_t st) {
         P.tpw = (P.tiles_total + n_warps - 1) / n_warps;
         P.rpw = (a.n_res + n_warps - 1) / n_warps;
         int warp_smem = 2 * slot + 2048 + 8 * P.tile + P.tpw * P.rows * P.prow + P.rpw * 8 * 4;
-        const int red_need = 8 * kD * 4;
+        P.out_off = 2 * slot > 8 * kD * 4 ? 2 * slot : 8 * kD * 4;   // behind the parked accumulators
+        const int red_need = P.out_off + 2 * kD * 4;
         if (warp_smem < red_need) warp_smem = red_need;
         P.warp_smem = (warp_smem + 15) & ~15;
         P.cta_off = kAW * P.warp_smem;

@@ -136,4 +136,59 @@ __device__ __forceinline__ uint64_t load_u64_align2(const uint8_t* p) {
     return (uint64_t)q[0] | ((uint64_t)q[1] << 16) | ((uint64_t)q[2] << 32) | ((uint64_t)q[3] << 48);
 }
 
+// Same window from SHARED memory with three aligned 32-bit loads and two funnel shifts.  Reads
+// the aligned words that contain [p, p+8) (up to 2 bytes before p and 4 bytes past p+8).
+__device__ __forceinline__ void load_u64_smem_align2(const uint8_t* p, unsigned& lo, unsigned& hi) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const unsigned* w = reinterpret_cast<const unsigned*>(a & ~(uintptr_t)3);
+    const unsigned sh = (unsigned)(a & 2) * 8;      // 0 or 16
+    const unsigned w0 = w[0], w1 = w[1], w2 = w[2];
+    lo = __funnelshift_r(w0, w1, sh);
+    hi = __funnelshift_r(w1, w2, sh);
+}
+
+// ---- shared-memory access by 32-bit shared-window address -----------------------------------
+// Hot loops address shared memory with 32-bit offsets and explicit ld.shared / st.shared so that
+// no 64-bit generic-pointer arithmetic is generated.  The "memory" clobbers keep the compiler from
+// moving them across the warp barriers and cp.async waits that order the data.
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned lds32(unsigned a) {
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(unsigned a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned lds16(unsigned a) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts32(unsigned a, unsigned v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
+__device__ __forceinline__ void sts16(unsigned a, unsigned short v) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "h"(v) : "memory"); }
+__device__ __forceinline__ void sts128(unsigned a, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// lane word of `width` bits (<= 16) at bit lane*width of a header that starts at shared address
+// hdr (any alignment): two aligned 32-bit loads and a funnel shift.  May read up to 7 bytes past
+// the header.
+__device__ __forceinline__ unsigned lds_lane_field(unsigned hdr, int lane, int width) {
+    const unsigned bit = hdr * 8u + (unsigned)(lane * width);
+    const unsigned wa = (bit >> 5) << 2;
+    return __funnelshift_r(lds32(wa), lds32(wa + 4), bit & 31u) & ((1u << width) - 1u);
+}
+
+// 64-bit window at shared address a (2-byte aligned): three aligned 32-bit loads, two funnel
+// shifts.  Reads up to 2 bytes before a and 4 bytes past a+8.
+__device__ __forceinline__ void lds_u64_align2(unsigned a, unsigned& lo, unsigned& hi) {
+    const unsigned wa = a & ~3u, sh = (a & 2u) * 8u;
+    const unsigned w0 = lds32(wa), w1 = lds32(wa + 4), w2 = lds32(wa + 8);
+    lo = __funnelshift_r(w0, w1, sh);
+    hi = __funnelshift_r(w1, w2, sh);
+}
+
 }  // namespace pkv
