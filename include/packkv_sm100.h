@@ -120,6 +120,33 @@ int32_t pkv_quantize(const void* x, int64_t stride_b, int64_t stride_h, int64_t 
                      int32_t is_bf16, uint32_t* dev_flags, void* cuda_stream);
 
 /*
+ * One-call encoder: quantise x (batch, heads, tokens, 128) and bit-pack it behind the blocks
+ * already in the streams.  Equivalent to pkv_quantize followed by pkv_k_encode (which = 0, blocks of
+ * cb tokens x 128 channels) or pkv_v_encode (which = 1, cb x 64); replaces the reference's
+ * quant_ints on the GPU + copy to the host + k/v_encode_cpu + copy back
+ * (evaluation/evaluation.py:402-428, 591-618).  `codes_scratch` is caller-provided device scratch
+ * of at least batch*tokens*heads*128 bytes (16-byte aligned) that holds the uint8 codes between the
+ * two stages; its contents are unspecified afterwards.  first_token = tokens already encoded per
+ * sequence (a multiple of cb and of qblock).
+ */
+typedef struct pkv_encode_args {
+    const void* x; int64_t stride_b, stride_h, stride_s;     /* strides in elements */
+    void* scale; void* zero; int32_t param_blocks, param_tokens;   /* as in pkv_quantize */
+    uint8_t* stream; int64_t stream_seq_stride, capacity;
+    uint32_t* block_info; int64_t info_seq_stride; uint32_t* stream_bytes;
+    uint32_t* flags;
+    int32_t batch, heads, tokens, first_token;
+    int32_t qblock;                 /* tokens per quantisation block */
+    int32_t cb;                     /* tokens per stream block */
+    int32_t which;                  /* 0 = K layout, 1 = V layout */
+    int32_t bits, mode, high_precision_zero, is_bf16;
+    float rel;
+} pkv_encode_args;
+
+int32_t pkv_encode_tensor(const pkv_encode_args* args_host, uint8_t* codes_scratch, int64_t scratch_bytes,
+                          void* cuda_stream);
+
+/*
  * Rotary embedding of new K tokens inside the cache; replaces apply_rotary_pos_emb_single
  * (utils/compute.py:32-43) bit for bit.  x/out (batch, heads, tokens, dim <= 128), cos/sin
  * (batch or 1, tokens, dim) with cs_stride_b = 0 to broadcast; strides in elements.

@@ -36,7 +36,20 @@ class AttnArgs(ctypes.Structure):
     ]
 
 
+class EncodeArgs(ctypes.Structure):
+    """Mirror of pkv_encode_args (include/packkv_sm100.h)."""
+    _fields_ = [
+        ("x", _p), ("stride_b", _i64), ("stride_h", _i64), ("stride_s", _i64),
+        ("scale", _p), ("zero", _p), ("param_blocks", _i32), ("param_tokens", _i32),
+        ("stream", _p), ("stream_seq_stride", _i64), ("capacity", _i64),
+        ("block_info", _p), ("info_seq_stride", _i64), ("stream_bytes", _p), ("flags", _p),
+        ("batch", _i32), ("heads", _i32), ("tokens", _i32), ("first_token", _i32), ("qblock", _i32), ("cb", _i32),
+        ("which", _i32), ("bits", _i32), ("mode", _i32), ("high_precision_zero", _i32), ("is_bf16", _i32), ("rel", _f32),
+    ]
+
+
 SIGNATURES = {
+    "pkv_encode_tensor": (_i32, [ctypes.POINTER(EncodeArgs), _p, _i64, _p]),
     "pkv_kq_mat_vec_mul": (_i32, [_p, _i64, _p, _p, _p] + [_i32] * 6 + [_p, _p]),
     "pkv_wv_mat_vec_mul": (_i32, [_p, _i64, _p, _p, _p] + [_i32] * 6 + [_p, _p]),
     "pkv_fused_kq": (_i32, [_p] * 5 + [_i32] * 4 + [_p]),

@@ -137,14 +137,13 @@ class PackKVCache(_HFCache):
         C, block = L.comp, cfg.block_size
         if self.flags is None:
             self.flags = ops.new_flags(k.device)
-        kq = ops.quantize(k, block, cfg.k_quant_scale_rel, C.k_mode, bits=C.bits_k, high_precision_zero=C.high_precision_zero,
-                          flags=self.flags, scale=C.k_scale, zero=C.k_zero, first_token=L.n_comp)
-        vq = ops.quantize(v, block, cfg.v_quant_scale_rel, ops.K_TOKEN, bits=C.bits_v, high_precision_zero=C.high_precision_zero,
-                          flags=self.flags, scale=C.v_scale, zero=C.v_zero, first_token=L.n_comp)
-        ops.encode_codes("k", kq.codes, C.cbk, C.bits_k, stream=C.k_stream, info=C.k_info, stream_bytes=C.k_bytes,
-                         flags=self.flags, first_cb=L.n_comp // C.cbk)
-        ops.encode_codes("v", vq.codes, C.cbv, C.bits_v, stream=C.v_stream, info=C.v_info, stream_bytes=C.v_bytes,
-                         flags=self.flags, first_cb=L.n_comp // C.cbv)
+        scratch = torch.empty(max(16, B * n * H * 128), dtype=torch.uint8, device=k.device)
+        ops.encode_tensor("k", k, block, cfg.k_quant_scale_rel, C.k_mode, C.bits_k, C.cbk, scale=C.k_scale, zero=C.k_zero,
+                          stream=C.k_stream, info=C.k_info, stream_bytes=C.k_bytes, flags=self.flags, first_token=L.n_comp,
+                          high_precision_zero=C.high_precision_zero, scratch=scratch)
+        ops.encode_tensor("v", v, block, cfg.v_quant_scale_rel, ops.K_TOKEN, C.bits_v, C.cbv, scale=C.v_scale, zero=C.v_zero,
+                          stream=C.v_stream, info=C.v_info, stream_bytes=C.v_bytes, flags=self.flags, first_token=L.n_comp,
+                          high_precision_zero=C.high_precision_zero, scratch=scratch)
         L.n_comp += n
         C.n_comp = L.n_comp
 

@@ -1,0 +1,32 @@
+// One-call encoder entry point: quantise fp16/bf16 K or V and bit-pack the codes into the
+// per-sequence streams (pkv_quantize followed by pkv_{k,v}_encode on a scratch code matrix).
+#include "../../include/packkv_sm100.h"
+#include "common.cuh"
+#include "launch.h"
+
+using namespace pkv;
+
+static int32_t encode_tensor(const pkv_encode_args& e, uint8_t* codes, cudaStream_t st) {
+    if (e.which != 0 && e.which != 1) return kBadArgument;
+    if (e.cb <= 0 || e.first_token % e.cb) return kBadArgument;
+    QuantArgs q{e.x, e.stride_b, e.stride_h, e.stride_s, codes, (int64_t)e.tokens * e.heads * 128, e.scale, e.zero,
+                e.param_blocks, e.qblock > 0 ? e.first_token / e.qblock : 0, e.param_tokens, e.first_token,
+                e.batch, e.heads, e.tokens, e.qblock, e.rel, e.bits, e.mode, e.high_precision_zero, e.is_bf16, e.flags};
+    int rc = launch_quantize(q, st);
+    if (rc != kOk) return rc;
+    CodecShape sh{e.batch, e.tokens, e.heads * 128, e.cb, e.which == 0 ? 128 : 64, e.bits, e.first_token / e.cb};
+    CodecBuffers b{codes, (int64_t)e.tokens * e.heads * 128, e.stream, e.stream_seq_stride, e.capacity, e.block_info,
+                   e.info_seq_stride, e.stream_bytes, e.flags};
+    return launch_encode(e.which == 0, sh, b, st);
+}
+
+extern "C" int32_t pkv_encode_tensor(const pkv_encode_args* args_host, uint8_t* codes_scratch, int64_t scratch_bytes,
+                                     void* cuda_stream) {
+    if (!args_host) return kBadArgument;
+    const pkv_encode_args& e = *args_host;
+    if (e.batch < 0 || e.heads <= 0 || e.tokens < 0) return kBadArgument;
+    const int64_t need = (int64_t)e.batch * e.tokens * e.heads * 128;
+    if (need == 0) return kOk;
+    if (!codes_scratch || scratch_bytes < need || (reinterpret_cast<uintptr_t>(codes_scratch) & 15)) return kBadArgument;
+    return encode_tensor(e, codes_scratch, static_cast<cudaStream_t>(cuda_stream));
+}

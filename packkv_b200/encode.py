@@ -40,19 +40,25 @@ def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bi
     dev = k.device
     if flags is None:
         flags = ops.new_flags(dev)
-    kq = ops.quantize(k, block, k_rel, k_mode, bits=bits_k, high_precision_zero=high_precision_zero, flags=flags,
-                      capacity_tokens=cap_tok)
-    vq = ops.quantize(v, block, v_rel, QuantMode.TokenQuant, bits=bits_v, high_precision_zero=high_precision_zero,
-                      flags=flags, capacity_tokens=cap_tok)
+    km = ops.K_CHANNEL if k_mode == QuantMode.ChannelQuant else ops.K_TOKEN
+    if k_mode not in (QuantMode.ChannelQuant, QuantMode.TokenQuant):
+        raise RuntimeError("not supported")
+    k_shape = (B, H, cap_tok // block, D) if km == ops.K_CHANNEL else (B, cap_tok)
+    k_scale, k_zero = torch.zeros(k_shape, dtype=k.dtype, device=dev), torch.zeros(k_shape, dtype=k.dtype, device=dev)
+    v_scale, v_zero = torch.zeros(B, cap_tok, dtype=k.dtype, device=dev), torch.zeros(B, cap_tok, dtype=k.dtype, device=dev)
     k_stream = torch.zeros(B, stream_capacity("k", cap_tok, H, cbk, bits_k), dtype=torch.uint8, device=dev)
     v_stream = torch.zeros(B, stream_capacity("v", cap_tok, H, cbv, bits_v), dtype=torch.uint8, device=dev)
     k_info = torch.zeros(B, (cap_tok // cbk) * H, 2, dtype=torch.int32, device=dev)
     v_info = torch.zeros(B, (cap_tok // cbv) * 2 * H, 2, dtype=torch.int32, device=dev)
-    _, _, k_bytes, _ = ops.encode_codes("k", kq.codes, cbk, bits_k, stream=k_stream, info=k_info, flags=flags)
-    _, _, v_bytes, _ = ops.encode_codes("v", vq.codes, cbv, bits_v, stream=v_stream, info=v_info, flags=flags)
+    k_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
+    v_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
+    scratch = torch.empty(max(16, B * S * H * D), dtype=torch.uint8, device=dev)
+    ops.encode_tensor("k", k, block, k_rel, km, bits_k, cbk, scale=k_scale, zero=k_zero, stream=k_stream, info=k_info,
+                      stream_bytes=k_bytes, flags=flags, high_precision_zero=high_precision_zero, scratch=scratch)
+    ops.encode_tensor("v", v, block, v_rel, ops.K_TOKEN, bits_v, cbv, scale=v_scale, zero=v_zero, stream=v_stream, info=v_info,
+                      stream_bytes=v_bytes, flags=flags, high_precision_zero=high_precision_zero, scratch=scratch)
     return ops.CompressedLayer(
-        k_stream=k_stream, k_info=k_info, k_bytes=k_bytes, k_scale=kq.scale, k_zero=kq.zero,
-        v_stream=v_stream, v_info=v_info, v_bytes=v_bytes, v_scale=vq.scale, v_zero=vq.zero,
-        n_comp=S, kv_heads=H, cbk=cbk, cbv=cbv, bits_k=bits_k, bits_v=bits_v,
-        k_mode=ops.K_CHANNEL if k_mode == QuantMode.ChannelQuant else ops.K_TOKEN,
+        k_stream=k_stream, k_info=k_info, k_bytes=k_bytes, k_scale=k_scale, k_zero=k_zero,
+        v_stream=v_stream, v_info=v_info, v_bytes=v_bytes, v_scale=v_scale, v_zero=v_zero,
+        n_comp=S, kv_heads=H, cbk=cbk, cbv=cbv, bits_k=bits_k, bits_v=bits_v, k_mode=km,
         high_precision_zero=high_precision_zero)

@@ -286,3 +286,40 @@ def dequantize(codes: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, hea
                                    int(high_precision_zero), int(scale.dtype == torch.bfloat16), _stream_ptr())
     _lib.check(st, "dequantize")
     return out
+
+
+def _encode_args(which: str, x, block, rel, mode, bits, hp, cb, scale, zero, stream, info, stream_bytes, flags, first_token):
+    B, H, S, D = x.shape
+    a = _lib.EncodeArgs()
+    a.x, a.stride_b, a.stride_h, a.stride_s = x.data_ptr(), x.stride(0), x.stride(1), x.stride(2)
+    a.scale, a.zero = scale.data_ptr(), zero.data_ptr()
+    a.param_blocks = scale.shape[2] if mode == K_CHANNEL else 0
+    a.param_tokens = scale.shape[1] if mode == K_TOKEN else 0
+    a.stream, a.stream_seq_stride, a.capacity = stream.data_ptr(), stream.stride(0), stream.shape[1]
+    a.block_info, a.info_seq_stride, a.stream_bytes = info.data_ptr(), info.shape[1], stream_bytes.data_ptr()
+    a.flags = flags.data_ptr()
+    a.batch, a.heads, a.tokens, a.first_token, a.qblock, a.cb = B, H, S, first_token, block, cb
+    a.which = 0 if which == "k" else 1
+    a.bits, a.mode, a.high_precision_zero, a.is_bf16, a.rel = bits, mode, int(hp), int(x.dtype == torch.bfloat16), float(rel)
+    return a
+
+
+def encode_tensor(which: str, x: torch.Tensor, block: int, rel: float, mode: int, bits: int, cb: int, *,
+                  scale: torch.Tensor, zero: torch.Tensor, stream: torch.Tensor, info: torch.Tensor,
+                  stream_bytes: torch.Tensor, flags: torch.Tensor, first_token: int = 0,
+                  high_precision_zero: bool = False, scratch: Optional[torch.Tensor] = None) -> None:
+    """Quantises x (B, H, S, 128) and packs it behind the `first_token` tokens already in the
+    streams (one C call).  `scratch` (uint8, >= B*S*H*128 bytes) holds the codes in between; one is
+    allocated when not given."""
+    _require_cuda(x, scale, zero, stream, info, stream_bytes, flags, scratch)
+    if x.dim() != 4 or x.shape[3] != 128 or x.stride(3) != 1 or x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("x must be (B, H, S, 128) fp16/bf16 with contiguous channels")
+    B, H, S, D = x.shape
+    if S % block or S % cb:
+        raise ValueError("Tensor shape is not divisible by block size")
+    need = B * S * H * D
+    if scratch is None:
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    a = _encode_args(which, x, block, rel, mode, bits, high_precision_zero, cb, scale, zero, stream, info, stream_bytes, flags, first_token)
+    st = _lib.lib().pkv_encode_tensor(ctypes.byref(a), scratch.data_ptr(), scratch.numel(), _stream_ptr())
+    _lib.check(st, f"encode_tensor({which})")
