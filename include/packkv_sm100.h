@@ -25,6 +25,7 @@ extern "C" {
 #define PKV_ERR_BAD_ARGUMENT 1
 #define PKV_ERR_UNSUPPORTED 2   /* the reference raises RuntimeError("not supported") here */
 #define PKV_ERR_CUDA 3
+#define PKV_ERR_TOO_LARGE 4     /* pkv_encode_tensor_static: the call needs more than the built-in scratch */
 
 #define PKV_FLAG_STREAM_OVERFLOW 1u
 #define PKV_FLAG_CODE_RANGE 2u
@@ -145,6 +146,31 @@ typedef struct pkv_encode_args {
 
 int32_t pkv_encode_tensor(const pkv_encode_args* args_host, uint8_t* codes_scratch, int64_t scratch_bytes,
                           void* cuda_stream);
+
+/*
+ * pkv_encode_tensor without a scratch argument, for callers that must not touch the device
+ * allocator.  (No counterpart in the reference, which allocates freely through torch.)
+ *
+ * Who needs it: the cache's append step when it runs inside a serving engine's decode loop.  Such
+ * engines hand all free HBM to their own KV-block pool at start-up, so a cudaMalloc made later can
+ * simply fail, and one that succeeds still stalls the whole device while the driver maps memory --
+ * in the middle of a latency-critical step.  They want every per-step call to bring its own memory.
+ *
+ * The uint8 codes live in a 16 MiB array inside the library image instead
+ * (PKV_STATIC_SCRATCH_BYTES; every GPU that loads the library keeps its copy until the process
+ * exits).  A call needs batch*tokens*heads*128 bytes of it -- e.g. one 64-token block of 8 KV heads
+ * for 256 sequences -- and is refused with PKV_ERR_TOO_LARGE beyond that; use pkv_encode_tensor
+ * with your own scratch for bulk prefill.  The call itself allocates nothing and frees nothing.
+ *
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call outside any stream capture.  All calls share the one array, which keeps
+ * whatever the previous call left in it: this entry point overwrites every byte it later reads, so
+ * nothing has to be cleared, but two calls that overlap on the GPU (different streams, or
+ * different host threads on one device) race on it -- serialise them.
+ * Inputs, outputs and results are exactly those of pkv_encode_tensor.
+ */
+#define PKV_STATIC_SCRATCH_BYTES (16u << 20)
+int32_t pkv_encode_tensor_static(const pkv_encode_args* args_host, void* cuda_stream);
 
 /*
  * Rotary embedding of new K tokens inside the cache; replaces apply_rotary_pos_emb_single

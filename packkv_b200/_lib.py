@@ -11,7 +11,8 @@ import os
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libpackkv_sm100.so")
 
-PKV_OK, PKV_ERR_BAD_ARGUMENT, PKV_ERR_UNSUPPORTED, PKV_ERR_CUDA = 0, 1, 2, 3
+PKV_OK, PKV_ERR_BAD_ARGUMENT, PKV_ERR_UNSUPPORTED, PKV_ERR_CUDA, PKV_ERR_TOO_LARGE = 0, 1, 2, 3, 4
+STATIC_SCRATCH_BYTES = 16 << 20
 FLAG_STREAM_OVERFLOW, FLAG_CODE_RANGE, FLAG_BAD_STREAM, FLAG_TIMEOUT = 1, 2, 4, 8
 
 _i32, _i64, _p, _f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
@@ -50,6 +51,7 @@ class EncodeArgs(ctypes.Structure):
 
 SIGNATURES = {
     "pkv_encode_tensor": (_i32, [ctypes.POINTER(EncodeArgs), _p, _i64, _p]),
+    "pkv_encode_tensor_static": (_i32, [ctypes.POINTER(EncodeArgs), _p]),
     "pkv_kq_mat_vec_mul": (_i32, [_p, _i64, _p, _p, _p] + [_i32] * 6 + [_p, _p]),
     "pkv_wv_mat_vec_mul": (_i32, [_p, _i64, _p, _p, _p] + [_i32] * 6 + [_p, _p]),
     "pkv_fused_kq": (_i32, [_p] * 5 + [_i32] * 4 + [_p]),
@@ -96,4 +98,7 @@ def check(status: int, what: str) -> None:
         raise RuntimeError("not supported")  # same text as the reference's dispatch failure
     if status == PKV_ERR_BAD_ARGUMENT:
         raise ValueError(f"{what}: bad argument")
+    if status == PKV_ERR_TOO_LARGE:
+        raise ValueError(f"{what}: the call needs more than the {STATIC_SCRATCH_BYTES >> 20} MiB built-in scratch; "
+                         "pass your own scratch to encode_tensor instead")
     raise RuntimeError(f"{what}: CUDA error")

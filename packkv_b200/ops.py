@@ -323,3 +323,23 @@ def encode_tensor(which: str, x: torch.Tensor, block: int, rel: float, mode: int
     a = _encode_args(which, x, block, rel, mode, bits, high_precision_zero, cb, scale, zero, stream, info, stream_bytes, flags, first_token)
     st = _lib.lib().pkv_encode_tensor(ctypes.byref(a), scratch.data_ptr(), scratch.numel(), _stream_ptr())
     _lib.check(st, f"encode_tensor({which})")
+
+
+def encode_tensor_static(which: str, x: torch.Tensor, block: int, rel: float, mode: int, bits: int, cb: int, *,
+                         scale: torch.Tensor, zero: torch.Tensor, stream: torch.Tensor, info: torch.Tensor,
+                         stream_bytes: torch.Tensor, flags: torch.Tensor, first_token: int = 0,
+                         high_precision_zero: bool = False) -> None:
+    """encode_tensor for callers that must stay away from the device allocator (a serving engine's
+    decode loop whose memory pool owns all free HBM: an allocation there can fail or stall the
+    device).  The codes go through a 16 MiB array built into the library, so B*S*H*128 must not
+    exceed that (ValueError otherwise), and calls must not overlap on the GPU because they share
+    it.  The first call on a device resolves the array's address: make it before capturing streams.
+    Results are identical to encode_tensor's."""
+    _require_cuda(x, scale, zero, stream, info, stream_bytes, flags)
+    if x.dim() != 4 or x.shape[3] != 128 or x.stride(3) != 1 or x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("x must be (B, H, S, 128) fp16/bf16 with contiguous channels")
+    if x.shape[2] % block or x.shape[2] % cb:
+        raise ValueError("Tensor shape is not divisible by block size")
+    a = _encode_args(which, x, block, rel, mode, bits, high_precision_zero, cb, scale, zero, stream, info, stream_bytes, flags, first_token)
+    st = _lib.lib().pkv_encode_tensor_static(ctypes.byref(a), _stream_ptr())
+    _lib.check(st, f"encode_tensor_static({which})")
