@@ -121,6 +121,23 @@ int32_t pkv_quantize(const void* x, int64_t stride_b, int64_t stride_h, int64_t 
                      int32_t is_bf16, uint32_t* dev_flags, void* cuda_stream);
 
 /*
+ * In-block token reordering; replaces median_repacking (utils/compute.py:262-270).
+ * pkv_median_order: key[token] = lower median of the token's V codes (all heads, all channels),
+ *   order[b][block][rank] = index inside the block of the token with that rank when sorted by key,
+ *   descending, ties in original order (torch's unstable sort leaves tie order unspecified).
+ *   v_codes (batch, tokens, heads*128) uint8 with codes <= 15; block <= 128; keys may be NULL.
+ * pkv_gather_rows: dst row (block*B + r) <- src row (block*B + order[r]) for code matrices
+ *   (row_bytes = heads*128); pkv_gather_params: the same gather for per-token fp16/bf16 parameter
+ *   arrays (batch, row_len), applied to tokens [first, first+tokens).  src and dst must differ.
+ */
+int32_t pkv_median_order(const uint8_t* v_codes, int64_t codes_seq_stride, uint8_t* order, uint8_t* keys,
+                         int32_t batch, int32_t heads, int32_t tokens, int32_t block, void* cuda_stream);
+int32_t pkv_gather_rows(const uint8_t* src, uint8_t* dst, int64_t seq_stride, const uint8_t* order, int32_t batch,
+                        int32_t tokens, int32_t block, int32_t row_bytes, void* cuda_stream);
+int32_t pkv_gather_params(const void* src, void* dst, int64_t row_len, int32_t first, const uint8_t* order,
+                          int32_t batch, int32_t tokens, int32_t block, void* cuda_stream);
+
+/*
  * One-call encoder: quantise x (batch, heads, tokens, 128) and bit-pack it behind the blocks
  * already in the streams.  Equivalent to pkv_quantize followed by pkv_k_encode (which = 0, blocks of
  * cb tokens x 128 channels) or pkv_v_encode (which = 1, cb x 64); replaces the reference's

@@ -126,24 +126,43 @@ class PackKVCache(_HFCache):
             new.v_scale[:, : old.v_scale.shape[1]] = old.v_scale
             new.v_zero[:, : old.v_zero.shape[1]] = old.v_zero
             new.n_comp = old.n_comp
+            new.order = old.order
         L.comp, L.capacity = new, cap
 
     def _compress(self, L: _Layer, k: torch.Tensor, v: torch.Tensor, cfg: PackKVCacheConfig):
         """Quantises and packs k, v (B, H, n*block, 128) behind the tokens already stored."""
-        if cfg.repack_method not in (None, RepackMethod.NONE):
-            raise RuntimeError("not supported")   # token reordering is applied by encode.compress_kv, not on append
+        if cfg.repack_method == RepackMethod.GREEDY:
+            raise RuntimeError("not supported")
         B, H, n, _ = k.shape
         self._ensure_store(L, H, L.n_comp + n, k.dtype, k.device, cfg)
         C, block = L.comp, cfg.block_size
         if self.flags is None:
             self.flags = ops.new_flags(k.device)
-        scratch = torch.empty(max(16, B * n * H * 128), dtype=torch.uint8, device=k.device)
-        ops.encode_tensor("k", k, block, cfg.k_quant_scale_rel, C.k_mode, C.bits_k, C.cbk, scale=C.k_scale, zero=C.k_zero,
-                          stream=C.k_stream, info=C.k_info, stream_bytes=C.k_bytes, flags=self.flags, first_token=L.n_comp,
-                          high_precision_zero=C.high_precision_zero, scratch=scratch)
-        ops.encode_tensor("v", v, block, cfg.v_quant_scale_rel, ops.K_TOKEN, C.bits_v, C.cbv, scale=C.v_scale, zero=C.v_zero,
-                          stream=C.v_stream, info=C.v_info, stream_bytes=C.v_bytes, flags=self.flags, first_token=L.n_comp,
-                          high_precision_zero=C.high_precision_zero, scratch=scratch)
+        if cfg.repack_method == RepackMethod.MEDIAN:
+            # quantise, order the tokens of each new block by the median of their V codes, pack
+            kq = ops.quantize(k, block, cfg.k_quant_scale_rel, C.k_mode, bits=C.bits_k, high_precision_zero=C.high_precision_zero,
+                              flags=self.flags, scale=C.k_scale, zero=C.k_zero, first_token=L.n_comp)
+            vq = ops.quantize(v, block, cfg.v_quant_scale_rel, ops.K_TOKEN, bits=C.bits_v, high_precision_zero=C.high_precision_zero,
+                              flags=self.flags, scale=C.v_scale, zero=C.v_zero, first_token=L.n_comp)
+            order = ops.median_order(vq.codes, H, block)
+            C.v_scale = ops.gather_params(C.v_scale, order, block, n, first=L.n_comp)
+            C.v_zero = ops.gather_params(C.v_zero, order, block, n, first=L.n_comp)
+            if C.k_mode == ops.K_TOKEN:
+                C.k_scale = ops.gather_params(C.k_scale, order, block, n, first=L.n_comp)
+                C.k_zero = ops.gather_params(C.k_zero, order, block, n, first=L.n_comp)
+            ops.encode_codes("k", ops.gather_rows(kq.codes, order, block), C.cbk, C.bits_k, stream=C.k_stream, info=C.k_info,
+                             stream_bytes=C.k_bytes, flags=self.flags, first_cb=L.n_comp // C.cbk)
+            ops.encode_codes("v", ops.gather_rows(vq.codes, order, block), C.cbv, C.bits_v, stream=C.v_stream, info=C.v_info,
+                             stream_bytes=C.v_bytes, flags=self.flags, first_cb=L.n_comp // C.cbv)
+            C.order = order if C.order is None else torch.cat([C.order, order], dim=1)
+        else:
+            scratch = torch.empty(max(16, B * n * H * 128), dtype=torch.uint8, device=k.device)
+            ops.encode_tensor("k", k, block, cfg.k_quant_scale_rel, C.k_mode, C.bits_k, C.cbk, scale=C.k_scale, zero=C.k_zero,
+                              stream=C.k_stream, info=C.k_info, stream_bytes=C.k_bytes, flags=self.flags, first_token=L.n_comp,
+                              high_precision_zero=C.high_precision_zero, scratch=scratch)
+            ops.encode_tensor("v", v, block, cfg.v_quant_scale_rel, ops.K_TOKEN, C.bits_v, C.cbv, scale=C.v_scale, zero=C.v_zero,
+                              stream=C.v_stream, info=C.v_info, stream_bytes=C.v_bytes, flags=self.flags, first_token=L.n_comp,
+                              high_precision_zero=C.high_precision_zero, scratch=scratch)
         L.n_comp += n
         C.n_comp = L.n_comp
 
@@ -207,6 +226,13 @@ class PackKVCache(_HFCache):
         vc, _ = ops.decode_codes("v", C.v_stream, C.v_info, L.n_comp, H * 128, C.cbv, C.bits_v, flags=self.flags)
         kd = ops.dequantize(kc, C.k_scale, C.k_zero, H, cfg.block_size, C.k_mode, high_precision_zero=C.high_precision_zero)
         vd = ops.dequantize(vc, C.v_scale, C.v_zero, H, cfg.block_size, ops.K_TOKEN, high_precision_zero=C.high_precision_zero)
+        if C.order is not None:   # undo the in-block reordering: original position of every stored row
+            block = cfg.block_size
+            pos = (C.order.to(torch.int64) + torch.arange(L.n_comp // block, device=kd.device).view(1, -1, 1) * block).reshape(kd.shape[0], -1)
+            inv = torch.empty_like(pos)
+            inv.scatter_(1, pos, torch.arange(L.n_comp, device=kd.device).expand_as(pos))
+            idx = inv.view(kd.shape[0], 1, L.n_comp, 1).expand_as(kd)
+            kd, vd = torch.gather(kd, 2, idx), torch.gather(vd, 2, idx)
         return torch.cat([kd, k_res], dim=2), torch.cat([vd, v_res], dim=2)
 
     def attend(self, query_states: torch.Tensor, layer_idx: int, scaling: Optional[float] = None) -> torch.Tensor:

@@ -89,6 +89,22 @@ int32_t pkv_quantize(const void* x, int64_t stride_b, int64_t stride_h, int64_t 
     return launch_quantize(q, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int32_t pkv_median_order(const uint8_t* v_codes, int64_t codes_seq_stride, uint8_t* order, uint8_t* keys,
+                         int32_t batch, int32_t heads, int32_t tokens, int32_t block, void* cuda_stream) {
+    ReorderArgs a{v_codes, codes_seq_stride, order, keys, batch, heads, tokens, block};
+    return launch_median_order(a, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_gather_rows(const uint8_t* src, uint8_t* dst, int64_t seq_stride, const uint8_t* order, int32_t batch,
+                        int32_t tokens, int32_t block, int32_t row_bytes, void* cuda_stream) {
+    return launch_gather_rows(src, dst, seq_stride, order, batch, tokens, block, row_bytes, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_gather_params(const void* src, void* dst, int64_t row_len, int32_t first, const uint8_t* order,
+                          int32_t batch, int32_t tokens, int32_t block, void* cuda_stream) {
+    return launch_gather_params(src, dst, row_len, first, order, batch, tokens, block, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int32_t pkv_rope(const void* x, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, const void* cos,
                  const void* sin, int64_t cs_stride_b, void* out, int64_t o_stride_b, int64_t o_stride_h,
                  int64_t o_stride_s, int32_t batch, int32_t heads, int32_t tokens, int32_t dim, int32_t is_bf16,

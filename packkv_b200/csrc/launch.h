@@ -68,6 +68,17 @@ struct DequantArgs {
     void* out; int64_t o_stride_b, o_stride_h, o_stride_s;         // (B, H, T, 128), strides in elements
     int batch, heads, tokens, block, mode, high_precision_zero, is_bf16;
 };
+struct ReorderArgs {
+    const uint8_t* v_codes; int64_t codes_seq_stride;   // (B, tokens, heads*128) uint8
+    uint8_t* order;                                     // (B, tokens/block, block): source row of each rank
+    uint8_t* keys;                                      // optional (B, tokens): the per-token median
+    int batch, heads, tokens, block;
+};
+int launch_median_order(const ReorderArgs& a, cudaStream_t st);
+int launch_gather_rows(const uint8_t* src, uint8_t* dst, int64_t seq_stride, const uint8_t* order, int batch, int tokens,
+                       int block, int row_bytes, cudaStream_t st);
+int launch_gather_params(const void* src, void* dst, int64_t row_len, int first, const uint8_t* order, int batch, int tokens,
+                         int block, cudaStream_t st);
 int launch_rope(const RopeArgs& r, cudaStream_t st);
 int launch_dequantize(const DequantArgs& q, cudaStream_t st);
 int launch_quantize(const QuantArgs& q, cudaStream_t st);

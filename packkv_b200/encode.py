@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 
 from . import ops
-from .config import QuantMode
+from .config import QuantMode, RepackMethod
 
 
 def _pad16(n: int) -> int:
@@ -26,10 +26,14 @@ def stream_capacity(which: str, n_tokens: int, kv_heads: int, cb: int, bits: int
 def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bits_v: int,
                 k_rel: float, v_rel: float, k_mode: QuantMode = QuantMode.ChannelQuant,
                 cbk: Optional[int] = None, cbv: Optional[int] = None, high_precision_zero: bool = False,
-                capacity_tokens: Optional[int] = None, flags: Optional[torch.Tensor] = None) -> ops.CompressedLayer:
+                capacity_tokens: Optional[int] = None, flags: Optional[torch.Tensor] = None,
+                repack_method: RepackMethod = RepackMethod.NONE) -> ops.CompressedLayer:
     """Compresses K, V of shape (B, Hkv, S, 128) (S a multiple of the block sizes).
 
-    `capacity_tokens` reserves stream and table room for later appends.
+    `capacity_tokens` reserves stream and table room for later appends.  With
+    RepackMethod.MEDIAN the tokens of every quantisation block are reordered (same order for K and
+    V) by the descending median of their V codes before packing, which narrows the per-pack value
+    ranges; attention over the block is unaffected and `order` is kept for dense reconstruction.
     """
     if k.shape != v.shape or k.dim() != 4 or k.shape[3] != 128:
         raise ValueError("k and v must both be (B, Hkv, S, 128)")
@@ -52,6 +56,26 @@ def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bi
     v_info = torch.zeros(B, (cap_tok // cbv) * 2 * H, 2, dtype=torch.int32, device=dev)
     k_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
     v_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
+    if repack_method == RepackMethod.GREEDY:
+        raise RuntimeError("not supported")
+    if repack_method == RepackMethod.MEDIAN:
+        kq = ops.quantize(k, block, k_rel, km, bits=bits_k, high_precision_zero=high_precision_zero, flags=flags,
+                          scale=k_scale, zero=k_zero)
+        vq = ops.quantize(v, block, v_rel, ops.K_TOKEN, bits=bits_v, high_precision_zero=high_precision_zero, flags=flags,
+                          scale=v_scale, zero=v_zero)
+        order = ops.median_order(vq.codes, H, block)
+        v_scale, v_zero = ops.gather_params(v_scale, order, block, S), ops.gather_params(v_zero, order, block, S)
+        if km == ops.K_TOKEN:
+            k_scale, k_zero = ops.gather_params(k_scale, order, block, S), ops.gather_params(k_zero, order, block, S)
+        ops.encode_codes("k", ops.gather_rows(kq.codes, order, block), cbk, bits_k, stream=k_stream, info=k_info,
+                         stream_bytes=k_bytes, flags=flags)
+        ops.encode_codes("v", ops.gather_rows(vq.codes, order, block), cbv, bits_v, stream=v_stream, info=v_info,
+                         stream_bytes=v_bytes, flags=flags)
+        return ops.CompressedLayer(
+            k_stream=k_stream, k_info=k_info, k_bytes=k_bytes, k_scale=k_scale, k_zero=k_zero,
+            v_stream=v_stream, v_info=v_info, v_bytes=v_bytes, v_scale=v_scale, v_zero=v_zero,
+            n_comp=S, kv_heads=H, cbk=cbk, cbv=cbv, bits_k=bits_k, bits_v=bits_v, k_mode=km,
+            high_precision_zero=high_precision_zero, order=order)
     scratch = torch.empty(max(16, B * S * H * D), dtype=torch.uint8, device=dev)
     ops.encode_tensor("k", k, block, k_rel, km, bits_k, cbk, scale=k_scale, zero=k_zero, stream=k_stream, info=k_info,
                       stream_bytes=k_bytes, flags=flags, high_precision_zero=high_precision_zero, scratch=scratch)

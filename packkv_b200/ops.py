@@ -180,6 +180,7 @@ class CompressedLayer:
     bits_v: int
     k_mode: int
     high_precision_zero: bool = False
+    order: Optional[torch.Tensor] = None   # (B, n_comp/block, block) u8 when tokens were reordered inside blocks
 
     def stream_bytes(self) -> int:
         """Compressed payload actually read by a decode step (streams + block tables + scales)."""
@@ -343,3 +344,36 @@ def encode_tensor_static(which: str, x: torch.Tensor, block: int, rel: float, mo
     a = _encode_args(which, x, block, rel, mode, bits, high_precision_zero, cb, scale, zero, stream, info, stream_bytes, flags, first_token)
     st = _lib.lib().pkv_encode_tensor_static(ctypes.byref(a), _stream_ptr())
     _lib.check(st, f"encode_tensor_static({which})")
+
+
+def median_order(v_codes: torch.Tensor, heads: int, block: int, want_keys: bool = False):
+    """Token order of every block by descending lower-median of the V codes (stable on ties).
+    v_codes (B, S, heads*128) uint8 -> order (B, S/block, block) uint8 [, keys (B, S) uint8]."""
+    _require_cuda(v_codes)
+    B, S, _ = v_codes.shape
+    order = torch.empty(B, S // block, block, dtype=torch.uint8, device=v_codes.device)
+    keys = torch.empty(B, S, dtype=torch.uint8, device=v_codes.device) if want_keys else None
+    st = _lib.lib().pkv_median_order(v_codes.data_ptr(), v_codes.stride(0), order.data_ptr(),
+                                     keys.data_ptr() if want_keys else None, B, heads, S, block, _stream_ptr())
+    _lib.check(st, "median_order")
+    return (order, keys) if want_keys else order
+
+
+def gather_rows(codes: torch.Tensor, order: torch.Tensor, block: int) -> torch.Tensor:
+    """Applies `order` to the token rows of a code matrix (B, S, row_bytes)."""
+    _require_cuda(codes, order)
+    B, S, rb = codes.shape
+    out = torch.empty_like(codes)
+    st = _lib.lib().pkv_gather_rows(codes.data_ptr(), out.data_ptr(), codes.stride(0), order.data_ptr(), B, S, block, rb, _stream_ptr())
+    _lib.check(st, "gather_rows")
+    return out
+
+
+def gather_params(params: torch.Tensor, order: torch.Tensor, block: int, tokens: int, first: int = 0) -> torch.Tensor:
+    """Applies `order` to per-token parameters (B, row_len) for tokens [first, first+tokens)."""
+    _require_cuda(params, order)
+    out = params.clone()
+    st = _lib.lib().pkv_gather_params(params.data_ptr(), out.data_ptr(), params.shape[1], first, order.data_ptr(),
+                                      params.shape[0], tokens, block, _stream_ptr())
+    _lib.check(st, "gather_params")
+    return out

@@ -12,20 +12,21 @@ from packkv_b200.config import PackKVCacheConfig, QuantMethod, RepackMethod
 pytestmark = pytest.mark.gpu
 
 
-def _cfg(method, k_rel=1 / 14, v_rel=1 / 14, hp=False, enable=True):
-    return PackKVCacheConfig("synthetic", method, RepackMethod.NONE, hp, 64, 192, 16, k_rel, v_rel, enable_quant=enable)
+def _cfg(method, k_rel=1 / 14, v_rel=1 / 14, hp=False, enable=True, repack=RepackMethod.NONE):
+    return PackKVCacheConfig("synthetic", method, repack, hp, 64, 192, 16, k_rel, v_rel, enable_quant=enable)
 
 
 def _modes(method):
     return {QuantMethod.KIVI: ("channel", "token"), QuantMethod.PackKV: ("token", "token")}[method]
 
 
-@pytest.mark.parametrize("method", [QuantMethod.KIVI, QuantMethod.PackKV])
+@pytest.mark.parametrize("method,repack", [(QuantMethod.KIVI, RepackMethod.NONE), (QuantMethod.PackKV, RepackMethod.NONE),
+                                           (QuantMethod.KIVI, RepackMethod.MEDIAN), (QuantMethod.PackKV, RepackMethod.MEDIAN)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_prefill_then_decode_matches_reference_cache(cuda_device, method, dtype):
+def test_prefill_then_decode_matches_reference_cache(cuda_device, method, repack, dtype):
     dev = cuda_device
     B, H, G, S0, steps = 2, 2, 4, 333, 140
-    cfg = _cfg(method)
+    cfg = _cfg(method, repack=repack)
     C.PackKVCacheConfigStatic.config = cfg
     try:
         cache = C.PackKVCache(B, H * G, 128, 1, materialize=True)
