@@ -98,16 +98,20 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-def build_layers(w, device, dtype):
-    from packkv_b200 import encode, synth
+def build_layers(w, device, dtype, head_shard=None):
+    from packkv_b200 import encode, parallel, synth
     from packkv_b200.config import QuantMode
     n_comp, n_res = split_context(w["ctx"], w["block"])
     layers = []
     for li in range(w["layers"]):
         k, v = synth.synth_kv(w["batch"], w["kv_heads"], w["ctx"], 128, seed=1000 + li, dtype=dtype, device=device, apply_rope=True)
-        layer = encode.compress_kv(k[:, :, :n_comp], v[:, :, :n_comp], block=w["block"], bits_k=w["bits_k"], bits_v=w["bits_v"],
-                                   k_rel=synth.rel_for_bits(w["bits_k"]), v_rel=synth.rel_for_bits(w["bits_v"]),
-                                   k_mode=QuantMode.ChannelQuant, cbk=w["cbk"], cbv=w["cbv"])
+        kw = dict(block=w["block"], bits_k=w["bits_k"], bits_v=w["bits_v"], k_rel=synth.rel_for_bits(w["bits_k"]),
+                  v_rel=synth.rel_for_bits(w["bits_v"]), k_mode=QuantMode.ChannelQuant, cbk=w["cbk"], cbv=w["cbv"])
+        if head_shard is None:
+            layer = encode.compress_kv(k[:, :, :n_comp], v[:, :, :n_comp], **kw)
+        else:
+            layer, (lo, hi) = parallel.compress_kv_head_shard(k[:, :, :n_comp], v[:, :, :n_comp], head_shard[0], head_shard[1], **kw)
+            k, v = k[:, lo:hi], v[:, lo:hi]
         # trim the streams to what is used (setup only), keeping 16-byte multiples
         kb = (int(layer.k_bytes.max().item()) + 31) // 16 * 16
         vb = (int(layer.v_bytes.max().item()) + 31) // 16 * 16
@@ -131,9 +135,12 @@ def layer_bytes(layer, k_res, v_res, n_res, batch, q_heads):
 
 def run_ours(args, w, rank, world, device):
     from packkv_b200 import ops
+    from packkv_b200 import parallel
     dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
-    layers, n_comp, n_res = build_layers(w, device, dtype)
-    B, Hq = w["batch"], w["q_heads"]
+    by_heads = args.shard == "heads" and world > 1
+    layers, n_comp, n_res = build_layers(w, device, dtype, head_shard=(rank, world) if by_heads else None)
+    B, Hq = w["batch"], w["q_heads"] // (world if by_heads else 1)
+    gather_buf = torch.empty(world, B, Hq, 128, dtype=dtype, device=device) if by_heads else None
     g = torch.Generator(device=device).manual_seed(77 + rank)
     q_dev = [torch.randn(B, Hq, 128, generator=g, device=device, dtype=torch.float32).to(dtype) for _ in layers]
     out_dev = [torch.empty_like(q) for q in q_dev]
@@ -143,6 +150,8 @@ def run_ours(args, w, rank, world, device):
     def step_resident():
         for (L, kr, vr), q, o in zip(layers, q_dev, out_dev):
             ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags)
+            if by_heads:
+                parallel.gather_heads(o, buffer=gather_buf)
 
     q_host = [q.cpu().pin_memory() for q in q_dev]
     out_host = [torch.empty(B, Hq, 128, dtype=dtype).pin_memory() for _ in layers]
@@ -152,6 +161,8 @@ def run_ours(args, w, rank, world, device):
         for (L, kr, vr), qh, oh, o in zip(layers, q_host, out_host, out_dev):
             q_stage.copy_(qh, non_blocking=True)
             ops.decode_attention(q_stage, L, kr, vr, n_res, out=o, flags=flags)
+            if by_heads:
+                parallel.gather_heads(o, buffer=gather_buf)
             oh.copy_(o, non_blocking=True)
 
     def timed(fn, steps):
@@ -187,18 +198,18 @@ def run_ours(args, w, rank, world, device):
     if rank != 0:
         return None
     ms_per_step = ms / args.steps
-    tokens = B * world
+    tokens = B if by_heads else B * world
     peak, peak_kind = measured_peak_gbs()
     per_launch_ms = ms_per_step / len(layers)
     achieved = (alg_bytes / len(layers)) / (per_launch_ms * 1e-3) / 1e9
     line = {
         "metric": "fused decompress-attention decode throughput", "value": tokens / (ms_per_step * 1e-3), "unit": "tok/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong" if by_heads else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
         "config": {"workload": w["name"], "layers": w["layers"], "batch_per_gpu": B, "context": w["ctx"],
                    "compressed_tokens": n_comp, "residual_tokens": n_res, "k_quant": "channel", "v_quant": "token",
-                   "l2": f"working set {alg_bytes / 1e9:.2f} GB per step >> 126 MB L2 (no flush needed)",
-                   "sharding": "batch (independent sequences, no collective)"},
+                   "l2": f"working set {alg_bytes / 1e9:.2f} GB per step and GPU >> 126 MB L2 (no flush needed)",
+                   "sharding": "KV heads per rank + NCCL all-gather of outputs" if by_heads else "batch (independent sequences, no collective)"},
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tok/s",
                 "h2d_bytes_per_step": len(layers) * B * Hq * 128 * 2, "d2h_bytes_per_step": len(layers) * B * Hq * 128 * 2},
         "gpu_launches": len(layers) * args.steps,
@@ -289,6 +300,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
+                    help="multi-GPU split: independent sequences per rank (weak scaling, no collective) or KV heads per "
+                         "rank with an all-gather of the outputs (strong scaling)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))

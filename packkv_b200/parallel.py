@@ -1,0 +1,83 @@
+"""Multi-GPU sharding of the decode path: one process per GPU, torch.distributed for plumbing.
+
+Two ways to split the work, both without any exchange inside the kernels:
+
+* batch sharding  - sequences are independent; rank r owns sequences [r*B/n, (r+1)*B/n).  No
+  collective on the data path.
+* KV-head sharding - rank r owns KV heads [r*H/n, (r+1)*H/n) and their q heads.  Streams are built
+  from per-head blocks, so a rank packs only its heads.  Per-token quantisation parameters (V, and K
+  in token mode) span ALL heads (reference QUANT_DIM, utils/compute.py:405-410), so the quantiser
+  runs on the full tensor and only the rank's columns of the code matrix are packed; the parameters
+  stay replicated.  The only collective is an all-gather of the attention outputs
+  (batch x q_heads/n x 128 per rank and layer) over NCCL.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def partition(n_items: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous, even split; raises if it does not divide."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("bad rank / world size")
+    if n_items % world:
+        raise ValueError(f"{n_items} items do not divide over {world} ranks")
+    per = n_items // world
+    return rank * per, (rank + 1) * per
+
+
+def q_heads_of(kv_lo: int, kv_hi: int, group: int) -> Tuple[int, int]:
+    return kv_lo * group, kv_hi * group
+
+
+def gather_heads(local_out: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
+                 buffer: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """all-gather of per-rank attention outputs (B, Hq/n, D) -> (B, Hq, D), rank-major heads."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return local_out
+    B, Hl, D = local_out.shape
+    if buffer is None:
+        buffer = torch.empty(world, B, Hl, D, dtype=local_out.dtype, device=local_out.device)
+    dist.all_gather(list(buffer.unbind(0)), local_out.contiguous(), group=group)
+    return buffer.permute(1, 0, 2, 3).reshape(B, world * Hl, D)
+
+
+def compress_kv_head_shard(k: torch.Tensor, v: torch.Tensor, rank: int, world: int, *, block: int, bits_k: int, bits_v: int,
+                           k_rel: float, v_rel: float, k_mode, cbk: Optional[int] = None, cbv: Optional[int] = None):
+    """Builds the rank's compressed layer from the FULL K, V (B, Hkv, S, 128): quantise with
+    all-head statistics, pack only this rank's heads.  Returns (layer, (kv_lo, kv_hi))."""
+    from . import encode, ops
+    from .config import QuantMode
+    B, H, S, D = k.shape
+    lo, hi = partition(H, rank, world)
+    Hs = hi - lo
+    cbk = block if cbk is None else cbk
+    cbv = block if cbv is None else cbv
+    km = ops.K_CHANNEL if k_mode == QuantMode.ChannelQuant else ops.K_TOKEN
+    flags = ops.new_flags(k.device)
+    kq = ops.quantize(k, block, k_rel, km, bits=bits_k, flags=flags)
+    vq = ops.quantize(v, block, v_rel, ops.K_TOKEN, bits=bits_v, flags=flags)
+    kc = kq.codes.view(B, S, H, D)[:, :, lo:hi].reshape(B, S, Hs * D).contiguous()
+    vc = vq.codes.view(B, S, H, D)[:, :, lo:hi].reshape(B, S, Hs * D).contiguous()
+    k_stream = torch.zeros(B, encode.stream_capacity("k", S, Hs, cbk, bits_k), dtype=torch.uint8, device=k.device)
+    v_stream = torch.zeros(B, encode.stream_capacity("v", S, Hs, cbv, bits_v), dtype=torch.uint8, device=k.device)
+    _, k_info, k_bytes, _ = ops.encode_codes("k", kc, cbk, bits_k, stream=k_stream, flags=flags)
+    _, v_info, v_bytes, _ = ops.encode_codes("v", vc, cbv, bits_v, stream=v_stream, flags=flags)
+    k_scale = kq.scale[:, lo:hi].contiguous() if km == ops.K_CHANNEL else kq.scale
+    k_zero = kq.zero[:, lo:hi].contiguous() if km == ops.K_CHANNEL else kq.zero
+    layer = ops.CompressedLayer(k_stream=k_stream, k_info=k_info, k_bytes=k_bytes, k_scale=k_scale, k_zero=k_zero,
+                                v_stream=v_stream, v_info=v_info, v_bytes=v_bytes, v_scale=vq.scale, v_zero=vq.zero,
+                                n_comp=S, kv_heads=Hs, cbk=cbk, cbv=cbv, bits_k=bits_k, bits_v=bits_v, k_mode=km)
+    return layer, (lo, hi)
+
+
+def max_over_ranks(ms: float, device) -> float:
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return ms
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
