@@ -292,24 +292,104 @@ def run_reference(args, w):
     }
 
 
+def run_encode(args, rank, world, device):
+    """Encoder / append throughput on Mistral-7B-shaped KV: prefill-encode `batch` sequences of
+    16384 tokens (K per-channel, V per-token, fp16), then append one token per step through the
+    cache class.  Algorithmic bytes = fp16 K and V read + streams, block tables and parameters
+    written.  Sequences are sharded over ranks (weak scaling, no collective)."""
+    from packkv_b200 import cache as C
+    from packkv_b200 import encode, synth
+    from packkv_b200.config import PackKVCacheConfig, QuantMethod, QuantMode, RepackMethod
+    B, H, S, bits, block = args.encode_batch, 8, 16384, args.encode_bits, args.encode_block
+    dtype = torch.float16
+    k, v = synth.synth_kv(B, H, S, 128, seed=3000 + rank, dtype=dtype, device=device, apply_rope=True)
+    rel = synth.rel_for_bits(bits)
+    kw = dict(block=block, bits_k=bits, bits_v=bits, k_rel=rel, v_rel=rel, k_mode=QuantMode.ChannelQuant)
+
+    def timed(fn, steps):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    layer = None
+    for _ in range(max(args.warmup, 3)):
+        layer = encode.compress_kv(k, v, **kw)
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    ms = timed(lambda: encode.compress_kv(k, v, **kw), args.steps) / args.steps
+    clocks = sampler.stop()
+    src_bytes = 2 * k.numel() * 2
+    out_bytes = layer.stream_bytes()
+    alg = src_bytes + out_bytes
+    # append: 512 single-token steps on a cache prefilled with 1024 tokens
+    C.PackKVCacheConfigStatic.config = PackKVCacheConfig("synthetic", QuantMethod.KIVI, RepackMethod.NONE, False, block, 128 + block, 16, rel, rel)
+    cache = C.PackKVCache(B, H, 128, 1)
+    cos, sin = synth.rope_tables(1024 + 512, 128, device=device, dtype=dtype)
+    cache.update(k[:, :, :1024], v[:, :, :1024], 0, {"cos": cos[:, :1024], "sin": sin[:, :1024]})
+    pos = [1024]
+
+    def append_step():
+        t = pos[0]
+        cache.update(k[:, :, t:t + 1], v[:, :, t:t + 1], 0, {"cos": cos[:, t:t + 1], "sin": sin[:, t:t + 1]})
+        pos[0] += 1
+    ms_append = timed(append_step, 512) / 512
+    cache._check_flags()
+    C.PackKVCacheConfigStatic.config = None
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peak_gbs()
+    achieved = alg / (ms * 1e-3) / 1e9
+    return {
+        "metric": "KV encode throughput", "value": world * alg / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"mistral-7b-shaped KV encode: {B} sequences x 16384 tokens x 8 KV heads x 128 per GPU, {bits}-bit, block {block}",
+                   "l2": f"{alg / 1e9:.2f} GB per step >> 126 MB L2"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                     "traffic": None, "algorithmic_bytes_per_step": alg, "kernel": "quantise + sizes + scan + write (K and V)"},
+        "source_fp16_gbs": world * src_bytes / (ms * 1e-3) / 1e9,
+        "compressed_over_fp16": out_bytes / src_bytes,
+        "append": {"ms_per_token_step": ms_append, "sequences": B, "steps": 512,
+                   "tokens_per_s": world * B / (ms_append * 1e-3)},
+        "gpu_launches": 8 * args.steps, "clocks": clocks,
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS) + ["mistral7b-encode"])
+    ap.add_argument("--encode-batch", type=int, default=16)
+    ap.add_argument("--encode-bits", type=int, default=4)
+    ap.add_argument("--encode-block", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
                     help="multi-GPU split: independent sequences per rank (weak scaling, no collective) or KV heads per "
                          "rank with an all-gather of the outputs (strong scaling)")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = WORKLOADS.get(args.workload)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
+        if w is None:
+            raise SystemExit("--impl reference is defined for the decode workloads")
         if rank == 0:
             print(json.dumps(run_reference(args, w)), flush=True)
         return
@@ -320,6 +400,14 @@ def main():
     device = torch.device("cuda", local)
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=device)
+    if args.workload == "mistral7b-encode":
+        line = run_encode(args, rank, world, device)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            torch.distributed.barrier()
+            torch.distributed.destroy_process_group()
+        return
     line = run_ours(args, w, rank, world, device)
     if rank == 0:
         if not args.no_cpu_baseline:

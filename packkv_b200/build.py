@@ -15,7 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libpackkv_sm100.so")
-SOURCES = ["pack.cu", "quant.cu", "attn.cu", "legacy.cu", "cache.cu", "reorder.cu", "encode_entry.cu", "capi.cu"]
+SOURCES = ["pack.cu", "quant.cu", "attn.cu", "legacy.cu", "cache.cu", "reorder.cu", "fused_encode.cu", "encode_entry.cu", "capi.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",

@@ -15,6 +15,10 @@ static __device__ __align__(256) uint8_t g_static_codes[PKV_STATIC_SCRATCH_BYTES
 static int32_t encode_tensor(const pkv_encode_args& e, uint8_t* codes, cudaStream_t st) {
     if (e.which != 0 && e.which != 1) return kBadArgument;
     if (e.cb <= 0 || e.first_token % e.cb) return kBadArgument;
+    // K per-channel and V per-token go through the single-pass kernels; the scratch then holds
+    // fixed-stride block slots (smaller than the code matrix it is sized for)
+    if (fused_encode_applicable(e) && fused_encode_scratch_bytes(e) <= (int64_t)e.batch * e.tokens * e.heads * 128)
+        return launch_fused_encode(e, codes, st);
     QuantArgs q{e.x, e.stride_b, e.stride_h, e.stride_s, codes, (int64_t)e.tokens * e.heads * 128, e.scale, e.zero,
                 e.param_blocks, e.qblock > 0 ? e.first_token / e.qblock : 0, e.param_tokens, e.first_token,
                 e.batch, e.heads, e.tokens, e.qblock, e.rel, e.bits, e.mode, e.high_precision_zero, e.is_bf16, e.flags};

@@ -1,0 +1,410 @@
+// Single-pass encoder: fp16/bf16 K or V -> packed stream blocks, without a code matrix in HBM.
+//
+// Replaces, for the north-star pairing (K per-channel, V per-token), the reference's
+// quant_ints (torch, utils/compute.py:84-112) + k/v_encode_cpu (C++ on the host,
+// packkv_cuda_ext/src/{k,v}_encode_cpu.cpp); codes, parameters and block bytes are identical to
+// the separate quantise + pack kernels.
+//
+// The stream format lays blocks back to back, so a block's byte offset is the sum of all earlier
+// block sizes of its sequence.  Three launches, no device-side waiting:
+//   encode : one warp per block reads its fp16/bf16 tile, quantises on the fly and builds the
+//            block in shared memory, then stores it to a fixed-stride SLOT in scratch memory and
+//            its size to block_info[blk][1]
+//   scan   : the existing per-sequence exclusive scan (scan_sizes_kernel, pack.cu)
+//   compact: one warp per block copies its slot to its final offset in the stream
+// HBM traffic per element: 2 B read (the second read of a tile comes from L1/L2) + the block
+// bytes written, read and written once more (~0.56 B each at 4 bit) = ~3.7 B, against 5.6 B for
+// quantise -> codes -> sizes -> write.
+#include "common.cuh"
+#include "launch.h"
+#include "pack_dev.cuh"
+#include "quant_dev.cuh"
+
+namespace pkv {
+
+struct FusedArgs {
+    const void* x; int64_t sb, sh, ss;      // (B, H, S, 128), strides in elements
+    void* scale; void* zero;
+    int param_blocks, first_block;          // K channel mode parameter layout
+    int param_tokens, first_token;          // V token mode parameter layout
+    uint8_t* slots; int slot_stride;        // scratch: one slot per block, sequence-major
+    uint32_t* info; int64_t info_seq_stride; int first_cb;
+    int batch, heads, tokens, cb, bits;
+    float rel;
+    unsigned* flags;
+};
+
+__device__ __forceinline__ void store_slot(uint8_t* slot, const uint8_t* stage, int size, int lane) {
+    // slot and stage are 16-byte aligned; the slot has room for the rounded-up size
+    for (int i = 16 * lane; i < size; i += 512) *reinterpret_cast<uint4*>(slot + i) = *reinterpret_cast<const uint4*>(stage + i);
+}
+
+// ------------------------------------------------------------------------------------------ K
+// rounds of one K block: quantise 16 tokens x 4 channels per lane, pack, append to `stage`
+template <typename T, bool HP, int BITS, bool FAST>
+__device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const Quantiser<T, HP>& q0, const Quantiser<T, HP>& q1,
+                                               const Quantiser<T, HP>& q2, const Quantiser<T, HP>& q3, const KGeom& g, uint8_t* stage,
+                                               int lane, bool& bad) {
+    constexpr int LB = len_field_bits(BITS);
+    constexpr unsigned kOver = 0xFFFFFFFFu ^ (0x01010101u * ((1u << BITS) - 1u));   // bits a valid code never sets
+    const int z0 = (int)q0.zero, z1 = (int)q1.zero, z2 = (int)q2.zero, z3 = (int)q3.zero;
+    int pos = g.head_bytes;
+    unsigned round_end = 0, over = 0;
+    for (int r = 0; r < g.rounds; r++) {
+        unsigned u[16];
+        unsigned mn = 0xFFFFFFFFu, mx = 0;
+#pragma unroll
+        for (int t = 0; t < 16; t++) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)(r * 16 + t) * ss));
+            const T* e = reinterpret_cast<const T*>(&raw);
+            u[t] = q0.template code_u8<FAST>(QT<T>::ld(e), z0) | (q1.template code_u8<FAST>(QT<T>::ld(e + 1), z1) << 8) |
+                   (q2.template code_u8<FAST>(QT<T>::ld(e + 2), z2) << 16) | (q3.template code_u8<FAST>(QT<T>::ld(e + 3), z3) << 24);
+            mn = __vminu4(mn, u[t]);
+            mx = __vmaxu4(mx, u[t]);
+        }
+        over |= mx & kOver;
+        const unsigned d = __vsub4(mx, mn);
+        unsigned minword = 0, lenword = 0, lens4 = 0;
+        int len[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            len[j] = bit_length_u32((d >> (8 * j)) & 0xFFu);
+            minword |= (((mn >> (8 * j)) & 0xFFu) & ((1u << BITS) - 1u)) << (j * BITS);
+            lenword |= (unsigned)min(len[j], BITS) << (j * LB);
+            lens4 |= (unsigned)min(len[j], BITS) << (8 * j);
+            len[j] = min(len[j], BITS);
+        }
+        store_lane_fields(stage + pos, lane, 4 * BITS, minword);
+        store_lane_fields(stage + pos + g.min_bytes, lane, 4 * LB, lenword);
+        const unsigned inc = warp_inclusive_sum(lens4);
+        const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+        const unsigned exc = inc - lens4;
+        uint8_t* packs = stage + pos + g.min_bytes + g.len_bytes;
+        unsigned before = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // tokens 0..7 and 8..15 as two words of at most 32 bits: w = w * 2^len + residual
+            const unsigned m = (mn >> (8 * j)) & 0xFFu, step = 1u << len[j];
+            unsigned wt = 0, wb = 0;
+#pragma unroll
+            for (int t = 0; t < 8; t++) {
+                wt = wt * step + (((u[t] >> (8 * j)) & 0xFFu) - m);
+                wb = wb * step + (((u[t + 8] >> (8 * j)) & 0xFFu) - m);
+            }
+            const uint64_t w = ((uint64_t)wt << (8 * len[j])) | wb;
+            store_pack_smem(packs + 2 * (before + ((exc >> (8 * j)) & 0xFFu)), w, len[j]);
+            before += (tot >> (8 * j)) & 0xFFu;
+        }
+        const unsigned round_size = g.min_bytes + g.len_bytes + 2 * before;
+        round_end += round_size;
+        if (lane == 0) *reinterpret_cast<uint16_t*>(stage + 2 * r) = (uint16_t)round_end;
+        pos += round_size;
+    }
+    bad = bad || over != 0;
+    return pos;
+}
+
+// one warp per K block (cb tokens x 128 channels of one head); lane owns channels 4l..4l+3, the
+// same ownership as the stream format, so per-channel statistics need no cross-lane step.
+template <typename T, bool HP, int BITS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(FusedArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int LB = len_field_bits(BITS);
+    const int lane = lane_id(), wic = threadIdx.x >> 5;
+    const int nctx = a.tokens / a.cb;
+    const int64_t per_seq = (int64_t)nctx * a.heads;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + wic;
+    if (warp >= per_seq * a.batch) return;
+    const int b = (int)(warp / per_seq);
+    const int rem = (int)(warp % per_seq);
+    const int cbi = rem / a.heads, h = rem % a.heads;
+    const KGeom g(a.cb, BITS);
+    const int slot_smem = (g.head_bytes + g.rounds * (g.min_bytes + g.len_bytes + 128 * 2 * BITS) + 15) & ~15;
+    uint8_t* stage = smem + wic * slot_smem;
+    const T* x = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)h * a.sh + (int64_t)cbi * a.cb * a.ss + 4 * lane;
+
+    // per-channel min / max over the block
+    float lo[4], hi[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) { lo[j] = INFINITY; hi[j] = -INFINITY; }
+    for (int t = 0; t < a.cb; t++) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)t * a.ss));
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; j++) { const float v = QT<T>::ld(e + j); lo[j] = fminf(lo[j], v); hi[j] = fmaxf(hi[j], v); }
+    }
+    const Quantiser<T, HP> q0(lo[0], hi[0], a.rel), q1(lo[1], hi[1], a.rel), q2(lo[2], hi[2], a.rel), q3(lo[3], hi[3], a.rel);
+    {
+        const int64_t pi = (((int64_t)b * a.heads + h) * a.param_blocks + a.first_block + cbi) * 128 + 4 * lane;
+        T sc[4] = {QT<T>::cvt(q0.scale), QT<T>::cvt(q1.scale), QT<T>::cvt(q2.scale), QT<T>::cvt(q3.scale)};
+        T zr[4] = {QT<T>::cvt(q0.zero), QT<T>::cvt(q1.zero), QT<T>::cvt(q2.zero), QT<T>::cvt(q3.zero)};
+        *reinterpret_cast<uint2*>(reinterpret_cast<T*>(a.scale) + pi) = *reinterpret_cast<const uint2*>(sc);
+        *reinterpret_cast<uint2*>(reinterpret_cast<T*>(a.zero) + pi) = *reinterpret_cast<const uint2*>(zr);
+    }
+    bool bad = q0.degenerate() || q1.degenerate() || q2.degenerate() || q3.degenerate();
+    const bool all_fast = __all_sync(0xffffffffu, q0.fast && q1.fast && q2.fast && q3.fast);
+    const int pos = all_fast ? k_encode_rounds<T, HP, BITS, true>(x, a.ss, q0, q1, q2, q3, g, stage, lane, bad)
+                             : k_encode_rounds<T, HP, BITS, false>(x, a.ss, q0, q1, q2, q3, g, stage, lane, bad);
+    __syncwarp();
+    store_slot(a.slots + (int64_t)warp * a.slot_stride, stage, pos, lane);
+    if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * a.heads + h) * 2 + 1] = (unsigned)pos;
+    if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
+}
+
+// ------------------------------------------------------------------------------------------ V
+// one CTA per (sequence, token block): pass 1 computes the per-token parameters over all heads
+// (one warp per token); pass 2 gives each warp whole V blocks (cb tokens x 64 channels): rows are
+// quantised as they are loaded (8 channels of one token per lane, so the token's parameters are
+// fetched once per 8 elements) into a uint8 tile in shared memory, from which the lane <-> channel
+// packing reads its columns.
+template <typename T, bool HP, int BITS, bool FAST>
+__device__ __forceinline__ void v_quantise_tile(const T* src, int64_t ss, int cb, const float4* prm, uint8_t* ctile, int lane) {
+    for (int r = lane >> 3; r < cb; r += 4) {          // 8 lanes x 16 B per 128-byte row
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)r * ss + 8 * (lane & 7)));
+        const float4 pr = prm[r];                       // scale, zero, 1/scale
+        Quantiser<T, HP> qz;
+        qz.scale = pr.x; qz.zero = pr.y; qz.rcp = pr.z;
+        const int zi = (int)pr.y;
+        const T* e = reinterpret_cast<const T*>(&raw);
+        unsigned w0 = 0, w1 = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            w0 |= qz.template code_u8<FAST>(QT<T>::ld(e + j), zi) << (8 * j);
+            w1 |= qz.template code_u8<FAST>(QT<T>::ld(e + 4 + j), zi) << (8 * j);
+        }
+        *reinterpret_cast<uint2*>(ctile + r * 64 + 8 * (lane & 7)) = make_uint2(w0, w1);
+    }
+}
+
+template <typename T, bool HP, int BITS>
+__global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int LB = len_field_bits(BITS);
+    const int lane = lane_id(), wic = threadIdx.x >> 5;
+    const int cbi = blockIdx.x, b = blockIdx.y;
+    const int nctx = a.tokens / a.cb;
+    const VGeom g(a.cb, BITS);
+    const int bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * g.ppt * 2 * BITS) + 15) & ~15;
+    float4* prm = reinterpret_cast<float4*>(smem);           // [cb] (scale, zero, 1/scale, fast)
+    uint8_t* wbase = smem + 16 * a.cb + wic * (a.cb * 64 + bound16);
+    uint8_t* ctile = wbase;                                  // [cb][64] codes
+    uint8_t* stage = wbase + a.cb * 64;
+    const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * a.cb * a.ss;
+
+    // pass 1: per-token statistics across every head and channel
+    bool bad = false;
+    for (int t = wic; t < a.cb; t += 8) {
+        const T* xt = xb + (int64_t)t * a.ss + 4 * lane;
+        float lo = INFINITY, hi = -INFINITY;
+        for (int h = 0; h < a.heads; h++) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(xt + (int64_t)h * a.sh));
+            const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; j++) { const float v = QT<T>::ld(e + j); lo = fminf(lo, v); hi = fmaxf(hi, v); }
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) {
+            lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, s));
+            hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, s));
+        }
+        const Quantiser<T, HP> qz(lo, hi, a.rel);
+        bad = bad || qz.degenerate();
+        if (lane == 0) {
+            prm[t] = make_float4(qz.scale, qz.zero, qz.rcp, qz.fast ? 1.f : 0.f);
+            const int64_t pi = (int64_t)b * a.param_tokens + a.first_token + cbi * a.cb + t;
+            reinterpret_cast<T*>(a.scale)[pi] = QT<T>::cvt(qz.scale);
+            reinterpret_cast<T*>(a.zero)[pi] = QT<T>::cvt(qz.zero);
+        }
+    }
+    // one decision for the whole CTA: the cheap quotient needs every token's scale in range
+    __syncthreads();
+    bool mine_ok = true;
+    for (int t = threadIdx.x; t < a.cb; t += 256) mine_ok = mine_ok && prm[t].w != 0.f;
+    const bool all_fast = __syncthreads_and(mine_ok);
+
+    // pass 2: quantise + pack, one warp per V block
+    constexpr unsigned kOver = 0xFFu ^ ((1u << BITS) - 1u);
+    unsigned over = 0;
+    const int nvb = 2 * a.heads;
+    for (int vb = wic; vb < nvb; vb += 8) {
+        const int h = vb >> 1, half = vb & 1;
+        const T* src = xb + (int64_t)h * a.sh + 64 * half;
+        __syncwarp();
+        if (all_fast) v_quantise_tile<T, HP, BITS, true>(src, a.ss, a.cb, prm, ctile, lane);
+        else v_quantise_tile<T, HP, BITS, false>(src, a.ss, a.cb, prm, ctile, lane);
+        __syncwarp();
+        int pos = g.head_bytes;
+        unsigned seg_end = 0;
+        for (int w = 0; w < 2; w++)
+            for (int r = 0; r < g.rpw; r++) {
+                const uint8_t* col = ctile + (r * g.ppt * 16) * 64 + w * 32 + lane;
+                unsigned minword = 0, lenword = 0, lens4 = 0;
+                uint64_t wd[4];
+                int len[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    len[q] = 0; wd[q] = 0;
+                    if (q < g.ppt) {
+                        unsigned c[16];
+                        unsigned mn = 255, mx = 0;
+#pragma unroll
+                        for (int t = 0; t < 16; t++) {
+                            c[t] = col[(q * 16 + t) * 64];
+                            mn = min(mn, c[t]); mx = max(mx, c[t]);
+                        }
+                        over |= mx & kOver;
+                        len[q] = min(bit_length_u32(mx - mn), BITS);
+                        const unsigned step = 1u << len[q];
+                        unsigned wt = 0, wb = 0;
+#pragma unroll
+                        for (int t = 0; t < 8; t++) { wt = wt * step + (c[t] - mn); wb = wb * step + (c[t + 8] - mn); }
+                        wd[q] = ((uint64_t)wt << (8 * len[q])) | wb;
+                        minword |= (mn & ((1u << BITS) - 1u)) << (q * BITS);
+                        lenword |= (unsigned)len[q] << (q * LB);
+                        lens4 |= (unsigned)len[q] << (8 * q);
+                    }
+                }
+                store_lane_fields(stage + pos, lane, g.ppt * BITS, minword);
+                store_lane_fields(stage + pos + g.min_bytes, lane, g.ppt * LB, lenword);
+                const unsigned inc = warp_inclusive_sum(lens4);
+                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+                const unsigned exc = inc - lens4;
+                uint8_t* packs = stage + pos + g.min_bytes + g.len_bytes;
+                unsigned before = 0;
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+                    if (q < g.ppt) {
+                        store_pack_smem(packs + 2 * (before + ((exc >> (8 * q)) & 0xFFu)), wd[q], len[q]);
+                        before += (tot >> (8 * q)) & 0xFFu;
+                    }
+                const unsigned seg_size = g.min_bytes + g.len_bytes + 2 * before;
+                seg_end += seg_size;
+                if (lane == 0) *reinterpret_cast<uint16_t*>(stage + 2 * (w * g.rpw + r)) = (uint16_t)seg_end;
+                pos += seg_size;
+            }
+        __syncwarp();
+        const int64_t blk = ((int64_t)b * nctx + cbi) * nvb + vb;
+        store_slot(a.slots + blk * a.slot_stride, stage, pos, lane);
+        if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * nvb + vb) * 2 + 1] = (unsigned)pos;
+    }
+    if (__any_sync(0xffffffffu, bad || over != 0) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
+}
+
+// ------------------------------------------------------------------------------------ compact
+// one warp per block: slot -> final offset in the sequence's stream
+__global__ void __launch_bounds__(kWarpsPerCta * 32) compact_kernel(const uint8_t* slots, int slot_stride, uint8_t* stream,
+                                                                    int64_t stream_seq_stride, int64_t capacity, const uint32_t* info,
+                                                                    int64_t info_seq_stride, int first_blk, int blocks_per_seq, int batch,
+                                                                    int slot_smem, unsigned* flags) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int lane = lane_id(), wic = threadIdx.x >> 5;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + wic;
+    if (warp >= (int64_t)blocks_per_seq * batch) return;
+    const int b = (int)(warp / blocks_per_seq), i = (int)(warp % blocks_per_seq);
+    const uint32_t* bi = info + ((int64_t)b * info_seq_stride + first_blk + i) * 2;
+    const unsigned off = bi[0], size = bi[1];
+    if ((int64_t)off + size > capacity) {
+        if (lane == 0) atomicOr(flags, kFlagStreamOverflow);
+        return;
+    }
+    uint8_t* dst = stream + (int64_t)b * stream_seq_stride + off;
+    const int phase = (int)(reinterpret_cast<uintptr_t>(dst) & 15);
+    uint8_t* stage = smem + wic * slot_smem;
+    const uint8_t* src = slots + warp * slot_stride;
+    // bring the slot into shared memory shifted by the destination's 16-byte phase (phase is even)
+    for (int j = 2 * lane; j < (int)size; j += 64)
+        *reinterpret_cast<uint16_t*>(stage + phase + j) = *reinterpret_cast<const uint16_t*>(src + j);
+    __syncwarp();
+    warp_copy_out(dst, stage + phase, (int)size, lane);
+}
+
+// --------------------------------------------------------------------------------------- host
+template <typename K>
+static int opt_in_smem(K kernel, int bytes) {
+    if (bytes > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return kCudaError;
+    return kOk;
+}
+
+bool fused_encode_applicable(const FusedEncodeRequest& r) {
+    if (r.bits < 2 || r.bits > 4) return false;
+    if (r.cb != 32 && r.cb != 64 && r.cb != 128) return false;
+    if (r.tokens % r.cb) return false;
+    if (r.which == 0 && (r.mode != 0 || r.qblock != r.cb)) return false;   // K: per-channel parameters per stream block
+    if (r.which == 1 && r.mode != 1) return false;                           // V: per-token parameters
+    if ((reinterpret_cast<uintptr_t>(r.x) & 15) || (r.stride_b & 7) || (r.stride_h & 7) || (r.stride_s & 7)) return false;
+    return true;
+}
+
+int64_t fused_encode_scratch_bytes(const FusedEncodeRequest& r) {
+    const int nblk = (r.tokens / r.cb) * r.heads * (r.which == 0 ? 1 : 2);
+    const int bound = r.which == 0 ? KGeom(r.cb, r.bits).head_bytes + (r.cb / 16) * (16 * r.bits + 16 * len_field_bits(r.bits) + 256 * r.bits)
+                                   : VGeom(r.cb, r.bits).head_bytes + VGeom(r.cb, r.bits).nseg * (VGeom(r.cb, r.bits).min_bytes + VGeom(r.cb, r.bits).len_bytes + 32 * VGeom(r.cb, r.bits).ppt * 2 * r.bits);
+    return (int64_t)r.batch * nblk * ((bound + 15) & ~15);
+}
+
+template <typename T, bool HP, int BITS>
+static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStream_t st) {
+    FusedArgs a{};
+    a.x = r.x; a.sb = r.stride_b; a.sh = r.stride_h; a.ss = r.stride_s;
+    a.scale = r.scale; a.zero = r.zero;
+    a.param_blocks = r.param_blocks; a.first_block = r.first_token / r.cb;
+    a.param_tokens = r.param_tokens; a.first_token = r.first_token;
+    a.slots = slots;
+    a.info = r.block_info; a.info_seq_stride = r.info_seq_stride; a.first_cb = r.first_token / r.cb;
+    a.batch = r.batch; a.heads = r.heads; a.tokens = r.tokens; a.cb = r.cb; a.bits = BITS; a.rel = r.rel; a.flags = r.flags;
+    const int nctx = r.tokens / r.cb;
+    int bound16, blocks_per_seq;
+    if (r.which == 0) {
+        const KGeom g(r.cb, BITS);
+        bound16 = (g.head_bytes + g.rounds * (g.min_bytes + g.len_bytes + 128 * 2 * BITS) + 15) & ~15;
+        a.slot_stride = bound16;
+        blocks_per_seq = nctx * r.heads;
+        const int64_t nwarps = (int64_t)blocks_per_seq * r.batch;
+        const int smem = kWarpsPerCta * bound16;
+        auto kern = k_fused_encode_kernel<T, HP, BITS>;
+        if (opt_in_smem(kern, smem)) return kCudaError;
+        kern<<<(unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta), kWarpsPerCta * 32, smem, st>>>(a);
+    } else {
+        const VGeom g(r.cb, BITS);
+        bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * g.ppt * 2 * BITS) + 15) & ~15;
+        a.slot_stride = bound16;
+        blocks_per_seq = nctx * 2 * r.heads;
+        const int smem = 16 * r.cb + 8 * (r.cb * 64 + bound16);
+        auto kern = v_fused_encode_kernel<T, HP, BITS>;
+        if (opt_in_smem(kern, smem)) return kCudaError;
+        kern<<<dim3(nctx, r.batch), 256, smem, st>>>(a);
+    }
+    // offsets: reuse the per-sequence scan of the two-pass encoder
+    CodecShape sh{r.batch, r.tokens, r.heads * 128, r.cb, r.which == 0 ? 128 : 64, BITS, r.first_token / r.cb};
+    CodecBuffers cbuf{nullptr, 0, r.stream, r.stream_seq_stride, r.capacity, r.block_info, r.info_seq_stride, r.stream_bytes, r.flags};
+    int rc = launch_scan_sizes(sh, cbuf, st);
+    if (rc != kOk) return rc;
+    const int slot_smem = bound16 + 16;
+    const int64_t nwarps = (int64_t)blocks_per_seq * r.batch;
+    const int per_cb = r.which == 0 ? r.heads : 2 * r.heads;
+    compact_kernel<<<(unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta), kWarpsPerCta * 32, kWarpsPerCta * slot_smem, st>>>(
+        slots, a.slot_stride, r.stream, r.stream_seq_stride, r.capacity, r.block_info, r.info_seq_stride, (r.first_token / r.cb) * per_cb,
+        blocks_per_seq, r.batch, slot_smem, r.flags);
+    return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
+}
+
+template <typename T, bool HP>
+static int launch_fused_b(const FusedEncodeRequest& r, uint8_t* slots, cudaStream_t st) {
+    switch (r.bits) {
+        case 2: return launch_fused_t<T, HP, 2>(r, slots, st);
+        case 3: return launch_fused_t<T, HP, 3>(r, slots, st);
+        case 4: return launch_fused_t<T, HP, 4>(r, slots, st);
+    }
+    return kUnsupported;
+}
+
+int launch_fused_encode(const FusedEncodeRequest& r, uint8_t* slots, cudaStream_t st) {
+    if (!fused_encode_applicable(r)) return kUnsupported;
+    if ((int64_t)r.batch * r.tokens == 0) return kOk;
+    if (!r.x || !r.scale || !r.zero || !r.stream || !r.block_info || !r.stream_bytes || !r.flags || !slots) return kBadArgument;
+    if ((reinterpret_cast<uintptr_t>(slots) & 15) || (reinterpret_cast<uintptr_t>(r.stream) & 1) || (r.stream_seq_stride & 1)) return kBadArgument;
+    if (r.is_bf16) return r.high_precision_zero ? launch_fused_b<__nv_bfloat16, true>(r, slots, st) : launch_fused_b<__nv_bfloat16, false>(r, slots, st);
+    return r.high_precision_zero ? launch_fused_b<__half, true>(r, slots, st) : launch_fused_b<__half, false>(r, slots, st);
+}
+
+}  // namespace pkv

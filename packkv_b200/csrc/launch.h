@@ -2,6 +2,7 @@
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
+#include "../../include/packkv_sm100.h"
 
 namespace pkv {
 
@@ -82,6 +83,12 @@ int launch_gather_params(const void* src, void* dst, int64_t row_len, int first,
 int launch_rope(const RopeArgs& r, cudaStream_t st);
 int launch_dequantize(const DequantArgs& q, cudaStream_t st);
 int launch_quantize(const QuantArgs& q, cudaStream_t st);
+// single-pass encoder (fused_encode.cu); the request is the C ABI's argument block
+using FusedEncodeRequest = pkv_encode_args;
+bool fused_encode_applicable(const FusedEncodeRequest& r);
+int64_t fused_encode_scratch_bytes(const FusedEncodeRequest& r);
+int launch_fused_encode(const FusedEncodeRequest& r, uint8_t* slots, cudaStream_t st);
+int launch_scan_sizes(const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
 int launch_encode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
 int launch_decode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
 

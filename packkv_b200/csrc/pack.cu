@@ -11,40 +11,10 @@
 // HBM traffic per code: 2 bytes read (codes are read twice) + the stream bytes written.
 #include "common.cuh"
 #include "launch.h"
+#include "pack_dev.cuh"
 
 namespace pkv {
 
-constexpr int kWarpsPerCta = 4;
-
-// ---- per-pack helpers --------------------------------------------------------------------
-
-// bytewise bit_length of four packed bytes, summed
-__device__ __forceinline__ unsigned sum_bitlen4(unsigned d) {
-    return bit_length_u32(d & 0xFFu) + bit_length_u32((d >> 8) & 0xFFu) + bit_length_u32((d >> 16) & 0xFFu) +
-           bit_length_u32(d >> 24);
-}
-
-__device__ __forceinline__ void store_pack_smem(uint8_t* dst, uint64_t w, int len) {
-    // dst is 2-byte aligned; the pack takes 2*len bytes = len u16 words
-    uint16_t* q = reinterpret_cast<uint16_t*>(dst);
-#pragma unroll
-    for (int i = 0; i < 4; i++)
-        if (i < len) q[i] = (uint16_t)(w >> (16 * i));
-}
-
-// Copies `size` bytes from shared `src` to global `dst`; both have the same address modulo
-// 16 and are 2-byte aligned.  Warp-cooperative.
-__device__ __forceinline__ void warp_copy_out(uint8_t* dst, const uint8_t* src, int size, int lane) {
-    int head = (16 - (int)(reinterpret_cast<uintptr_t>(dst) & 15)) & 15;
-    if (head > size) head = size;
-    for (int i = 2 * lane; i < head; i += 64)
-        *reinterpret_cast<uint16_t*>(dst + i) = *reinterpret_cast<const uint16_t*>(src + i);
-    int body = (size - head) & ~15;
-    for (int i = 16 * lane; i < body; i += 16 * 32)
-        *reinterpret_cast<uint4*>(dst + head + i) = *reinterpret_cast<const uint4*>(src + head + i);
-    for (int i = head + body + 2 * lane; i < size; i += 64)
-        *reinterpret_cast<uint16_t*>(dst + i) = *reinterpret_cast<const uint16_t*>(src + i);
-}
 
 // Copies `size` bytes (plus up to 16 bytes of slack on either side, inside the stream
 // allocation) from global `src` into shared memory so that the shared copy of src[0] has
@@ -538,6 +508,13 @@ static PackParams make_params(const CodecShape& sh, const CodecBuffers& b) {
     p.n_seq = sh.n_seq; p.nctx = sh.ctx_len / sh.cb; p.nhid = sh.hidden / sh.hb;
     p.hidden = sh.hidden; p.cb = sh.cb; p.first_cb = sh.first_cb;
     return p;
+}
+
+int launch_scan_sizes(const CodecShape& sh, const CodecBuffers& b, cudaStream_t st) {
+    PackParams p = make_params(sh, b);
+    if (p.n_seq <= 0) return kOk;
+    scan_sizes_kernel<<<p.n_seq, 1024, 0, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
 }
 
 int launch_encode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st) {

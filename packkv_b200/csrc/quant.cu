@@ -13,38 +13,9 @@
 // Codes are written as the codec's input matrix: (B, S, H*128) uint8, row = token.
 #include "common.cuh"
 #include "launch.h"
+#include "quant_dev.cuh"
 
 namespace pkv {
-
-template <typename T> struct QT;
-template <> struct QT<__half> {
-    static __device__ __forceinline__ float ld(const __half* p) { return __half2float(*p); }
-    static __device__ __forceinline__ float rnd(float x) { return __half2float(__float2half_rn(x)); }
-    static __device__ __forceinline__ __half cvt(float x) { return __float2half_rn(x); }
-};
-template <> struct QT<__nv_bfloat16> {
-    static __device__ __forceinline__ float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-    static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-    static __device__ __forceinline__ __nv_bfloat16 cvt(float x) { return __float2bfloat16_rn(x); }
-};
-
-template <typename T, bool HP>
-struct Quantiser {
-    float scale, zero;
-    __device__ __forceinline__ Quantiser(float lo, float hi, float rel) {
-        scale = QT<T>::rnd(QT<T>::rnd(hi - lo) * rel);
-        zero = HP ? lo : QT<T>::rnd(rintf(QT<T>::rnd(__fdiv_rn(lo, scale))));
-    }
-    __device__ __forceinline__ float code(float x) const {
-        if (HP) return QT<T>::rnd(rintf(QT<T>::rnd(__fdiv_rn(QT<T>::rnd(x - zero), scale))));
-        return QT<T>::rnd(QT<T>::rnd(rintf(QT<T>::rnd(__fdiv_rn(x, scale)))) - zero);
-    }
-};
-
-__device__ __forceinline__ unsigned code_byte(float c, float limit, bool& bad) {
-    if (!(c >= 0.f && c < limit)) { bad = true; return 0u; }
-    return (unsigned)c;
-}
 
 // grid (n_blocks, H, B), 128 threads: thread = channel
 template <typename T, bool HP>

@@ -1,0 +1,81 @@
+// The reference quantiser's arithmetic (utils/compute.py:84-112) as device code: every op in
+// fp32, rounded back to the element type, round() = round-half-to-even.  Shared by quant.cu and
+// fused_encode.cu.
+#pragma once
+#include "common.cuh"
+
+namespace pkv {
+
+template <typename T> struct QT;
+template <> struct QT<__half> {
+    static __device__ __forceinline__ float ld(const __half* p) { return __half2float(*p); }
+    static __device__ __forceinline__ float rnd(float x) { return __half2float(__float2half_rn(x)); }
+    static __device__ __forceinline__ __half cvt(float x) { return __float2half_rn(x); }
+    // round(x rounded to the element type), as an integer: two conversions
+    static __device__ __forceinline__ int rnd_to_int(float x) { return __half2int_rn(__float2half_rn(x)); }
+};
+template <> struct QT<__nv_bfloat16> {
+    static __device__ __forceinline__ float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ __nv_bfloat16 cvt(float x) { return __float2bfloat16_rn(x); }
+    static __device__ __forceinline__ int rnd_to_int(float x) { return __bfloat162int_rn(__float2bfloat16_rn(x)); }
+};
+
+// Quotient x / scale as PyTorch's half/bfloat16 kernels produce it (fp32 division, then rounding
+// to the element type) at a fraction of the cost of an IEEE division per element: with the
+// correctly rounded reciprocal r = RN(1/scale), q0 = x*r, e = fma(-scale, q0, x), q1 = fma(e, r, q0)
+// is within one fp32 ulp of the exact quotient and exact whenever the quotient is representable.
+// x and scale carry at most 11 significant bits, so the exact quotient is either exactly a rounding
+// boundary of the element type (then q1 is exact) or at least one fp32 ulp away from every boundary:
+// rounding q1 to the element type gives the same value as rounding the IEEE quotient.  Scales
+// outside [1e-30, 1e30] (where r or the residual could leave the normal range) take the IEEE path.
+template <typename T, bool HP>
+struct Quantiser {
+    float scale, zero, rcp;
+    bool fast;
+    __device__ __forceinline__ Quantiser() {}
+    __device__ __forceinline__ Quantiser(float lo, float hi, float rel) {
+        scale = QT<T>::rnd(QT<T>::rnd(hi - lo) * rel);
+        zero = HP ? lo : QT<T>::rnd(rintf(QT<T>::rnd(__fdiv_rn(lo, scale))));
+        prepare();
+    }
+    __device__ __forceinline__ void prepare() {
+        const float m = fabsf(scale);
+        fast = m > 1e-30f && m < 1e30f;
+        rcp = __frcp_rn(scale);
+    }
+    template <bool FAST>
+    __device__ __forceinline__ float quotient_t(float x) const {
+        if (FAST) {
+            const float q0 = x * rcp;
+            return fmaf(fmaf(-scale, q0, x), rcp, q0);
+        }
+        return __fdiv_rn(x, scale);
+    }
+    // The code as a float.  round() of an element-type value is exact, and the final subtraction
+    // of two small integers is exact whenever the code is in range, so those two roundings of the
+    // reference are no-ops and are skipped; out-of-range codes are flagged by the caller.
+    // FAST must only be true when `fast` is (callers decide once per warp, not per element).
+    template <bool FAST>
+    __device__ __forceinline__ float code_t(float x) const {
+        if (HP) return rintf(QT<T>::rnd(quotient_t<FAST>(QT<T>::rnd(x - zero))));
+        return rintf(QT<T>::rnd(quotient_t<FAST>(x))) - zero;
+    }
+    __device__ __forceinline__ float code(float x) const { return fast ? code_t<true>(x) : code_t<false>(x); }
+    // The same code as an unsigned byte, saturated to 255 (negative, huge or NaN-derived values
+    // all end at >= 2^bits... 255, which the callers' range check reports).  zero_i = (int)zero.
+    template <bool FAST>
+    __device__ __forceinline__ unsigned code_u8(float x, int zero_i) const {
+        const int q = HP ? QT<T>::rnd_to_int(quotient_t<FAST>(QT<T>::rnd(x - zero))) : QT<T>::rnd_to_int(quotient_t<FAST>(x)) - zero_i;
+        return min((unsigned)q, 255u);
+    }
+    // parameters that cannot produce valid codes (constant channel: scale 0, or NaN / inf input)
+    __device__ __forceinline__ bool degenerate() const { return !(scale > 0.f) || !(fabsf(zero) < 3.0e4f) || !(scale < 3.0e38f); }
+};
+
+__device__ __forceinline__ unsigned code_byte(float c, float limit, bool& bad) {
+    if (!(c >= 0.f && c < limit)) { bad = true; return 0u; }
+    return (unsigned)c;
+}
+
+}  // namespace pkv
