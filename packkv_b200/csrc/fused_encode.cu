@@ -308,14 +308,23 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) compact_kernel(const uint8_
         return;
     }
     uint8_t* dst = stream + (int64_t)b * stream_seq_stride + off;
-    const int phase = (int)(reinterpret_cast<uintptr_t>(dst) & 15);
-    uint8_t* stage = smem + wic * slot_smem;
-    const uint8_t* src = slots + warp * slot_stride;
-    // bring the slot into shared memory shifted by the destination's 16-byte phase (phase is even)
-    for (int j = 2 * lane; j < (int)size; j += 64)
-        *reinterpret_cast<uint16_t*>(stage + phase + j) = *reinterpret_cast<const uint16_t*>(src + j);
-    __syncwarp();
-    warp_copy_out(dst, stage + phase, (int)size, lane);
+    const uint8_t* src = slots + warp * slot_stride;          // 16-byte aligned
+    // destination 16-byte chunks: chunk c covers block bytes [16c - phase, 16c - phase + 16)
+    const int phase = (int)(reinterpret_cast<uintptr_t>(dst) & 15);   // even
+    const int head = min((16 - phase) & 15, (int)size);               // bytes before the first aligned chunk
+    for (int j = 2 * lane; j < head; j += 64) *reinterpret_cast<uint16_t*>(dst + j) = *reinterpret_cast<const uint16_t*>(src + j);
+    const int nfull = ((int)size - head) >> 4;
+    const unsigned* s32 = reinterpret_cast<const unsigned*>(src);
+    const int sw = head >> 2;                                          // first source word of the body
+    const unsigned sh = (unsigned)(head & 3) * 8;                      // 0 or 16: byte offset inside that word
+    for (int c = lane; c < nfull; c += 32) {
+        const unsigned* p = s32 + sw + 4 * c;                          // aligned 32-bit loads, realigned by funnel shifts
+        const unsigned w0 = p[0], w1 = p[1], w2 = p[2], w3 = p[3], w4 = p[4];
+        *reinterpret_cast<uint4*>(dst + head + 16 * c) = make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh),
+                                                                    __funnelshift_r(w2, w3, sh), __funnelshift_r(w3, w4, sh));
+    }
+    for (int j = head + 16 * nfull + 2 * lane; j < (int)size; j += 64)
+        *reinterpret_cast<uint16_t*>(dst + j) = *reinterpret_cast<const uint16_t*>(src + j);
 }
 
 // --------------------------------------------------------------------------------------- host
@@ -379,10 +388,10 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
     CodecBuffers cbuf{nullptr, 0, r.stream, r.stream_seq_stride, r.capacity, r.block_info, r.info_seq_stride, r.stream_bytes, r.flags};
     int rc = launch_scan_sizes(sh, cbuf, st);
     if (rc != kOk) return rc;
-    const int slot_smem = bound16 + 16;
+    const int slot_smem = 0;
     const int64_t nwarps = (int64_t)blocks_per_seq * r.batch;
     const int per_cb = r.which == 0 ? r.heads : 2 * r.heads;
-    compact_kernel<<<(unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta), kWarpsPerCta * 32, kWarpsPerCta * slot_smem, st>>>(
+    compact_kernel<<<(unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(
         slots, a.slot_stride, r.stream, r.stream_seq_stride, r.capacity, r.block_info, r.info_seq_stride, (r.first_token / r.cb) * per_cb,
         blocks_per_seq, r.batch, slot_smem, r.flags);
     return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
