@@ -79,17 +79,19 @@ __device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const Qua
         const unsigned inc = warp_inclusive_sum(lens4);
         const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
         const unsigned exc = inc - lens4;
+#pragma unroll
+        for (int t = 0; t < 16; t++) u[t] = __vsub4(u[t], mn);
         uint8_t* packs = stage + pos + g.min_bytes + g.len_bytes;
         unsigned before = 0;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             // tokens 0..7 and 8..15 as two words of at most 32 bits: w = w * 2^len + residual
-            const unsigned m = (mn >> (8 * j)) & 0xFFu, step = 1u << len[j];
+            const unsigned step = 1u << len[j];
             unsigned wt = 0, wb = 0;
 #pragma unroll
-            for (int t = 0; t < 8; t++) {
-                wt = wt * step + (((u[t] >> (8 * j)) & 0xFFu) - m);
-                wb = wb * step + (((u[t + 8] >> (8 * j)) & 0xFFu) - m);
+            for (int t = 0; t < 8; t++) {           // u[] holds code - min for all four channels (bytewise)
+                wt = wt * step + __byte_perm(u[t], 0, 0x4440 + j);
+                wb = wb * step + __byte_perm(u[t + 8], 0, 0x4440 + j);
             }
             const uint64_t w = ((uint64_t)wt << (8 * len[j])) | wb;
             store_pack_smem(packs + 2 * (before + ((exc >> (8 * j)) & 0xFFu)), w, len[j]);
@@ -123,16 +125,18 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
     uint8_t* stage = smem + wic * slot_smem;
     const T* x = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)h * a.sh + (int64_t)cbi * a.cb * a.ss + 4 * lane;
 
-    // per-channel min / max over the block
-    float lo[4], hi[4];
-#pragma unroll
-    for (int j = 0; j < 4; j++) { lo[j] = INFINITY; hi[j] = -INFINITY; }
+    // per-channel min / max over the block, two channels per instruction in the element type
+    // (min/max of element-type values is exact, so the fp32 detour is not needed here)
+    using T2 = typename QT<T>::T2;
+    T2 lo01 = QT<T>::init2(INFINITY), lo23 = lo01, hi01 = QT<T>::init2(-INFINITY), hi23 = hi01;
     for (int t = 0; t < a.cb; t++) {
         const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)t * a.ss));
-        const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 4; j++) { const float v = QT<T>::ld(e + j); lo[j] = fminf(lo[j], v); hi[j] = fmaxf(hi[j], v); }
+        const T2 v01 = *reinterpret_cast<const T2*>(&raw.x), v23 = *reinterpret_cast<const T2*>(&raw.y);
+        lo01 = QT<T>::min2(lo01, v01); hi01 = QT<T>::max2(hi01, v01);
+        lo23 = QT<T>::min2(lo23, v23); hi23 = QT<T>::max2(hi23, v23);
     }
+    const float lo[4] = {QT<T>::lo_f(lo01), QT<T>::hi_f(lo01), QT<T>::lo_f(lo23), QT<T>::hi_f(lo23)};
+    const float hi[4] = {QT<T>::lo_f(hi01), QT<T>::hi_f(hi01), QT<T>::lo_f(hi23), QT<T>::hi_f(hi23)};
     const Quantiser<T, HP> q0(lo[0], hi[0], a.rel), q1(lo[1], hi[1], a.rel), q2(lo[2], hi[2], a.rel), q3(lo[3], hi[3], a.rel);
     {
         const int64_t pi = (((int64_t)b * a.heads + h) * a.param_blocks + a.first_block + cbi) * 128 + 4 * lane;
@@ -195,13 +199,15 @@ __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
     bool bad = false;
     for (int t = wic; t < a.cb; t += 8) {
         const T* xt = xb + (int64_t)t * a.ss + 4 * lane;
-        float lo = INFINITY, hi = -INFINITY;
+        using T2 = typename QT<T>::T2;
+        T2 lo2 = QT<T>::init2(INFINITY), hi2 = QT<T>::init2(-INFINITY);
         for (int h = 0; h < a.heads; h++) {
             const uint2 raw = __ldg(reinterpret_cast<const uint2*>(xt + (int64_t)h * a.sh));
-            const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-            for (int j = 0; j < 4; j++) { const float v = QT<T>::ld(e + j); lo = fminf(lo, v); hi = fmaxf(hi, v); }
+            const T2 v01 = *reinterpret_cast<const T2*>(&raw.x), v23 = *reinterpret_cast<const T2*>(&raw.y);
+            lo2 = QT<T>::min2(lo2, QT<T>::min2(v01, v23));
+            hi2 = QT<T>::max2(hi2, QT<T>::max2(v01, v23));
         }
+        float lo = fminf(QT<T>::lo_f(lo2), QT<T>::hi_f(lo2)), hi = fmaxf(QT<T>::lo_f(hi2), QT<T>::hi_f(hi2));
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) {
             lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, s));

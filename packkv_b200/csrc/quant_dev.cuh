@@ -13,12 +13,24 @@ template <> struct QT<__half> {
     static __device__ __forceinline__ __half cvt(float x) { return __float2half_rn(x); }
     // round(x rounded to the element type), as an integer: two conversions
     static __device__ __forceinline__ int rnd_to_int(float x) { return __half2int_rn(__float2half_rn(x)); }
+    using T2 = __half2;
+    static __device__ __forceinline__ T2 min2(T2 a, T2 b) { return __hmin2(a, b); }
+    static __device__ __forceinline__ T2 max2(T2 a, T2 b) { return __hmax2(a, b); }
+    static __device__ __forceinline__ T2 init2(float v) { return __float2half2_rn(v); }
+    static __device__ __forceinline__ float lo_f(T2 a) { return __low2float(a); }
+    static __device__ __forceinline__ float hi_f(T2 a) { return __high2float(a); }
 };
 template <> struct QT<__nv_bfloat16> {
     static __device__ __forceinline__ float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
     static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
     static __device__ __forceinline__ __nv_bfloat16 cvt(float x) { return __float2bfloat16_rn(x); }
     static __device__ __forceinline__ int rnd_to_int(float x) { return __bfloat162int_rn(__float2bfloat16_rn(x)); }
+    using T2 = __nv_bfloat162;
+    static __device__ __forceinline__ T2 min2(T2 a, T2 b) { return __hmin2(a, b); }
+    static __device__ __forceinline__ T2 max2(T2 a, T2 b) { return __hmax2(a, b); }
+    static __device__ __forceinline__ T2 init2(float v) { return __float2bfloat162_rn(v); }
+    static __device__ __forceinline__ float lo_f(T2 a) { return __low2float(a); }
+    static __device__ __forceinline__ float hi_f(T2 a) { return __high2float(a); }
 };
 
 // Quotient x / scale as PyTorch's half/bfloat16 kernels produce it (fp32 division, then rounding
