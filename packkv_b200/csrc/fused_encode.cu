@@ -46,53 +46,55 @@ __device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const Qua
                                                const Quantiser<T, HP>& q2, const Quantiser<T, HP>& q3, const KGeom& g, uint8_t* stage,
                                                int lane, bool& bad) {
     constexpr int LB = len_field_bits(BITS);
-    constexpr unsigned kOver = 0xFFFFFFFFu ^ (0x01010101u * ((1u << BITS) - 1u));   // bits a valid code never sets
     const int z0 = (int)q0.zero, z1 = (int)q1.zero, z2 = (int)q2.zero, z3 = (int)q3.zero;
     int pos = g.head_bytes;
     unsigned round_end = 0, over = 0;
     for (int r = 0; r < g.rounds; r++) {
-        unsigned u[16];
-        unsigned mn = 0xFFFFFFFFu, mx = 0;
+        unsigned u[16];                               // four channel codes per token, one byte each
+        unsigned mnj[4] = {255u, 255u, 255u, 255u}, mxj[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
         for (int t = 0; t < 16; t++) {
             const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)(r * 16 + t) * ss));
             const T* e = reinterpret_cast<const T*>(&raw);
-            u[t] = q0.template code_u8<FAST>(QT<T>::ld(e), z0) | (q1.template code_u8<FAST>(QT<T>::ld(e + 1), z1) << 8) |
-                   (q2.template code_u8<FAST>(QT<T>::ld(e + 2), z2) << 16) | (q3.template code_u8<FAST>(QT<T>::ld(e + 3), z3) << 24);
-            mn = __vminu4(mn, u[t]);
-            mx = __vmaxu4(mx, u[t]);
+            const unsigned c0 = q0.template code_u8<FAST>(QT<T>::ld(e), z0), c1 = q1.template code_u8<FAST>(QT<T>::ld(e + 1), z1);
+            const unsigned c2 = q2.template code_u8<FAST>(QT<T>::ld(e + 2), z2), c3 = q3.template code_u8<FAST>(QT<T>::ld(e + 3), z3);
+            mnj[0] = min(mnj[0], c0); mxj[0] = max(mxj[0], c0);
+            mnj[1] = min(mnj[1], c1); mxj[1] = max(mxj[1], c1);
+            mnj[2] = min(mnj[2], c2); mxj[2] = max(mxj[2], c2);
+            mnj[3] = min(mnj[3], c3); mxj[3] = max(mxj[3], c3);
+            u[t] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
         }
-        over |= mx & kOver;
-        const unsigned d = __vsub4(mx, mn);
         unsigned minword = 0, lenword = 0, lens4 = 0;
         int len[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            len[j] = bit_length_u32((d >> (8 * j)) & 0xFFu);
-            minword |= (((mn >> (8 * j)) & 0xFFu) & ((1u << BITS) - 1u)) << (j * BITS);
-            lenword |= (unsigned)min(len[j], BITS) << (j * LB);
-            lens4 |= (unsigned)min(len[j], BITS) << (8 * j);
-            len[j] = min(len[j], BITS);
+            over |= mxj[j] >> BITS;
+            len[j] = min(bit_length_u32(mxj[j] - mnj[j]), BITS);
+            minword |= (mnj[j] & ((1u << BITS) - 1u)) << (j * BITS);
+            lenword |= (unsigned)len[j] << (j * LB);
+            lens4 |= (unsigned)len[j] << (8 * j);
         }
         store_lane_fields(stage + pos, lane, 4 * BITS, minword);
         store_lane_fields(stage + pos + g.min_bytes, lane, 4 * LB, lenword);
         const unsigned inc = warp_inclusive_sum(lens4);
         const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
         const unsigned exc = inc - lens4;
-#pragma unroll
-        for (int t = 0; t < 16; t++) u[t] = __vsub4(u[t], mn);
         uint8_t* packs = stage + pos + g.min_bytes + g.len_bytes;
         unsigned before = 0;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            // tokens 0..7 and 8..15 as two words of at most 32 bits: w = w * 2^len + residual
+            // tokens 0..7 and 8..15 as two words of at most 32 bits: w = w * 2^len + code, then the
+            // minimum is taken off all eight fields at once (min * (1 + 2^len + ... + 2^(7 len)))
             const unsigned step = 1u << len[j];
-            unsigned wt = 0, wb = 0;
+            unsigned wt = 0, wb = 0, ones = 0;
 #pragma unroll
-            for (int t = 0; t < 8; t++) {           // u[] holds code - min for all four channels (bytewise)
+            for (int t = 0; t < 8; t++) {
                 wt = wt * step + __byte_perm(u[t], 0, 0x4440 + j);
                 wb = wb * step + __byte_perm(u[t + 8], 0, 0x4440 + j);
+                ones = ones * step + 1u;
             }
+            wt -= mnj[j] * ones;
+            wb -= mnj[j] * ones;
             const uint64_t w = ((uint64_t)wt << (8 * len[j])) | wb;
             store_pack_smem(packs + 2 * (before + ((exc >> (8 * j)) & 0xFFu)), w, len[j]);
             before += (tot >> (8 * j)) & 0xFFu;
@@ -180,24 +182,25 @@ __device__ __forceinline__ void v_quantise_tile(const T* src, int64_t ss, int cb
     }
 }
 
-template <typename T, bool HP, int BITS>
+template <typename T, bool HP, int BITS, int CB>
 __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int LB = len_field_bits(BITS);
     const int lane = lane_id(), wic = threadIdx.x >> 5;
     const int cbi = blockIdx.x, b = blockIdx.y;
-    const int nctx = a.tokens / a.cb;
-    const VGeom g(a.cb, BITS);
-    const int bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * g.ppt * 2 * BITS) + 15) & ~15;
+    const int nctx = a.tokens / CB;
+    constexpr int PPT = CB == 32 ? 2 : 4, RPW = CB == 128 ? 2 : 1;
+    const VGeom g(CB, BITS);
+    const int bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * PPT * 2 * BITS) + 15) & ~15;
     float4* prm = reinterpret_cast<float4*>(smem);           // [cb] (scale, zero, 1/scale, fast)
-    uint8_t* wbase = smem + 16 * a.cb + wic * (a.cb * 64 + bound16);
+    uint8_t* wbase = smem + 16 * CB + wic * (CB * 64 + bound16);
     uint8_t* ctile = wbase;                                  // [cb][64] codes
-    uint8_t* stage = wbase + a.cb * 64;
-    const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * a.cb * a.ss;
+    uint8_t* stage = wbase + CB * 64;
+    const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
 
     // pass 1: per-token statistics across every head and channel
     bool bad = false;
-    for (int t = wic; t < a.cb; t += 8) {
+    for (int t = wic; t < CB; t += 8) {
         const T* xt = xb + (int64_t)t * a.ss + 4 * lane;
         using T2 = typename QT<T>::T2;
         T2 lo2 = QT<T>::init2(INFINITY), hi2 = QT<T>::init2(-INFINITY);
@@ -217,7 +220,7 @@ __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
         bad = bad || qz.degenerate();
         if (lane == 0) {
             prm[t] = make_float4(qz.scale, qz.zero, qz.rcp, qz.fast ? 1.f : 0.f);
-            const int64_t pi = (int64_t)b * a.param_tokens + a.first_token + cbi * a.cb + t;
+            const int64_t pi = (int64_t)b * a.param_tokens + a.first_token + cbi * CB + t;
             reinterpret_cast<T*>(a.scale)[pi] = QT<T>::cvt(qz.scale);
             reinterpret_cast<T*>(a.zero)[pi] = QT<T>::cvt(qz.zero);
         }
@@ -225,7 +228,7 @@ __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
     // one decision for the whole CTA: the cheap quotient needs every token's scale in range
     __syncthreads();
     bool mine_ok = true;
-    for (int t = threadIdx.x; t < a.cb; t += 256) mine_ok = mine_ok && prm[t].w != 0.f;
+    for (int t = threadIdx.x; t < CB; t += 256) mine_ok = mine_ok && prm[t].w != 0.f;
     const bool all_fast = __syncthreads_and(mine_ok);
 
     // pass 2: quantise + pack, one warp per V block
@@ -236,21 +239,21 @@ __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
         const int h = vb >> 1, half = vb & 1;
         const T* src = xb + (int64_t)h * a.sh + 64 * half;
         __syncwarp();
-        if (all_fast) v_quantise_tile<T, HP, BITS, true>(src, a.ss, a.cb, prm, ctile, lane);
-        else v_quantise_tile<T, HP, BITS, false>(src, a.ss, a.cb, prm, ctile, lane);
+        if (all_fast) v_quantise_tile<T, HP, BITS, true>(src, a.ss, CB, prm, ctile, lane);
+        else v_quantise_tile<T, HP, BITS, false>(src, a.ss, CB, prm, ctile, lane);
         __syncwarp();
         int pos = g.head_bytes;
         unsigned seg_end = 0;
         for (int w = 0; w < 2; w++)
-            for (int r = 0; r < g.rpw; r++) {
-                const uint8_t* col = ctile + (r * g.ppt * 16) * 64 + w * 32 + lane;
+            for (int r = 0; r < RPW; r++) {
+                const uint8_t* col = ctile + (r * PPT * 16) * 64 + w * 32 + lane;
                 unsigned minword = 0, lenword = 0, lens4 = 0;
                 uint64_t wd[4];
                 int len[4];
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     len[q] = 0; wd[q] = 0;
-                    if (q < g.ppt) {
+                    if (q < PPT) {
                         unsigned c[16];
                         unsigned mn = 255, mx = 0;
 #pragma unroll
@@ -270,8 +273,8 @@ __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
                         lens4 |= (unsigned)len[q] << (8 * q);
                     }
                 }
-                store_lane_fields(stage + pos, lane, g.ppt * BITS, minword);
-                store_lane_fields(stage + pos + g.min_bytes, lane, g.ppt * LB, lenword);
+                store_lane_fields(stage + pos, lane, PPT * BITS, minword);
+                store_lane_fields(stage + pos + g.min_bytes, lane, PPT * LB, lenword);
                 const unsigned inc = warp_inclusive_sum(lens4);
                 const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
                 const unsigned exc = inc - lens4;
@@ -279,13 +282,13 @@ __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
                 unsigned before = 0;
 #pragma unroll
                 for (int q = 0; q < 4; q++)
-                    if (q < g.ppt) {
+                    if (q < PPT) {
                         store_pack_smem(packs + 2 * (before + ((exc >> (8 * q)) & 0xFFu)), wd[q], len[q]);
                         before += (tot >> (8 * q)) & 0xFFu;
                     }
                 const unsigned seg_size = g.min_bytes + g.len_bytes + 2 * before;
                 seg_end += seg_size;
-                if (lane == 0) *reinterpret_cast<uint16_t*>(stage + 2 * (w * g.rpw + r)) = (uint16_t)seg_end;
+                if (lane == 0) *reinterpret_cast<uint16_t*>(stage + 2 * (w * RPW + r)) = (uint16_t)seg_end;
                 pos += seg_size;
             }
         __syncwarp();
@@ -341,6 +344,7 @@ static int opt_in_smem(K kernel, int bytes) {
 }
 
 bool fused_encode_applicable(const FusedEncodeRequest& r) {
+    if (r.high_precision_zero) return false;   // rare mode: served by the two-stage encoder
     if (r.bits < 2 || r.bits > 4) return false;
     if (r.cb != 32 && r.cb != 64 && r.cb != 128) return false;
     if (r.tokens % r.cb) return false;
@@ -385,9 +389,16 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
         a.slot_stride = bound16;
         blocks_per_seq = nctx * 2 * r.heads;
         const int smem = 16 * r.cb + 8 * (r.cb * 64 + bound16);
-        auto kern = v_fused_encode_kernel<T, HP, BITS>;
-        if (opt_in_smem(kern, smem)) return kCudaError;
-        kern<<<dim3(nctx, r.batch), 256, smem, st>>>(a);
+        auto launch_v = [&](auto kern) {
+            if (opt_in_smem(kern, smem)) return (int)kCudaError;
+            kern<<<dim3(nctx, r.batch), 256, smem, st>>>(a);
+            return (int)kOk;
+        };
+        int rc = kOk;
+        if (r.cb == 32) rc = launch_v(v_fused_encode_kernel<T, HP, BITS, 32>);
+        else if (r.cb == 64) rc = launch_v(v_fused_encode_kernel<T, HP, BITS, 64>);
+        else rc = launch_v(v_fused_encode_kernel<T, HP, BITS, 128>);
+        if (rc != kOk) return rc;
     }
     // offsets: reuse the per-sequence scan of the two-pass encoder
     CodecShape sh{r.batch, r.tokens, r.heads * 128, r.cb, r.which == 0 ? 128 : 64, BITS, r.first_token / r.cb};
@@ -418,8 +429,7 @@ int launch_fused_encode(const FusedEncodeRequest& r, uint8_t* slots, cudaStream_
     if ((int64_t)r.batch * r.tokens == 0) return kOk;
     if (!r.x || !r.scale || !r.zero || !r.stream || !r.block_info || !r.stream_bytes || !r.flags || !slots) return kBadArgument;
     if ((reinterpret_cast<uintptr_t>(slots) & 15) || (reinterpret_cast<uintptr_t>(r.stream) & 1) || (r.stream_seq_stride & 1)) return kBadArgument;
-    if (r.is_bf16) return r.high_precision_zero ? launch_fused_b<__nv_bfloat16, true>(r, slots, st) : launch_fused_b<__nv_bfloat16, false>(r, slots, st);
-    return r.high_precision_zero ? launch_fused_b<__half, true>(r, slots, st) : launch_fused_b<__half, false>(r, slots, st);
+    return r.is_bf16 ? launch_fused_b<__nv_bfloat16, false>(r, slots, st) : launch_fused_b<__half, false>(r, slots, st);
 }
 
 }  // namespace pkv
