@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libpackkv_sm100.so")
+# PACKKV_SM100_LIB points at another build of the same ABI (e.g. an instrumented one)
+LIB_PATH = os.environ.get("PACKKV_SM100_LIB") or os.path.join(_PKG, "libpackkv_sm100.so")
 
 PKV_OK, PKV_ERR_BAD_ARGUMENT, PKV_ERR_UNSUPPORTED, PKV_ERR_CUDA, PKV_ERR_TOO_LARGE = 0, 1, 2, 3, 4
 STATIC_SCRATCH_BYTES = 16 << 20

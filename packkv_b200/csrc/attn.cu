@@ -20,7 +20,9 @@
 //   phase 1  every warp of the cluster walks its 128-token (or 64-token) tiles: K blocks are
 //            staged with cp.async, unpacked, dequantised and contracted with q on the tensor
 //            cores; scores stay in the warp's shared memory.  Residual (uncompressed) tokens
-//            are spread over the same warps.
+//            are 16-token tiles handed to the same warps and contracted by the same mma
+//            (K rows straight from global memory as A fragments, V rows staged in shared
+//            memory and transposed on load with ldmatrix).
 //   exchange per-CTA (max, sum) go through distributed shared memory, one cluster barrier.
 //   phase 2  scores -> probabilities in place, V blocks are unpacked and contracted.
 //   reduce   warps -> CTA in shared memory, CTAs -> rank 0 through distributed shared memory.
@@ -55,6 +57,8 @@ template <> struct Tr<__half> {
     static __device__ __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
     static __device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
     static __device__ __forceinline__ T2 dup(__half x) { return __half2half2(x); }
+    static __device__ __forceinline__ float2 unpack2(unsigned v) { return __half22float2(*reinterpret_cast<const __half2*>(&v)); }
+    static __device__ __forceinline__ unsigned pack2(float lo, float hi) { __half2 h = __floats2half2_rn(lo, hi); return *reinterpret_cast<unsigned*>(&h); }
     static __device__ __forceinline__ void mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
         asm volatile(
             "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -72,6 +76,8 @@ template <> struct Tr<__nv_bfloat16> {
     static __device__ __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
     static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
     static __device__ __forceinline__ T2 dup(__nv_bfloat16 x) { return __bfloat162bfloat162(x); }
+    static __device__ __forceinline__ float2 unpack2(unsigned v) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v)); }
+    static __device__ __forceinline__ unsigned pack2(float lo, float hi) { __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<unsigned*>(&h); }
     static __device__ __forceinline__ void mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
         asm volatile(
             "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -99,7 +105,21 @@ __device__ __forceinline__ void cp_async16(uint8_t* smem_dst, const uint8_t* gsr
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-__device__ __forceinline__ float fast_exp(float x) { return exp2f(x * 1.4426950408889634f); }
+// exp(x) for x <= 0 (softmax arguments): one multiply and one MUFU; results below the normal
+// range flush to zero, which the rounding to the element type does anyway
+__device__ __forceinline__ float fast_exp(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+    return y;
+}
+__device__ __forceinline__ void cp_async16_zfill(unsigned smem_dst, const void* gsrc, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_dst), "l"(gsrc), "r"(valid ? 16 : 0));
+}
+// four 8x8 b16 matrices, transposed on load: lane l passes the address of row l%8 of matrix l/8
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned addr, unsigned (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
 
 struct AttnDev {
     AttnArgs a;
@@ -107,7 +127,7 @@ struct AttnDev {
     int tile;            // tokens per warp tile: 128 or 64
     int tiles_total;     // n_comp / tile
     int tpw;             // max tiles per warp
-    int rpw;             // max residual tokens per warp
+    int rtw;             // max residual tiles (16 tokens) per warp
     int rows;            // score rows kept per tile (q heads of the group, rounded up to even)
     int slot;            // bytes of one staging slot
     int prow;            // bytes of one row of the score / probability tile
@@ -152,7 +172,7 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
     T* vsz = reinterpret_cast<T*>(xch + 2048);         // [tile] V scale, [tile] V zero(-bias)
     T* ksz = vsz + 2 * P.tile;                         // token mode: [tile] K scale, [tile] K zero(-bias)
     uint8_t* stile = reinterpret_cast<uint8_t*>(ksz + 2 * P.tile);   // [tpw][rows][prow] scores -> probabilities
-    float* rsc = reinterpret_cast<float*>(stile + P.tpw * P.rows * P.prow);   // [rpw][8] residual scores
+    const unsigned rst_a = smem_addr(stile + P.tpw * P.rows * P.prow);      // [rtw][rows][16] residual scores -> probabilities
     CtaShared* cs = reinterpret_cast<CtaShared*>(smem + P.cta_off);
     // 32-bit shared-window addresses for the hot loops
     const unsigned wbase_a = smem_addr(wbase), xch_a = smem_addr(xch), vsz_a = smem_addr(vsz), stile_a = smem_addr(stile);
@@ -164,7 +184,10 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
     const unsigned vld = xch_a + g * 64 + ((c ^ ((g >> 1) & 3)) << 4);
 
     const int my_tiles = gw < P.tiles_total ? (P.tiles_total - gw + n_warps - 1) / n_warps : 0;
-    const int my_res = gw < a.n_res ? (a.n_res - gw + n_warps - 1) / n_warps : 0;
+    // residual tiles are dealt from the last warp backwards (the compressed tiles are dealt from
+    // the first warp forwards, so the warps with one tile fewer take them)
+    const int n_rt = (a.n_res + 15) >> 4, rslot = n_warps - 1 - gw;
+    const int my_rt = rslot < n_rt ? (n_rt - rslot + n_warps - 1) / n_warps : 0;
     const int nkb = 1 << P.nkb_shift, nvi = 1 << P.nvi_shift;   // K blocks / V blocks per tile
     const int k_items = my_tiles << P.nkb_shift, v_items = my_tiles << P.nvi_shift;
     const int total_items = k_items + v_items;
@@ -368,41 +391,39 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
         __syncwarp();
     }
 
-    // ---- residual tokens, phase 1: scores ------------------------------------------------------
-    // token r = gw + k*n_warps; lane owns channels 4*lane .. 4*lane+3
-    const T* kr = reinterpret_cast<const T*>(a.k_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride + 4 * lane;
-    const T* vr = reinterpret_cast<const T*>(a.v_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride + 4 * lane;
-    float mres[8];
+    // ---- residual tiles, phase 1: scores -------------------------------------------------------
+    // A fragments come straight from the uncompressed rows: lane (g, c) reads channels
+    // 32c..32c+31 of tokens g and g+8, the same channel order as the q fragments.
+    const T* kres = reinterpret_cast<const T*>(a.k_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
+    const T* vres = reinterpret_cast<const T*>(a.v_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
+    for (int k = 0; k < my_rt; k++) {
+        const int tok0 = (rslot + k * n_warps) << 4;
+        const int ta = tok0 + g, tb = tok0 + g + 8;
+        const uint4* pa = reinterpret_cast<const uint4*>(kres + (int64_t)min(ta, a.n_res - 1) * kD + 32 * c);
+        const uint4* pb = reinterpret_cast<const uint4*>(kres + (int64_t)min(tb, a.n_res - 1) * kD + 32 * c);
+        uint4 ra[4], rb[4];
 #pragma unroll
-    for (int i = 0; i < 8; i++) mres[i] = -INFINITY;
-    if (my_res > 0) {
-        float qv[8][4];
+        for (int i = 0; i < 4; i++) { ra[i] = __ldg(pa + i); rb[i] = __ldg(pb + i); }
+        float accs[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const T* qp = reinterpret_cast<const T*>(a.q) + ((int64_t)(b * q_heads + h * G + min(i, G - 1))) * kD + 4 * lane;
-            const uint2 qq = *reinterpret_cast<const uint2*>(qp);
-            const T* qt = reinterpret_cast<const T*>(&qq);
-#pragma unroll
-            for (int j = 0; j < 4; j++) qv[i][j] = i < G ? Tr<T>::to_float(qt[j]) : 0.f;
+        for (int i = 0; i < 4; i++) {
+            const unsigned f0[4] = {ra[i].x, rb[i].x, ra[i].y, rb[i].y};
+            const unsigned f1[4] = {ra[i].z, rb[i].z, ra[i].w, rb[i].w};
+            Tr<T>::mma(accs[0], f0, qf[2 * i][0], qf[2 * i][1]);
+            Tr<T>::mma(accs[1], f1, qf[2 * i + 1][0], qf[2 * i + 1][1]);
         }
-        for (int k = 0; k < my_res; k++) {
-            const int r = gw + k * n_warps;
-            const uint2 kk = *reinterpret_cast<const uint2*>(kr + (int64_t)r * kD);
-            const T* kt = reinterpret_cast<const T*>(&kk);
-            float kf[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) kf[j] = Tr<T>::to_float(kt[j]);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                if (i < G) {
-                    float d = qv[i][0] * kf[0] + qv[i][1] * kf[1] + qv[i][2] * kf[2] + qv[i][3] * kf[3];
-#pragma unroll
-                    for (int s = 16; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
-                    const float sc = Tr<T>::round(Tr<T>::round(d) * a.scaling);
-                    mres[i] = fmaxf(mres[i], sc);
-                    if (lane == 0) rsc[k * 8 + i] = sc;
-                }
-            }
+        if (col_live) {
+            const float ninf = -INFINITY;
+            const float sa0 = ta < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][0] + accs[1][0]) * a.scaling) : ninf;
+            const float sa1 = ta < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][1] + accs[1][1]) * a.scaling) : ninf;
+            const float sb0 = tb < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][2] + accs[1][2]) * a.scaling) : ninf;
+            const float sb1 = tb < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][3] + accs[1][3]) * a.scaling) : ninf;
+            const unsigned row0 = rst_a + (k * P.rows + 2 * c) * 32 + 2 * g, row1 = row0 + 32;
+            const T h00 = Tr<T>::from_float(sa0), h01 = Tr<T>::from_float(sa1), h10 = Tr<T>::from_float(sb0), h11 = Tr<T>::from_float(sb1);
+            sts16(row0, *reinterpret_cast<const unsigned short*>(&h00)); sts16(row1, *reinterpret_cast<const unsigned short*>(&h01));
+            sts16(row0 + 16, *reinterpret_cast<const unsigned short*>(&h10)); sts16(row1 + 16, *reinterpret_cast<const unsigned short*>(&h11));
+            mloc0 = fmaxf(mloc0, fmaxf(sa0, sb0));
+            mloc1 = fmaxf(mloc1, fmaxf(sa1, sb1));
         }
     }
 
@@ -412,14 +433,9 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
         mloc0 = fmaxf(mloc0, __shfl_xor_sync(0xffffffffu, mloc0, d));
         mloc1 = fmaxf(mloc1, __shfl_xor_sync(0xffffffffu, mloc1, d));
     }
-    if (lane == 0) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) cs->wm[wic][i] = mres[i];
-    }
-    __syncwarp();
-    if (g == 0 && col_live) {
-        cs->wm[wic][2 * c] = fmaxf(cs->wm[wic][2 * c], mloc0);
-        cs->wm[wic][2 * c + 1] = fmaxf(cs->wm[wic][2 * c + 1], mloc1);
+    if (g == 0) {
+        cs->wm[wic][2 * c] = mloc0;                     // columns >= rows carry -inf or the score of a zero q
+        cs->wm[wic][2 * c + 1] = mloc1;
     }
     __syncthreads();
     if (threadIdx.x < 8) {
@@ -429,43 +445,54 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
         cs->cl_m[threadIdx.x] = m;
     }
     __syncthreads();
-    // ---- sums relative to the CTA max ---------------------------------------------------------
+    // ---- sums relative to the CTA max: every lane takes one pair of tokens per row -------------
     {
-        float l0 = 0.f, l1 = 0.f;
-        if (col_live) {
-            const float m0 = cs->cl_m[2 * c], m1 = cs->cl_m[2 * c + 1];
-            for (int tl = 0; tl < my_tiles; tl++) {
-                const T* row0 = reinterpret_cast<const T*>(stile + tl * P.rows * P.prow + (2 * c) * P.prow);
-                const T* row1 = reinterpret_cast<const T*>(stile + tl * P.rows * P.prow + (2 * c + 1) * P.prow);
-                for (int t = g; t < P.tile; t += 8) {
-                    l0 += fast_exp(Tr<T>::to_float(row0[t]) - m0);
-                    l1 += fast_exp(Tr<T>::to_float(row1[t]) - m1);
+        float lsum[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) lsum[r] = 0.f;
+        const int chunks = P.tile >> 6;                  // 32 pairs per chunk
+        for (int tl = 0; tl < my_tiles; tl++) {
+            const unsigned st = stile_a + tl * P.rows * P.prow + 4 * lane;
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                if (r < P.rows) {
+                    const float m = cs->cl_m[r];
+                    for (int ch = 0; ch < chunks; ch++) {
+                        const float2 x = Tr<T>::unpack2(lds32(st + r * P.prow + 128 * ch));
+                        lsum[r] += fast_exp(x.x - m) + fast_exp(x.y - m);
+                    }
+                }
+            }
+        }
+        if (lane < 8) {
+            for (int k = 0; k < my_rt; k++) {
+#pragma unroll
+                for (int r = 0; r < 8; r++) {
+                    if (r < P.rows) {
+                        const float m = cs->cl_m[r];
+                        const float2 x = Tr<T>::unpack2(lds32(rst_a + (k * P.rows + r) * 32 + 4 * lane));
+                        // a masked token holds -inf; if the whole CTA is masked m is -inf too and the term must be 0
+                        lsum[r] += (x.x == -INFINITY ? 0.f : fast_exp(x.x - m)) + (x.y == -INFINITY ? 0.f : fast_exp(x.y - m));
+                    }
                 }
             }
         }
 #pragma unroll
-        for (int d = 4; d < 32; d <<= 1) {
-            l0 += __shfl_xor_sync(0xffffffffu, l0, d);
-            l1 += __shfl_xor_sync(0xffffffffu, l1, d);
-        }
-        // residual scores: lanes 0..7 take head = lane
-        float lr = 0.f;
-        if (lane < G) {
-            const float m = cs->cl_m[lane];
-            for (int k = 0; k < my_res; k++) lr += fast_exp(rsc[k * 8 + lane] - m);
-        }
-        if (lane < 8) cs->wm[wic][lane] = lr;           // wm's maxima were consumed before the barrier above
-        __syncwarp();
-        if (g == 0 && col_live) {
-            cs->wm[wic][2 * c] += l0;
-            cs->wm[wic][2 * c + 1] += l1;
+        for (int r = 0; r < 8; r++) {
+            if (r < P.rows) {
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], d);
+                if (lane == 0) cs->wm[wic][r] = lsum[r];   // wm's maxima were consumed before the barrier above
+            }
         }
     }
     __syncthreads();
     if (threadIdx.x < 8) {
         float l = 0.f;
+        if ((int)threadIdx.x < P.rows) {
 #pragma unroll
-        for (int w = 0; w < kAW; w++) l += cs->wm[w][threadIdx.x];
+            for (int w = 0; w < kAW; w++) l += cs->wm[w][threadIdx.x];
+        }
         cs->cl_l[threadIdx.x] = l;
     }
     // ---- cluster exchange: global max and sum ---------------------------------------------------
@@ -500,18 +527,19 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
         const int m = n - k_items;
         const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
         const int t0 = (gw + tl * n_warps) << P.tile_shift;
-        uint8_t* st = stile + tl * P.rows * P.prow;
         const unsigned st_a = stile_a + tl * P.rows * P.prow;
 
         if (vi == 0) {
             // scores -> probabilities rounded to the element type, in place; V scale / zero of the tile
-            if (col_live) {
-                T* row0 = reinterpret_cast<T*>(st + (2 * c) * P.prow);
-                T* row1 = reinterpret_cast<T*>(st + (2 * c + 1) * P.prow);
-                const float M0 = cs->gM[2 * c], M1 = cs->gM[2 * c + 1], I0 = cs->gInvL[2 * c], I1 = cs->gInvL[2 * c + 1];
-                for (int t = g; t < P.tile; t += 8) {
-                    row0[t] = Tr<T>::from_float(fast_exp(Tr<T>::to_float(row0[t]) - M0) * I0);
-                    row1[t] = Tr<T>::from_float(fast_exp(Tr<T>::to_float(row1[t]) - M1) * I1);
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                if (r < P.rows) {
+                    const float M = cs->gM[r], I = cs->gInvL[r];
+                    for (int ch = 0; ch < (P.tile >> 6); ch++) {
+                        const unsigned ad = st_a + r * P.prow + 128 * ch + 4 * lane;
+                        const float2 x = Tr<T>::unpack2(lds32(ad));
+                        sts32(ad, Tr<T>::pack2(fast_exp(x.x - M) * I, fast_exp(x.y - M) * I));
+                    }
                 }
             }
             const T* vs = reinterpret_cast<const T*>(a.v_scale) + (int64_t)b * a.param_tokens + t0;
@@ -627,27 +655,43 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
     cp_async_wait<0>();
     __syncwarp();
 
-    // ---- residual tokens, phase 2: probabilities x V (lane owns channels 4*lane..+3) ----------
-    // (done before the accumulators are parked in shared memory: that region may overlap rsc)
-    float racc[8][4];
+    // ---- residual tiles, phase 2: probabilities x V ---------------------------------------------
+    // The tile's 16 V rows are staged (padded to 272 bytes so that ldmatrix is conflict free) in the
+    // idle staging slots; ldmatrix.trans turns them into channels x tokens A fragments.
+    for (int k = 0; k < my_rt; k++) {
+        const int tok0 = (rslot + k * n_warps) << 4;
+        __syncwarp();
+        for (int j = lane; j < 256; j += 32) {           // 16 rows x 16 chunks of 16 bytes
+            const int row = j >> 4, chunk = j & 15;
+            const bool live = tok0 + row < a.n_res;
+            cp_async16_zfill(wbase_a + row * 272 + chunk * 16, vres + (int64_t)(live ? tok0 + row : 0) * kD + 8 * chunk, live);
+        }
+        cp_async_commit();
+        if (lane < 8) {
 #pragma unroll
-    for (int i = 0; i < 8; i++)
-#pragma unroll
-        for (int j = 0; j < 4; j++) racc[i][j] = 0.f;
-    for (int k = 0; k < my_res; k++) {
-        const int r = gw + k * n_warps;
-        const uint2 vv = *reinterpret_cast<const uint2*>(vr + (int64_t)r * kD);
-        const T* vt = reinterpret_cast<const T*>(&vv);
-        float vf[4];
-#pragma unroll
-        for (int j = 0; j < 4; j++) vf[j] = Tr<T>::to_float(vt[j]);
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            if (i < G) {
-                const float p = Tr<T>::round(fast_exp(rsc[k * 8 + i] - cs->gM[i]) * cs->gInvL[i]);
-#pragma unroll
-                for (int j = 0; j < 4; j++) racc[i][j] += p * vf[j];
+            for (int r = 0; r < 8; r++) {
+                if (r < P.rows) {
+                    const float M = cs->gM[r], I = cs->gInvL[r];
+                    const unsigned ad = rst_a + (k * P.rows + r) * 32 + 4 * lane;
+                    const float2 x = Tr<T>::unpack2(lds32(ad));
+                    sts32(ad, Tr<T>::pack2(x.x == -INFINITY ? 0.f : fast_exp(x.x - M) * I, x.y == -INFINITY ? 0.f : fast_exp(x.y - M) * I));
+                }
             }
+        }
+        cp_async_wait<0>();
+        __syncwarp();
+        unsigned b0 = 0, b1 = 0;
+        if (g < P.rows) {
+            b0 = lds32(rst_a + (k * P.rows + g) * 32 + 4 * c);
+            b1 = lds32(rst_a + (k * P.rows + g) * 32 + 4 * c + 16);
+        }
+        // matrix m of the x4 load: tokens 8*(m>>1).., channels 16*mt + 8*(m&1)..
+        const unsigned lm = wbase_a + (((lane >> 4) << 3) + (lane & 7)) * 272 + (((lane >> 3) & 1) << 4);
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++) {
+            unsigned af[4];
+            ldmatrix_x4_trans(lm + 32 * mt, af);
+            Tr<T>::mma(o[mt], af, b0, b1);
         }
     }
     __syncwarp();
@@ -661,14 +705,6 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
         red[(2 * c + 1) * kD + 16 * mt + g + 8] = o[mt][3];
     }
     __syncwarp();
-    if (my_res > 0) {
-#pragma unroll
-        for (int i = 0; i < 8; i++)
-            if (i < G) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) red[i * kD + 4 * lane + j] += racc[i][j];
-            }
-    }
     __syncthreads();
     // ---- CTA reduce, then cluster reduce on rank 0 ---------------------------------------------
     {
@@ -742,7 +778,7 @@ int launch_attention(const AttnArgs& a, cudaStream_t st) {
     }
     if (a.n_res > 0) {
         if (!a.k_res || !a.v_res) return kBadArgument;
-        if ((reinterpret_cast<uintptr_t>(a.k_res) & 7) || (reinterpret_cast<uintptr_t>(a.v_res) & 7) || (a.res_seq_stride & 3) || (a.res_head_stride & 3))
+        if ((reinterpret_cast<uintptr_t>(a.k_res) & 15) || (reinterpret_cast<uintptr_t>(a.v_res) & 15) || (a.res_seq_stride & 7) || (a.res_head_stride & 7))
             return kBadArgument;
     }
     if (reinterpret_cast<uintptr_t>(a.q) & 15) return kBadArgument;
@@ -770,14 +806,15 @@ int launch_attention(const AttnArgs& a, cudaStream_t st) {
         const int kb = k_bound(a.cbk, a.bits_k), vb = v_bound(a.cbv, a.bits_v);
         slot = ((kb > vb ? kb : vb) + 48 + 15) & ~15;
     }
+    if (a.n_res > 0 && 2 * slot < 16 * 272) slot = 16 * 272 / 2;   // the residual V tile borrows both slots
     P.slot = slot;
     int smem = 0;
     for (;;) {
         P.cluster = cl;
         const int n_warps = kAW * cl;
         P.tpw = (P.tiles_total + n_warps - 1) / n_warps;
-        P.rpw = (a.n_res + n_warps - 1) / n_warps;
-        int warp_smem = 2 * slot + 2048 + 8 * P.tile + P.tpw * P.rows * P.prow + P.rpw * 8 * 4;
+        P.rtw = ((a.n_res + 15) / 16 + n_warps - 1) / n_warps;
+        int warp_smem = 2 * slot + 2048 + 8 * P.tile + P.tpw * P.rows * P.prow + P.rtw * P.rows * 32;
         P.out_off = 2 * slot > 8 * kD * 4 ? 2 * slot : 8 * kD * 4;   // behind the parked accumulators
         const int red_need = P.out_off + 2 * kD * 4;
         if (warp_smem < red_need) warp_smem = red_need;
