@@ -14,6 +14,12 @@ block.  For prefill (more than one new token), for `materialize=True` and when q
 disabled it returns dense K/V exactly like the reference (dequantised history + residual); on a
 decode step with `materialize=False` it returns (None, None) and `attend` computes the attention
 straight from the packed streams.
+
+With the installed transformers (5.x) the attention modules rotate K themselves and call
+`update(key_states, value_states, layer_idx)` without sin/cos: then no RoPE is applied here.
+`decode_handles=True` makes a decode step return a pair of `PackKVHandle`s instead of
+(None, None); the attention function registered by `packkv_b200.hf` turns them into a call of
+`attend`.
 """
 from __future__ import annotations
 
@@ -47,6 +53,14 @@ def compress_block_count(length: int, block: int, recent: int) -> int:
     return max(0, (length + block - length % block - recent) // block)
 
 
+class PackKVHandle:
+    """Stands in for the K (or V) tensor of a decode step: names the cache and the layer."""
+    __slots__ = ("cache", "layer_idx")
+
+    def __init__(self, cache: "PackKVCache", layer_idx: int):
+        self.cache, self.layer_idx = cache, layer_idx
+
+
 class _Layer:
     def __init__(self):
         self.comp: Optional[ops.CompressedLayer] = None
@@ -58,7 +72,7 @@ class _Layer:
 
 
 class PackKVCache(_HFCache):
-    def __init__(self, batch_size, head_num, head_dim, layer_num, materialize: bool = False):
+    def __init__(self, batch_size, head_num, head_dim, layer_num, materialize: bool = False, decode_handles: bool = False):
         if _HFCache is not object:
             try:
                 super().__init__(layers=[])
@@ -71,6 +85,7 @@ class PackKVCache(_HFCache):
         self.head_num = head_num          # the models pass num_attention_heads; KV heads come from the tensors
         self.head_dim = head_dim
         self.materialize = materialize
+        self.decode_handles = decode_handles
         self._layers: List[_Layer] = [_Layer() for _ in range(layer_num)]
         self.flags: Optional[torch.Tensor] = None
 
@@ -168,13 +183,15 @@ class PackKVCache(_HFCache):
 
     # ---------------------------------------------------------------------------------------------
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
-               cache_kwargs: Optional[Dict[str, Any]] = None) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+               cache_kwargs: Optional[Dict[str, Any]] = None, **_unused) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
         cfg = self._config()
         if PackKVCacheConfigStatic.extract_cache is not None:
             assert not cfg.enable_quant, "Disable quant to enable cache collect."
         L = self._layers[layer_idx]
-        cos, sin = cache_kwargs["cos"], cache_kwargs["sin"]
-        k_new = ops.rope(key_states, cos, sin)
+        if cache_kwargs is not None and "cos" in cache_kwargs and "sin" in cache_kwargs:
+            k_new = ops.rope(key_states, cache_kwargs["cos"], cache_kwargs["sin"])     # the reference's models pass K before RoPE
+        else:
+            k_new = key_states.contiguous()                                            # already rotated by the caller
         v_new = value_states
         B, H, T, D = k_new.shape
         if D != 128:
@@ -212,6 +229,8 @@ class PackKVCache(_HFCache):
             L.v_res[:, :, : L.n_res] = v_all[:, :, n_c:]
         if T > 1 or self.materialize:
             return self.dense(layer_idx)
+        if self.decode_handles:
+            return PackKVHandle(self, layer_idx), PackKVHandle(self, layer_idx)
         return None, None
 
     def dense(self, layer_idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -254,6 +273,10 @@ class PackKVCache(_HFCache):
         self._config()
         L = self._layers[0 if layer_idx is None else layer_idx]
         return L.n_comp + L.n_res
+
+    def get_mask_sizes(self, query_length: int, layer_idx: int = 0) -> Tuple[int, int]:
+        """(kv_length, kv_offset) of the mask transformers builds before this layer's update."""
+        return self.get_seq_length(layer_idx) + int(query_length), 0
 
     def compressed_bytes(self) -> int:
         """Bytes of packed streams held by all layers (synchronises)."""

@@ -1,0 +1,72 @@
+"""The cache and the fused decode attention inside an unmodified transformers model.
+
+A randomly initialised Llama-shaped model (no checkpoint) is run twice over the same tokens:
+once with dense dequantised K/V and the library's eager attention at every step -- what the
+reference's patched models do (models/llama.py:259-282) -- and once with decode steps served by
+the fused decompress-attention kernel through the registered attention function.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_llama_decode_through_registered_attention(dtype):
+    transformers = pytest.importorskip("transformers")
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from packkv_b200 import hf
+    from packkv_b200.cache import PackKVCacheConfigStatic
+    from packkv_b200.config import PackKVCacheConfig, QuantMethod, RepackMethod
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=2,
+                      intermediate_size=1024, vocab_size=2000, head_dim=128, max_position_embeddings=1024)
+    model = LlamaForCausalLM(cfg).to("cuda", dtype).eval()
+    hf.register()
+    model.set_attn_implementation(hf.ATTN_NAME)
+    PackKVCacheConfigStatic.config = PackKVCacheConfig("llama", QuantMethod.KIVI, RepackMethod.NONE, False, 64, 192, 16, 1 / 14, 1 / 14)
+    B, prefill, steps = 3, 330, 70
+    ids = torch.randint(0, 2000, (B, prefill + steps), device="cuda")
+
+    def run(materialize):
+        cache = hf.make_cache(cfg, B, materialize=materialize)
+        outs = []
+        with torch.no_grad():
+            outs.append(model(ids[:, :prefill], past_key_values=cache, use_cache=True).logits[:, -1:])
+            for t in range(prefill, prefill + steps):
+                outs.append(model(ids[:, t:t + 1], past_key_values=cache, use_cache=True).logits)
+        assert cache.get_seq_length() == prefill + steps
+        cache._check_flags()
+        return torch.cat(outs, 1).float(), cache
+
+    ref, _ = run(True)
+    got, cache = run(False)
+    assert cache._layers[0].n_comp >= 192          # the decode steps crossed block boundaries
+    err = (got - ref).abs().max() / ref.abs().max()
+    assert err < 2e-2, float(err)
+    # greedy decoding picks the same tokens wherever the reference's margin is not a near tie
+    top2 = ref.topk(2, dim=-1).values
+    clear = (top2[..., 0] - top2[..., 1]) > 4 * (got - ref).abs().max()
+    assert bool((got.argmax(-1) == ref.argmax(-1))[clear].all())
+
+
+def test_generate_runs():
+    transformers = pytest.importorskip("transformers")
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from packkv_b200 import hf
+    from packkv_b200.cache import PackKVCacheConfigStatic
+    from packkv_b200.config import PackKVCacheConfig, QuantMethod, RepackMethod
+
+    torch.manual_seed(1)
+    cfg = LlamaConfig(hidden_size=256, num_attention_heads=2, num_key_value_heads=1, num_hidden_layers=2,
+                      intermediate_size=512, vocab_size=500, head_dim=128, max_position_embeddings=1024)
+    model = LlamaForCausalLM(cfg).to("cuda", torch.float16).eval()
+    hf.register()
+    model.set_attn_implementation(hf.ATTN_NAME)
+    PackKVCacheConfigStatic.config = PackKVCacheConfig("llama", QuantMethod.KIVI, RepackMethod.NONE, False, 64, 192, 16, 1 / 14, 1 / 14)
+    ids = torch.randint(3, 500, (2, 260), device="cuda")
+    cache = hf.make_cache(cfg, 2)
+    out = model.generate(ids, attention_mask=torch.ones_like(ids), past_key_values=cache, max_new_tokens=6, do_sample=False)
+    assert out.shape == (2, 266)
+    assert cache.get_seq_length() == 265          # the last generated token is not fed back
