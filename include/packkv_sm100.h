@@ -138,6 +138,27 @@ int32_t pkv_gather_params(const void* src, void* dst, int64_t row_len, int32_t f
                           int32_t batch, int32_t tokens, int32_t block, void* cuda_stream);
 
 /*
+ * pkv_greedy_order: the reference's greedy_repacking (utils/compute.py:210-260) per sequence and token
+ *   block.  A token's feature vector is its K codes followed by its V codes (k_codes, v_codes:
+ *   (batch, tokens, heads*128) uint8, same stride).  For every pack of pack_len tokens the seed is the
+ *   remaining token with the largest cosine to the rounded mean of the remaining tokens; the others
+ *   are picked one by one as the token that adds the fewest bits (sum over features of
+ *   bit_length(max - min) of the pack); ties take the first remaining token.  order (batch,
+ *   tokens/block, block) lists original in-block positions in picked order, usable with
+ *   pkv_gather_rows / pkv_gather_params.  Comparisons are exact (integer / rational); the reference
+ *   evaluates them in fp32, so the two can differ only where two cosines tie within fp32 rounding.
+ * pkv_size_model: the reference's bit_pack size estimate (utils/compute.py:272-297) for one code
+ *   tensor (batch, tokens, hidden) uint8: *bits_sum += sum over packs (pack_len consecutive tokens of
+ *   one feature) of bit_length(max - min); present[8] |= bitmap of the code values that occur.  Both
+ *   outputs are device memory the caller zeroes.  bytes = (bits_sum * pack_len + n_packs *
+ *   (b + ceil(log2(b + 1)))) / 8 with b = ceil(log2(popcount(present))).
+ */
+int32_t pkv_greedy_order(const uint8_t* k_codes, const uint8_t* v_codes, int64_t codes_seq_stride, uint8_t* order,
+                         int32_t batch, int32_t heads, int32_t tokens, int32_t block, int32_t pack_len, void* cuda_stream);
+int32_t pkv_size_model(const uint8_t* codes, int64_t codes_seq_stride, int32_t batch, int32_t tokens, int32_t hidden,
+                       int32_t pack_len, uint64_t* bits_sum, uint32_t* present, void* cuda_stream);
+
+/*
  * One-call encoder: quantise x (batch, heads, tokens, 128) and bit-pack it behind the blocks
  * already in the streams.  Equivalent to pkv_quantize followed by pkv_k_encode (which = 0, blocks of
  * cb tokens x 128 channels) or pkv_v_encode (which = 1, cb x 64); replaces the reference's

@@ -84,6 +84,56 @@ def median_reorder(blocks: torch.Tensor) -> torch.Tensor:
     return torch.gather(blocks, 1, order.unsqueeze(2).expand_as(blocks))
 
 
+def greedy_order(blocks: torch.Tensor, pack_len: int) -> torch.Tensor:
+    """Token order (n_blocks, block) int64 of the reference's greedy_repacking
+    (utils/compute.py:210-260), restated with exact integer arithmetic: the seed of a pack is the
+    remaining token with the largest cosine to the rounded mean of the remaining tokens (compared
+    as dot^2/|x|^2 by cross-multiplication: the mean's norm is common and dots are non-negative),
+    every further token is the first remaining one that minimises the pack's bit count
+    sum_f bit_length(max_f - min_f).  The reference evaluates the cosine in fp32; both agree unless
+    two candidates tie within fp32 rounding."""
+    import numpy as np
+    x = blocks.to(torch.int64).numpy()
+    nb, n, f = x.shape
+    order = np.zeros((nb, n), dtype=np.int64)
+    bl = np.array([int(v).bit_length() for v in range(256)], dtype=np.int64)
+    for b in range(nb):
+        rem = list(range(n))
+        out = []
+        for _ in range(n // pack_len):
+            xs = x[b, rem]                                   # (r, f)
+            tot, r = xs.sum(axis=0), len(rem)
+            q, r2 = tot // r, 2 * (tot % r)
+            mean = q + ((r2 > r) | ((r2 == r) & (q % 2 == 1)))
+            dots = (xs * mean).sum(axis=1)
+            nrm = (xs * xs).sum(axis=1)
+            best = 0
+            for c in range(1, r):
+                d2, n2, bd, bn = int(dots[c]) ** 2, int(nrm[c]), int(dots[best]) ** 2, int(nrm[best])
+                gt = False if n2 == 0 else (d2 > 0 if bn == 0 else d2 * bn > bd * n2)
+                if gt:
+                    best = c
+            tok = rem.pop(best)
+            out.append(tok)
+            lo = x[b, tok].copy()
+            hi = lo.copy()
+            for _ in range(pack_len - 1):
+                if not rem:
+                    break
+                xs = x[b, rem]
+                cost = bl[np.maximum(xs, hi) - np.minimum(xs, lo)].sum(axis=1)
+                tok = rem.pop(int(np.argmin(cost)))
+                out.append(tok)
+                lo, hi = np.minimum(lo, x[b, tok]), np.maximum(hi, x[b, tok])
+        order[b] = out
+    return torch.from_numpy(order)
+
+
+def greedy_reorder(blocks: torch.Tensor, pack_len: int) -> torch.Tensor:
+    order = greedy_order(blocks, pack_len)
+    return torch.gather(blocks, 1, order.unsqueeze(2).expand_as(blocks))
+
+
 def kv_feature_blocks(k_codes5: torch.Tensor, v_codes5: torch.Tensor) -> torch.Tensor:
     """(B,H,nb,block,D) x2 -> (nb, block, 2*B*H*D), compute.py:336-338."""
     kb = k_codes5.permute(2, 3, 0, 1, 4).flatten(2, 4)

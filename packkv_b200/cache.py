@@ -146,20 +146,19 @@ class PackKVCache(_HFCache):
 
     def _compress(self, L: _Layer, k: torch.Tensor, v: torch.Tensor, cfg: PackKVCacheConfig):
         """Quantises and packs k, v (B, H, n*block, 128) behind the tokens already stored."""
-        if cfg.repack_method == RepackMethod.GREEDY:
-            raise RuntimeError("not supported")
         B, H, n, _ = k.shape
         self._ensure_store(L, H, L.n_comp + n, k.dtype, k.device, cfg)
         C, block = L.comp, cfg.block_size
         if self.flags is None:
             self.flags = ops.new_flags(k.device)
-        if cfg.repack_method == RepackMethod.MEDIAN:
-            # quantise, order the tokens of each new block by the median of their V codes, pack
+        if cfg.repack_method in (RepackMethod.MEDIAN, RepackMethod.GREEDY):
+            # quantise, reorder the tokens of each new block (median of the V codes, or greedy packs), pack
             kq = ops.quantize(k, block, cfg.k_quant_scale_rel, C.k_mode, bits=C.bits_k, high_precision_zero=C.high_precision_zero,
                               flags=self.flags, scale=C.k_scale, zero=C.k_zero, first_token=L.n_comp)
             vq = ops.quantize(v, block, cfg.v_quant_scale_rel, ops.K_TOKEN, bits=C.bits_v, high_precision_zero=C.high_precision_zero,
                               flags=self.flags, scale=C.v_scale, zero=C.v_zero, first_token=L.n_comp)
-            order = ops.median_order(vq.codes, H, block)
+            order = (ops.median_order(vq.codes, H, block) if cfg.repack_method == RepackMethod.MEDIAN
+                     else ops.greedy_order(kq.codes, vq.codes, H, block, cfg.pack_size))
             C.v_scale = ops.gather_params(C.v_scale, order, block, n, first=L.n_comp)
             C.v_zero = ops.gather_params(C.v_zero, order, block, n, first=L.n_comp)
             if C.k_mode == ops.K_TOKEN:

@@ -105,6 +105,18 @@ int32_t pkv_gather_params(const void* src, void* dst, int64_t row_len, int32_t f
     return launch_gather_params(src, dst, row_len, first, order, batch, tokens, block, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int32_t pkv_greedy_order(const uint8_t* k_codes, const uint8_t* v_codes, int64_t codes_seq_stride, uint8_t* order,
+                         int32_t batch, int32_t heads, int32_t tokens, int32_t block, int32_t pack_len, void* cuda_stream) {
+    return launch_greedy_order(k_codes, v_codes, codes_seq_stride, order, batch, heads, tokens, block, pack_len,
+                               static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_size_model(const uint8_t* codes, int64_t codes_seq_stride, int32_t batch, int32_t tokens, int32_t hidden,
+                       int32_t pack_len, uint64_t* bits_sum, uint32_t* present, void* cuda_stream) {
+    return launch_size_model(codes, codes_seq_stride, batch, tokens, hidden, pack_len,
+                             reinterpret_cast<unsigned long long*>(bits_sum), present, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int32_t pkv_rope(const void* x, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, const void* cos,
                  const void* sin, int64_t cs_stride_b, void* out, int64_t o_stride_b, int64_t o_stride_h,
                  int64_t o_stride_s, int32_t batch, int32_t heads, int32_t tokens, int32_t dim, int32_t is_bf16,

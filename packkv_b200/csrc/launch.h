@@ -76,6 +76,10 @@ struct ReorderArgs {
     int batch, heads, tokens, block;
 };
 int launch_median_order(const ReorderArgs& a, cudaStream_t st);
+int launch_greedy_order(const uint8_t* k_codes, const uint8_t* v_codes, int64_t seq_stride, uint8_t* order, int batch, int heads,
+                        int tokens, int block, int pack_len, cudaStream_t st);
+int launch_size_model(const uint8_t* codes, int64_t seq_stride, int batch, int tokens, int hidden, int pack_len,
+                      unsigned long long* bits_sum, unsigned* present, cudaStream_t st);
 int launch_gather_rows(const uint8_t* src, uint8_t* dst, int64_t seq_stride, const uint8_t* order, int batch, int tokens,
                        int block, int row_bytes, cudaStream_t st);
 int launch_gather_params(const void* src, void* dst, int64_t row_len, int first, const uint8_t* order, int batch, int tokens,

@@ -32,8 +32,9 @@ def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bi
 
     `capacity_tokens` reserves stream and table room for later appends.  With
     RepackMethod.MEDIAN the tokens of every quantisation block are reordered (same order for K and
-    V) by the descending median of their V codes before packing, which narrows the per-pack value
-    ranges; attention over the block is unaffected and `order` is kept for dense reconstruction.
+    V) by the descending median of their V codes before packing, with RepackMethod.GREEDY by the
+    reference's greedy pack-building heuristic on the K||V codes; both narrow the per-pack value
+    ranges, attention over the block is unaffected and `order` is kept for dense reconstruction.
     """
     if k.shape != v.shape or k.dim() != 4 or k.shape[3] != 128:
         raise ValueError("k and v must both be (B, Hkv, S, 128)")
@@ -57,14 +58,13 @@ def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bi
     v_info = torch.zeros(B, (cap_tok // cbv) * 2 * H, 2, dtype=torch.int32, device=dev)
     k_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
     v_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
-    if repack_method == RepackMethod.GREEDY:
-        raise RuntimeError("not supported")
-    if repack_method == RepackMethod.MEDIAN:
+    if repack_method in (RepackMethod.MEDIAN, RepackMethod.GREEDY):
         kq = ops.quantize(k, block, k_rel, km, bits=bits_k, high_precision_zero=high_precision_zero, flags=flags,
                           scale=k_scale, zero=k_zero)
         vq = ops.quantize(v, block, v_rel, ops.K_TOKEN, bits=bits_v, high_precision_zero=high_precision_zero, flags=flags,
                           scale=v_scale, zero=v_zero)
-        order = ops.median_order(vq.codes, H, block)
+        order = (ops.median_order(vq.codes, H, block) if repack_method == RepackMethod.MEDIAN
+                 else ops.greedy_order(kq.codes, vq.codes, H, block, 16))
         v_scale, v_zero = ops.gather_params(v_scale, order, block, S), ops.gather_params(v_zero, order, block, S)
         if km == ops.K_TOKEN:
             k_scale, k_zero = ops.gather_params(k_scale, order, block, S), ops.gather_params(k_zero, order, block, S)

@@ -10,6 +10,8 @@ import ctypes
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
+import math
+
 import torch
 
 from . import _lib
@@ -357,6 +359,38 @@ def median_order(v_codes: torch.Tensor, heads: int, block: int, want_keys: bool 
                                      keys.data_ptr() if want_keys else None, B, heads, S, block, _stream_ptr())
     _lib.check(st, "median_order")
     return (order, keys) if want_keys else order
+
+
+def greedy_order(k_codes: torch.Tensor, v_codes: torch.Tensor, heads: int, block: int, pack_len: int = 16) -> torch.Tensor:
+    """Token order of every block by the reference's greedy repacking heuristic
+    (utils/compute.py:210-260) on the K||V code vectors of each token.
+    k_codes, v_codes (B, S, heads*128) uint8 -> order (B, S/block, block) uint8."""
+    _require_cuda(k_codes, v_codes)
+    if k_codes.shape != v_codes.shape or k_codes.stride() != v_codes.stride():
+        raise ValueError("k_codes and v_codes must have the same shape and strides")
+    B, S, _ = k_codes.shape
+    order = torch.empty(B, S // block, block, dtype=torch.uint8, device=k_codes.device)
+    st = _lib.lib().pkv_greedy_order(k_codes.data_ptr(), v_codes.data_ptr(), k_codes.stride(0), order.data_ptr(),
+                                     B, heads, S, block, pack_len, _stream_ptr())
+    _lib.check(st, "greedy_order")
+    return order
+
+
+def size_model(codes: torch.Tensor, pack_len: int = 16) -> int:
+    """Bytes the reference's bit_pack estimate (utils/compute.py:272-297) gives for one code tensor
+    (B, S, hidden) uint8 (synchronises to read the two counters back)."""
+    _require_cuda(codes)
+    B, S, hidden = codes.shape
+    bits = torch.zeros(1, dtype=torch.int64, device=codes.device)
+    present = torch.zeros(8, dtype=torch.int32, device=codes.device)
+    st = _lib.lib().pkv_size_model(codes.data_ptr(), codes.stride(0), B, S, hidden, pack_len, bits.data_ptr(), present.data_ptr(), _stream_ptr())
+    _lib.check(st, "size_model")
+    n_values = sum(bin(int(w) & 0xFFFFFFFF).count("1") for w in present.tolist())
+    if n_values == 0:
+        return 0
+    b = math.ceil(math.log2(n_values))
+    n_packs = B * (S // pack_len) * hidden
+    return (int(bits.item()) * pack_len + n_packs * (b + math.ceil(math.log2(b + 1)))) // 8
 
 
 def gather_rows(codes: torch.Tensor, order: torch.Tensor, block: int) -> torch.Tensor:

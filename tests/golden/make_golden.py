@@ -101,6 +101,8 @@ def make_quant():
         re = ref.median_repacking(blocks)
         out[f"{dname}_median_blocks"] = re.to(torch.uint8).numpy()
         out[f"{dname}_sizes"] = np.array(ref.repack_and_encode(kc, vc, 16, ref.RepackMethod.MEDIAN), dtype=np.int64)
+        out[f"{dname}_greedy_blocks"] = ref.greedy_repacking(blocks, 16).to(torch.uint8).numpy()
+        out[f"{dname}_greedy_sizes"] = np.array(ref.repack_and_encode(kc, vc, 16, ref.RepackMethod.GREEDY), dtype=np.int64)
     out["cases"] = np.array(cases)
     np.savez_compressed(os.path.join(HERE, "quant_golden.npz"), **out)
 

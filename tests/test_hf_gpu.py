@@ -11,6 +11,42 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("family", ["mistral", "qwen3"])
+def test_other_model_families(family):
+    """The same drop-in on the other head_dim-128 families the reference patches (models/mistral.py, qwen3.py)."""
+    transformers = pytest.importorskip("transformers")
+    from packkv_b200 import hf
+    from packkv_b200.cache import PackKVCacheConfigStatic
+    from packkv_b200.config import PackKVCacheConfig, QuantMethod, RepackMethod
+    kw = dict(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=2, intermediate_size=1024,
+              vocab_size=1000, head_dim=128, max_position_embeddings=1024)
+    if family == "mistral":
+        from transformers import MistralConfig as Cfg, MistralForCausalLM as Model
+        kw["sliding_window"] = None
+    else:
+        from transformers import Qwen3Config as Cfg, Qwen3ForCausalLM as Model
+    torch.manual_seed(2)
+    cfg = Cfg(**kw)
+    model = Model(cfg).to("cuda", torch.bfloat16).eval()
+    hf.register()
+    model.set_attn_implementation(hf.ATTN_NAME)
+    PackKVCacheConfigStatic.config = PackKVCacheConfig(family, QuantMethod.KIVI, RepackMethod.MEDIAN, False, 64, 192, 16, 1 / 14, 1 / 14)
+    ids = torch.randint(0, 1000, (2, 300), device="cuda")
+
+    def run(materialize):
+        cache = hf.make_cache(cfg, 2, materialize=materialize)
+        outs = []
+        with torch.no_grad():
+            outs.append(model(ids[:, :280], past_key_values=cache, use_cache=True).logits[:, -1:])
+            for t in range(280, 300):
+                outs.append(model(ids[:, t:t + 1], past_key_values=cache, use_cache=True).logits)
+        cache._check_flags()
+        return torch.cat(outs, 1).float()
+
+    ref, got = run(True), run(False)
+    assert ((got - ref).abs().max() / ref.abs().max()).item() < 2e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_llama_decode_through_registered_attention(dtype):
     transformers = pytest.importorskip("transformers")

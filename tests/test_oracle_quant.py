@@ -52,6 +52,19 @@ def test_median_reorder_and_size_model_match_golden(golden):
         assert list(golden[f"{dname}_sizes"]) == [pre[0], pre[1], aft[0], aft[1]]
 
 
+def test_greedy_reorder_matches_golden(golden):
+    for dname, dtype in (("f16", torch.float16), ("bf16", torch.bfloat16)):
+        k = torch.from_numpy(golden[f"{dname}_k"]).view(dtype)
+        v = torch.from_numpy(golden[f"{dname}_v"]).view(dtype)
+        kc, _, _ = Q.quant_ints(k, 64, 1 / 14, "channel")
+        vc, _, _ = Q.quant_ints(v, 64, 1 / 14, "token")
+        blocks = Q.kv_feature_blocks(kc, vc)
+        re = Q.greedy_reorder(blocks, 16)
+        assert np.array_equal(re.to(torch.uint8).numpy(), golden[f"{dname}_greedy_blocks"])
+        pre, aft = Q.size_model(blocks, 16), Q.size_model(re, 16)
+        assert list(golden[f"{dname}_greedy_sizes"]) == [pre[0], pre[1], aft[0], aft[1]]
+
+
 def test_cfg0_digests(golden_dir):
     """seq-1024 plumbing configuration, every stage, by SHA-256."""
     with open(os.path.join(golden_dir, "cfg0_digest.json")) as f:
@@ -111,6 +124,7 @@ def test_against_imported_reference():
         blocks = Q.kv_feature_blocks(kc, vc)
         assert torch.equal(ref.median_repacking(blocks), Q.median_reorder(blocks))
         assert ref.repack_and_encode(kc, vc, 16, ref.RepackMethod.MEDIAN)[2:] == Q.size_model(Q.median_reorder(blocks), 16)
+        assert torch.equal(ref.greedy_repacking(blocks, 16).to(blocks.dtype), Q.greedy_reorder(blocks, 16))
         cos, sin = synth.rope_tables(256, 128, dtype=dtype)
         assert torch.equal(ref.apply_rotary_pos_emb_single(k, cos, sin), Q.rope(k, cos, sin))
         # cache step: cut + quantise + dequantise + cat
