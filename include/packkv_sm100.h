@@ -138,6 +138,19 @@ int32_t pkv_gather_params(const void* src, void* dst, int64_t row_len, int32_t f
                           int32_t batch, int32_t tokens, int32_t block, void* cuda_stream);
 
 /*
+ * Decode-step append to the uncompressed residual: rows [position, position + tokens) of k_res / v_res
+ * (batch, heads, res_capacity, 128) receive the new K tokens after rotary embedding (the reference's
+ * apply_rotary_pos_emb_single inside PackKVCachePytorchQuant.update, models/cache/packkv_quant.py:57-60;
+ * cos = sin = NULL when the caller has rotated K already) and the new V tokens
+ * (torch.cat of the buffers, utils/compute.py:160-163).  Strides in elements.
+ */
+int32_t pkv_append_residual(const void* k, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s, const void* v,
+                            int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s, const void* cos, const void* sin,
+                            int64_t cs_stride_b, void* k_res, void* v_res, int64_t res_stride_b, int64_t res_stride_h,
+                            int32_t res_capacity, int32_t position, int32_t batch, int32_t heads, int32_t tokens,
+                            int32_t is_bf16, void* cuda_stream);
+
+/*
  * pkv_greedy_order: the reference's greedy_repacking (utils/compute.py:210-260) per sequence and token
  *   block.  A token's feature vector is its K codes followed by its V codes (k_codes, v_codes:
  *   (batch, tokens, heads*128) uint8, same stride).  For every pack of pack_len tokens the seed is the

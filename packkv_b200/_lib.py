@@ -59,6 +59,7 @@ SIGNATURES = {
     "pkv_fused_wv": (_i32, [_p] * 5 + [_i32] * 4 + [_p]),
     "pkv_median_order": (_i32, [_p, _i64, _p, _p] + [_i32] * 4 + [_p]),
     "pkv_gather_rows": (_i32, [_p, _p, _i64, _p] + [_i32] * 4 + [_p]),
+    "pkv_append_residual": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _i64, _i64, _p, _p, _i64, _p, _p, _i64, _i64] + [_i32] * 6 + [_p]),
     "pkv_greedy_order": (_i32, [_p, _p, _i64, _p] + [_i32] * 5 + [_p]),
     "pkv_size_model": (_i32, [_p, _i64] + [_i32] * 4 + [_p, _p, _p]),
     "pkv_gather_params": (_i32, [_p, _p, _i64, _i32, _p] + [_i32] * 3 + [_p]),

@@ -187,14 +187,20 @@ class PackKVCache(_HFCache):
         if PackKVCacheConfigStatic.extract_cache is not None:
             assert not cfg.enable_quant, "Disable quant to enable cache collect."
         L = self._layers[layer_idx]
-        if cache_kwargs is not None and "cos" in cache_kwargs and "sin" in cache_kwargs:
-            k_new = ops.rope(key_states, cache_kwargs["cos"], cache_kwargs["sin"])     # the reference's models pass K before RoPE
-        else:
-            k_new = key_states.contiguous()                                            # already rotated by the caller
-        v_new = value_states
-        B, H, T, D = k_new.shape
+        B, H, T, D = key_states.shape
         if D != 128:
             raise RuntimeError("not supported")   # streams are built from 128-channel blocks
+        # the reference's models pass K before RoPE together with sin/cos; the installed transformers rotates K itself
+        cos, sin = (cache_kwargs["cos"], cache_kwargs["sin"]) if cache_kwargs is not None and "cos" in cache_kwargs and "sin" in cache_kwargs else (None, None)
+        if cfg.enable_quant and L.k_res is not None:
+            total = L.n_res + T
+            if compress_block_count(total, cfg.block_size, cfg.buffer_size) == 0:
+                # the common decode step: rotate K and copy V straight into the residual, one launch
+                ops.append_residual(key_states, value_states, L.k_res, L.v_res, L.n_res, cos, sin)
+                L.n_res = total
+                return self._step_result(layer_idx, T)
+        k_new = ops.rope(key_states, cos, sin) if cos is not None else key_states.contiguous()
+        v_new = value_states
         if not cfg.enable_quant:
             L.k_res = k_new if L.k_res is None else torch.cat([L.k_res[:, :, : L.n_res], k_new], dim=2)
             L.v_res = v_new.clone() if L.v_res is None else torch.cat([L.v_res[:, :, : L.n_res], v_new], dim=2)
@@ -226,6 +232,9 @@ class PackKVCache(_HFCache):
             L.n_res = total - n_c
             L.k_res[:, :, : L.n_res] = k_all[:, :, n_c:]
             L.v_res[:, :, : L.n_res] = v_all[:, :, n_c:]
+        return self._step_result(layer_idx, T)
+
+    def _step_result(self, layer_idx: int, T: int):
         if T > 1 or self.materialize:
             return self.dense(layer_idx)
         if self.decode_handles:

@@ -2,6 +2,8 @@
 //   rope        : rotary embedding of new K tokens, op for op like the reference's
 //                 apply_rotary_pos_emb_single (utils/compute.py:22-43): (t*cos) + (rotate_half(t)*sin),
 //                 each op rounded to the element type.
+//   append      : rope (optional) on the new K tokens + copy of the new V tokens into the residual
+//                 buffers, one launch per decode step and layer.
 //   dequantize  : codes + scale/zero -> dense K or V exactly as the reference's cache does it,
 //                 (code + zero) * scale or code * scale + min (utils/compute.py:173-178); used when a
 //                 caller asks for the dense history (prefill attention, debugging).
@@ -39,6 +41,28 @@ __global__ void __launch_bounds__(128) rope_kernel(RopeArgs r) {
     o[d] = CT<T>::cvt(a + c);
 }
 
+// Append of new tokens to the uncompressed residual in one launch: K is rotated (or copied when the
+// caller already applied RoPE: cos == nullptr) and V copied to rows [position, position + tokens).
+// grid (tokens, heads, batch), 128 threads = channels
+template <typename T>
+__global__ void __launch_bounds__(128) append_kernel(AppendArgs r) {
+    const int t = blockIdx.x, h = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
+    const T* x = reinterpret_cast<const T*>(r.k) + (int64_t)b * r.k_stride_b + (int64_t)h * r.k_stride_h + (int64_t)t * r.k_stride_s;
+    const T* y = reinterpret_cast<const T*>(r.v) + (int64_t)b * r.v_stride_b + (int64_t)h * r.v_stride_h + (int64_t)t * r.v_stride_s;
+    const int64_t o = (int64_t)b * r.res_stride_b + (int64_t)h * r.res_stride_h + (int64_t)(r.position + t) * 128 + d;
+    T kv = x[d];
+    if (r.cos) {
+        const T* cs = reinterpret_cast<const T*>(r.cos) + (int64_t)b * r.cs_stride_b + (int64_t)t * 128;
+        const T* sn = reinterpret_cast<const T*>(r.sin) + (int64_t)b * r.cs_stride_b + (int64_t)t * 128;
+        const float rot = d < 64 ? -CT<T>::ld(x + d + 64) : CT<T>::ld(x + d - 64);
+        const float a = CT<T>::rnd(CT<T>::ld(x + d) * CT<T>::ld(cs + d));
+        const float c = CT<T>::rnd(rot * CT<T>::ld(sn + d));
+        kv = CT<T>::cvt(a + c);
+    }
+    reinterpret_cast<T*>(r.k_res)[o] = kv;
+    reinterpret_cast<T*>(r.v_res)[o] = y[d];
+}
+
 // grid (tokens, heads, batch), 128 threads = channels
 template <typename T, bool HP>
 __global__ void __launch_bounds__(128) dequant_kernel(DequantArgs q) {
@@ -59,6 +83,16 @@ int launch_rope(const RopeArgs& r, cudaStream_t st) {
     dim3 grid(r.tokens, r.heads, r.batch);
     if (r.is_bf16) rope_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(r);
     else rope_kernel<__half><<<grid, 128, 0, st>>>(r);
+    return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
+}
+
+int launch_append(const AppendArgs& r, cudaStream_t st) {
+    if (r.batch < 0 || r.heads <= 0 || r.tokens < 0 || r.position < 0 || r.position + r.tokens > r.res_capacity) return kBadArgument;
+    if ((int64_t)r.batch * r.tokens == 0) return kOk;
+    if (!r.k || !r.v || !r.k_res || !r.v_res || ((r.cos == nullptr) != (r.sin == nullptr))) return kBadArgument;
+    dim3 grid(r.tokens, r.heads, r.batch);
+    if (r.is_bf16) append_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(r);
+    else append_kernel<__half><<<grid, 128, 0, st>>>(r);
     return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
 }
 

@@ -105,6 +105,16 @@ int32_t pkv_gather_params(const void* src, void* dst, int64_t row_len, int32_t f
     return launch_gather_params(src, dst, row_len, first, order, batch, tokens, block, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int32_t pkv_append_residual(const void* k, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s, const void* v,
+                            int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_s, const void* cos, const void* sin,
+                            int64_t cs_stride_b, void* k_res, void* v_res, int64_t res_stride_b, int64_t res_stride_h,
+                            int32_t res_capacity, int32_t position, int32_t batch, int32_t heads, int32_t tokens,
+                            int32_t is_bf16, void* cuda_stream) {
+    AppendArgs r{k, k_stride_b, k_stride_h, k_stride_s, v, v_stride_b, v_stride_h, v_stride_s, cos, sin, cs_stride_b,
+                 k_res, v_res, res_stride_b, res_stride_h, res_capacity, position, batch, heads, tokens, is_bf16};
+    return launch_append(r, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int32_t pkv_greedy_order(const uint8_t* k_codes, const uint8_t* v_codes, int64_t codes_seq_stride, uint8_t* order,
                          int32_t batch, int32_t heads, int32_t tokens, int32_t block, int32_t pack_len, void* cuda_stream) {
     return launch_greedy_order(k_codes, v_codes, codes_seq_stride, order, batch, heads, tokens, block, pack_len,

@@ -62,6 +62,14 @@ struct RopeArgs {
     void* out; int64_t o_stride_b, o_stride_h, o_stride_s;
     int batch, heads, tokens, dim, is_bf16;
 };
+struct AppendArgs {
+    const void* k; int64_t k_stride_b, k_stride_h, k_stride_s;   // new K (B, H, T, 128), strides in elements
+    const void* v; int64_t v_stride_b, v_stride_h, v_stride_s;   // new V
+    const void* cos; const void* sin; int64_t cs_stride_b;       // (B or 1, T, 128) or both null: K is already rotated
+    void* k_res; void* v_res; int64_t res_stride_b, res_stride_h; // residual buffers (B, H, capacity, 128)
+    int res_capacity, position;                                    // rows [position, position + tokens) are written
+    int batch, heads, tokens, is_bf16;
+};
 struct DequantArgs {
     const uint8_t* codes; int64_t codes_seq_stride;               // (B, T, H*128)
     const void* scale; const void* zero;
@@ -85,6 +93,7 @@ int launch_gather_rows(const uint8_t* src, uint8_t* dst, int64_t seq_stride, con
 int launch_gather_params(const void* src, void* dst, int64_t row_len, int first, const uint8_t* order, int batch, int tokens,
                          int block, cudaStream_t st);
 int launch_rope(const RopeArgs& r, cudaStream_t st);
+int launch_append(const AppendArgs& r, cudaStream_t st);
 int launch_dequantize(const DequantArgs& q, cudaStream_t st);
 int launch_quantize(const QuantArgs& q, cudaStream_t st);
 // single-pass encoder (fused_encode.cu); the request is the C ABI's argument block

@@ -275,6 +275,32 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[to
     return out
 
 
+def append_residual(k_new: torch.Tensor, v_new: torch.Tensor, k_res: torch.Tensor, v_res: torch.Tensor, position: int,
+                    cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> None:
+    """Writes the new tokens (B, H, T, 128) into rows [position, position+T) of the residual buffers
+    (B, H, capacity, 128): K after RoPE (skipped when cos/sin are None), V as is.  One launch."""
+    _require_cuda(k_new, v_new, k_res, v_res, cos, sin)
+    B, H, T, D = k_new.shape
+    if D != 128 or v_new.shape != k_new.shape or k_new.stride(3) != 1 or v_new.stride(3) != 1:
+        raise ValueError("k_new and v_new must be (B, H, T, 128) with contiguous channels")
+    if k_res.shape != v_res.shape or k_res.stride() != v_res.stride() or k_res.stride(3) != 1 or k_res.stride(2) != 128:
+        raise ValueError("k_res and v_res must be (B, H, capacity, 128) with contiguous rows and equal strides")
+    if k_res.dtype != k_new.dtype or v_new.dtype != k_new.dtype or k_new.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("dtype mismatch")
+    cs_stride = 0
+    if cos is not None:
+        cos, sin = cos.to(k_new.dtype).contiguous(), sin.to(k_new.dtype).contiguous()
+        if cos.shape[-2:] != (T, D) or sin.shape != cos.shape:
+            raise ValueError("cos/sin must be (B or 1, T, 128)")
+        cs_stride = 0 if cos.shape[0] == 1 else T * D
+    st = _lib.lib().pkv_append_residual(
+        k_new.data_ptr(), k_new.stride(0), k_new.stride(1), k_new.stride(2), v_new.data_ptr(), v_new.stride(0), v_new.stride(1), v_new.stride(2),
+        cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None, cs_stride,
+        k_res.data_ptr(), v_res.data_ptr(), k_res.stride(0), k_res.stride(1), k_res.shape[2], position, B, H, T,
+        int(k_new.dtype == torch.bfloat16), _stream_ptr())
+    _lib.check(st, "append_residual")
+
+
 def dequantize(codes: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, heads: int, block: int, mode: int, *,
                first_token: int = 0, high_precision_zero: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """codes (B, T, heads*128) uint8 + scale/zero -> dense (B, heads, T, 128) in scale's dtype."""
