@@ -121,6 +121,43 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned addr, unsigned (&r)[4
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
 }
 
+// header fields of width w at bits 0, w, 2w, 3w of a lane word -> one byte each
+struct FieldSpread { int s1, s2; unsigned m1, m2; };
+__device__ __forceinline__ unsigned spread_fields(unsigned x, const FieldSpread& f) {
+    const unsigned y = (x | (x << f.s1)) & f.m1;
+    return (y | (y << f.s2)) & f.m2;
+}
+__host__ inline FieldSpread make_field_spread(int w) {
+    return FieldSpread{16 - 2 * w, 8 - w, ((1u << (2 * w)) - 1u) * 0x00010001u, ((1u << w) - 1u) * 0x01010101u};
+}
+
+// One pack (16 codes of `len` bits, token 0 in the top bits of the 2*len-byte word) -> 16 bytes.
+// la = {2^(4 len) - 1, (2^(2 len) - 1) * 0x00010001, (2^len - 1) * 0x01010101, 4 len},
+// lb = {16 - 2 len, 8 - len, 8 len, -}: the table entry of this length.  Fields are spread by two
+// shift-or-mask steps per four codes; byte p of the result holds token p ^ 3 (the consumers pick
+// their byte pairs accordingly), each plus the pack minimum replicated in `minrep`.
+__device__ __forceinline__ uint4 unpack_pack(unsigned lo, unsigned hi, const uint4& la, const uint4& lb, unsigned minrep) {
+    const unsigned tp = __funnelshift_rc(lo, hi, lb.z);
+    unsigned w[4] = {(tp >> la.w) & la.x, tp & la.x, (lo >> la.w) & la.x, lo & la.x};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const unsigned y = (w[i] | (w[i] << lb.x)) & la.y;
+        w[i] = ((y | (y << lb.y)) & la.z) + minrep;
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ unsigned byte_of(unsigned x, int j) { return __byte_perm(x, 0, 0x4440 + j); }
+
+// Channel order of the K contraction.  mma step j = 2m + b covers, for the lanes with c = lane & 3,
+// the channels 32m + 8c + {2b, 2b+4} (k = 2c, 2c+1) and 32m + 8c + {2b+1, 2b+5} (k = 2c+8, 2c+9): the
+// order in which ldmatrix.trans delivers the exchange tile.  From the 8 consecutive elements
+// x0..x7 of channels 32m + 8c.. this forms the four operand registers of steps 2m and 2m+1:
+// f[b][0] = (x[2b], x[2b+4]), f[b][1] = (x[2b+1], x[2b+5]).
+__device__ __forceinline__ void pair_shuffle(const uint4& v, unsigned (&f0)[2], unsigned (&f1)[2]) {
+    f0[0] = __byte_perm(v.x, v.z, 0x5410); f0[1] = __byte_perm(v.x, v.z, 0x7632);
+    f1[0] = __byte_perm(v.y, v.w, 0x5410); f1[1] = __byte_perm(v.y, v.w, 0x7632);
+}
+
 struct AttnDev {
     AttnArgs a;
     int cluster;         // CTAs per (sequence, kv head)
@@ -136,6 +173,7 @@ struct AttnDev {
     int out_off;         // byte offset, inside a warp's region, of its rows of the CTA's reduced output
     int tile_shift, cbk_shift, cbv_shift;   // log2 of tile, cbk, cbv
     int nkb_shift, nvi_shift;               // log2 of K blocks per tile and of V blocks (2 halves x token blocks) per tile
+    FieldSpread klen, kmin, vlen, vmin;     // header field widths -> bytes
 };
 
 // CTA-shared block (cluster-visible)
@@ -176,9 +214,11 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
     CtaShared* cs = reinterpret_cast<CtaShared*>(smem + P.cta_off);
     // 32-bit shared-window addresses for the hot loops
     const unsigned wbase_a = smem_addr(wbase), xch_a = smem_addr(xch), vsz_a = smem_addr(vsz), stile_a = smem_addr(stile);
-    // K exchange: store address of this lane's 4 channel bytes for even / odd tokens; fragment rows g and g+8
-    const unsigned kst_even = xch_a + (((lane >> 2) << 4) | ((lane & 3) << 2)), kst_odd = xch_a + ((((lane >> 2) ^ 1) << 4) | ((lane & 3) << 2));
-    const unsigned kld0 = xch_a + g * 128 + (((2 * c) ^ (g & 1)) << 4), kld1 = xch_a + g * 128 + (((2 * c + 1) ^ (g & 1)) << 4);
+    // K exchange tile: one 16-byte row (16 tokens) per channel; channel 4*lane + i lives in row
+    // lane + 32*i, so the four row stores of a warp are contiguous and the 8x8 matrices that
+    // ldmatrix.trans turns into fragments (plane i, rows 8m..8m+7) are contiguous too.
+    const unsigned kst = xch_a + lane * 16;
+    const unsigned kldm = xch_a + (32 * (lane >> 3) + (lane & 7)) * 16;
     // V exchange: row = lane (channel), chunk swizzle by (row >> 1) & 3; fragment rows g, g+8, g+16, g+24 share that swizzle
     const unsigned vst = xch_a + lane * 64, vsw = ((lane >> 1) & 3) << 4;
     const unsigned vld = xch_a + g * 64 + ((c ^ ((g >> 1) & 3)) << 4);
@@ -240,15 +280,26 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
     int cur_phase = 0, cur_size = 0, nxt_phase = 0, nxt_size = 0;
     if (total_items > 0) issue(0, nxt_phase, nxt_size);
 
+    // unpack table: two 16-byte entries per pack length 0..4 (see unpack_pack)
+    __shared__ uint4 ulut[10];
+    if (threadIdx.x < 5) {
+        const unsigned L = threadIdx.x;
+        ulut[2 * L] = make_uint4(L == 4 ? 0xFFFFu : (1u << (4 * L)) - 1u, ((1u << (2 * L)) - 1u) * 0x00010001u, ((1u << L) - 1u) * 0x01010101u, 4 * L);
+        ulut[2 * L + 1] = make_uint4(16 - 2 * L, 8 - L, 8 * L, 0);
+    }
+    const unsigned ulut_a = smem_addr(ulut);
+    bool bad_len = false;
+    __syncthreads();
+
     // q fragments: column g of the n-tile is q head g
     unsigned qf[8][2];
     {
         const uint4* qp = reinterpret_cast<const uint4*>(
-            reinterpret_cast<const T*>(a.q) + ((int64_t)(b * q_heads + h * G + min(g, G - 1))) * kD + 32 * c);
+            reinterpret_cast<const T*>(a.q) + ((int64_t)(b * q_heads + h * G + min(g, G - 1))) * kD + 8 * c);
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            uint4 v = g < G ? __ldg(qp + i) : make_uint4(0, 0, 0, 0);
-            qf[2 * i][0] = v.x; qf[2 * i][1] = v.y; qf[2 * i + 1][0] = v.z; qf[2 * i + 1][1] = v.w;
+        for (int m = 0; m < 4; m++) {
+            const uint4 v = g < G ? __ldg(qp + 4 * m) : make_uint4(0, 0, 0, 0);
+            pair_shuffle(v, qf[2 * m], qf[2 * m + 1]);
         }
     }
 
@@ -278,16 +329,19 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
             // channel mode: per-(block, channel) scale and zero for this lane's 32 channels
             T2 ksc[8][2], kzb[8][2];
             if (KMODE == kKChannel) {
-                const int64_t row = ((int64_t)(b * a.kv_heads + h) * a.param_blocks + ((t0 >> P.cbk_shift) + i)) * kD + 32 * c;
+                const int64_t row = ((int64_t)(b * a.kv_heads + h) * a.param_blocks + ((t0 >> P.cbk_shift) + i)) * kD + 8 * c;
                 const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_scale) + row);
                 const uint4* zp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_zero) + row);
 #pragma unroll
-                for (int q4 = 0; q4 < 4; q4++) {
-                    uint4 sv = __ldg(sp + q4), zv = __ldg(zp + q4);
-                    ksc[2 * q4][0] = as_t2<T2>(sv.x); ksc[2 * q4][1] = as_t2<T2>(sv.y);
-                    ksc[2 * q4 + 1][0] = as_t2<T2>(sv.z); ksc[2 * q4 + 1][1] = as_t2<T2>(sv.w);
-                    kzb[2 * q4][0] = as_t2<T2>(zv.x); kzb[2 * q4][1] = as_t2<T2>(zv.y);
-                    kzb[2 * q4 + 1][0] = as_t2<T2>(zv.z); kzb[2 * q4 + 1][1] = as_t2<T2>(zv.w);
+                for (int m = 0; m < 4; m++) {
+                    const uint4 sv = __ldg(sp + 4 * m), zv = __ldg(zp + 4 * m);
+                    unsigned s0[2], s1[2], z0[2], z1[2];
+                    pair_shuffle(sv, s0, s1);
+                    pair_shuffle(zv, z0, z1);
+                    ksc[2 * m][0] = as_t2<T2>(s0[0]); ksc[2 * m][1] = as_t2<T2>(s0[1]);
+                    ksc[2 * m + 1][0] = as_t2<T2>(s1[0]); ksc[2 * m + 1][1] = as_t2<T2>(s1[1]);
+                    kzb[2 * m][0] = as_t2<T2>(z0[0]); kzb[2 * m][1] = as_t2<T2>(z0[1]);
+                    kzb[2 * m + 1][0] = as_t2<T2>(z1[0]); kzb[2 * m + 1][1] = as_t2<T2>(z1[1]);
                 }
                 if (!HP) {
 #pragma unroll
@@ -300,90 +354,68 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
                 const unsigned hdr = blk + pos;
                 const unsigned minword = lds_lane_field(hdr, lane, 4 * bits_k);
                 const unsigned lenword = lds_lane_field(hdr + 16 * bits_k, lane, 4 * lbk);
-                unsigned lens4 = 0, mins4 = 0;
-                int len[4];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    len[j] = min((int)((lenword >> (j * lbk)) & ((1u << lbk) - 1u)), 4);
-                    lens4 |= (unsigned)len[j] << (8 * j);
-                    mins4 |= ((minword >> (j * bits_k)) & ((1u << bits_k) - 1u)) << (8 * j);
-                }
+                unsigned lens4 = spread_fields(lenword, P.klen);          // byte j = length of pack j
+                const unsigned mins4 = spread_fields(minword, P.kmin);
+                if ((lens4 + 0x03030303u) & 0x08080808u) { lens4 = 0; bad_len = true; }   // no encoder writes a length above 4
                 const unsigned inc = warp_inclusive_sum(lens4);
                 const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
                 const unsigned exc = inc - lens4;
                 const unsigned packs = hdr + 16 * bits_k + 16 * lbk;
+                const unsigned lidx = lens4 << 5;                          // byte j = offset of the table entry
                 unsigned before = 0;
-                unsigned top[4], bot[4], msk[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     unsigned lo, hi;
-                    lds_u64_align2(packs + 2 * (before + ((exc >> (8 * j)) & 0xFFu)), lo, hi);
-                    before += (tot >> (8 * j)) & 0xFFu;
-                    // tokens 0..7 live in bits [8*len, 16*len): bring them to the low word
-                    const unsigned tp = __funnelshift_rc(lo, hi, 8 * len[j]);
-                    // rotate so that token 0 (bit offset 7*len) sits at byte j
-                    const int rot = (8 * j - 7 * len[j]) & 31;
-                    top[j] = __funnelshift_l(tp, tp, rot);
-                    bot[j] = __funnelshift_l(lo, lo, rot);
-                    msk[j] = ((1u << len[j]) - 1u) << (8 * j);
-                }
-                // 16 tokens: one u32 (4 channel bytes) each, stored to the exchange tile
-#pragma unroll
-                for (int t = 0; t < 16; t++) {
-                    unsigned u;
-                    if (t < 8) {
-                        u = (top[0] & msk[0]) | (top[1] & msk[1]) | (top[2] & msk[2]) | (top[3] & msk[3]);
-#pragma unroll
-                        for (int j = 0; j < 4; j++) top[j] = __funnelshift_l(top[j], top[j], len[j]);
-                    } else {
-                        u = (bot[0] & msk[0]) | (bot[1] & msk[1]) | (bot[2] & msk[2]) | (bot[3] & msk[3]);
-#pragma unroll
-                        for (int j = 0; j < 4; j++) bot[j] = __funnelshift_l(bot[j], bot[j], len[j]);
-                    }
-                    u += mins4;
-                    sts32(((t & 1) ? kst_odd : kst_even) + t * 128, u);
+                    lds_u64_align2(packs + 2 * (before + byte_of(exc, j)), lo, hi);
+                    before += byte_of(tot, j);
+                    const unsigned le = ulut_a + byte_of(lidx, j);
+                    const uint4 la = lds128(le), lb = lds128(le + 16);
+                    sts128(kst + 512 * j, unpack_pack(lo, hi, la, lb, __byte_perm(mins4, 0, 0x1111 * j)));
                 }
                 __syncwarp();
-                // A fragments: rows g and g+8, this lane's 32 channels (two 16-byte chunks each)
-                const uint4 ra0 = lds128(kld0), ra1 = lds128(kld1), rb0 = lds128(kld0 + 8 * 128), rb1 = lds128(kld1 + 8 * 128);
+                unsigned fr[4][4];
+#pragma unroll
+                for (int m = 0; m < 4; m++) ldmatrix_x4_trans(kldm + 128 * m, fr[m]);
                 __syncwarp();
-                const unsigned ua[8] = {ra0.x, ra0.y, ra0.z, ra0.w, ra1.x, ra1.y, ra1.z, ra1.w};
-                const unsigned ub[8] = {rb0.x, rb0.y, rb0.z, rb0.w, rb1.x, rb1.y, rb1.z, rb1.w};
-                const int tk = i * a.cbk + r * 16 + g;       // token (in the tile) of row g
+                // Lane (g, c) holds, per plane, channels (row 2c | row 2c+1) x tokens (2(g^1)+1 | 2(g^1)):
+                // fragment row g is token T0 = 2(g^1), row g+8 is token T0 + 1.
+                const int tk = i * a.cbk + r * 16 + 2 * (g ^ 1);
                 T2 sg, zg, sg8, zg8;                         // token mode: per-row scale / zero
                 if (KMODE == kKToken) {
-                    sg = Tr<T>::dup(ksz[tk]); zg = Tr<T>::dup(ksz[P.tile + tk]);
-                    sg8 = Tr<T>::dup(ksz[tk + 8]); zg8 = Tr<T>::dup(ksz[P.tile + tk + 8]);
+                    const unsigned sv = lds32(smem_addr(ksz) + 2 * tk), zv = lds32(smem_addr(ksz) + 2 * (P.tile + tk));
+                    sg = as_t2<T2>(__byte_perm(sv, sv, 0x1010)); sg8 = as_t2<T2>(__byte_perm(sv, sv, 0x3232));
+                    zg = as_t2<T2>(__byte_perm(zv, zv, 0x1010)); zg8 = as_t2<T2>(__byte_perm(zv, zv, 0x3232));
                 }
                 float accs[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // two chains hide the mma latency
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
+                    const unsigned u0 = fr[j >> 1][2 * (j & 1)], u1 = fr[j >> 1][2 * (j & 1) + 1];
+                    const unsigned a0 = __byte_perm(u0, Tr<T>::kMagic, 0x4341), a1 = __byte_perm(u0, Tr<T>::kMagic, 0x4240);
+                    const unsigned a2 = __byte_perm(u1, Tr<T>::kMagic, 0x4341), a3 = __byte_perm(u1, Tr<T>::kMagic, 0x4240);
                     unsigned af[4];
-                    const unsigned a_lo = __byte_perm(ua[j], Tr<T>::kMagic, 0x4140), a_hi = __byte_perm(ua[j], Tr<T>::kMagic, 0x4342);
-                    const unsigned b_lo = __byte_perm(ub[j], Tr<T>::kMagic, 0x4140), b_hi = __byte_perm(ub[j], Tr<T>::kMagic, 0x4342);
                     if (KMODE == kKChannel) {
-                        af[0] = deq2<T, HP>(a_lo, kzb[j][0], ksc[j][0]);
-                        af[1] = deq2<T, HP>(b_lo, kzb[j][0], ksc[j][0]);
-                        af[2] = deq2<T, HP>(a_hi, kzb[j][1], ksc[j][1]);
-                        af[3] = deq2<T, HP>(b_hi, kzb[j][1], ksc[j][1]);
+                        af[0] = deq2<T, HP>(a0, kzb[j][0], ksc[j][0]);
+                        af[1] = deq2<T, HP>(a1, kzb[j][0], ksc[j][0]);
+                        af[2] = deq2<T, HP>(a2, kzb[j][1], ksc[j][1]);
+                        af[3] = deq2<T, HP>(a3, kzb[j][1], ksc[j][1]);
                     } else {
-                        af[0] = deq2<T, HP>(a_lo, zg, sg);
-                        af[1] = deq2<T, HP>(b_lo, zg8, sg8);
-                        af[2] = deq2<T, HP>(a_hi, zg, sg);
-                        af[3] = deq2<T, HP>(b_hi, zg8, sg8);
+                        af[0] = deq2<T, HP>(a0, zg, sg);
+                        af[1] = deq2<T, HP>(a1, zg8, sg8);
+                        af[2] = deq2<T, HP>(a2, zg, sg);
+                        af[3] = deq2<T, HP>(a3, zg8, sg8);
                     }
                     Tr<T>::mma(accs[j & 1], af, qf[j][0], qf[j][1]);
                 }
-                const float acc[4] = {accs[0][0] + accs[1][0], accs[0][1] + accs[1][1], accs[0][2] + accs[1][2], accs[0][3] + accs[1][3]};
-                // scores rounded like the reference: matmul output, then * scaling
+                // scores rounded like the reference: matmul output, then * scaling; tokens T0, T0+1 share a store
                 if (col_live) {
-                    const unsigned row0 = st + (2 * c) * P.prow + 2 * tk, row1 = row0 + P.prow;
-                    const T s00 = Tr<T>::from_float(Tr<T>::round(acc[0]) * a.scaling), s01 = Tr<T>::from_float(Tr<T>::round(acc[1]) * a.scaling);
-                    const T s10 = Tr<T>::from_float(Tr<T>::round(acc[2]) * a.scaling), s11 = Tr<T>::from_float(Tr<T>::round(acc[3]) * a.scaling);
-                    sts16(row0, *reinterpret_cast<const unsigned short*>(&s00)); sts16(row1, *reinterpret_cast<const unsigned short*>(&s01));
-                    sts16(row0 + 16, *reinterpret_cast<const unsigned short*>(&s10)); sts16(row1 + 16, *reinterpret_cast<const unsigned short*>(&s11));
-                    mloc0 = fmaxf(mloc0, fmaxf(Tr<T>::to_float(s00), Tr<T>::to_float(s10)));
-                    mloc1 = fmaxf(mloc1, fmaxf(Tr<T>::to_float(s01), Tr<T>::to_float(s11)));
+                    const unsigned row0 = st + (2 * c) * P.prow + 2 * tk;
+                    const unsigned p0 = Tr<T>::pack2(Tr<T>::round(accs[0][0] + accs[1][0]) * a.scaling, Tr<T>::round(accs[0][2] + accs[1][2]) * a.scaling);
+                    const unsigned p1 = Tr<T>::pack2(Tr<T>::round(accs[0][1] + accs[1][1]) * a.scaling, Tr<T>::round(accs[0][3] + accs[1][3]) * a.scaling);
+                    sts32(row0, p0);
+                    sts32(row0 + P.prow, p1);
+                    const float2 f0 = Tr<T>::unpack2(p0), f1 = Tr<T>::unpack2(p1);
+                    mloc0 = fmaxf(mloc0, fmaxf(f0.x, f0.y));
+                    mloc1 = fmaxf(mloc1, fmaxf(f1.x, f1.y));
                 }
                 pos += 16 * bits_k + 16 * lbk + 2 * (int)before;
             }
@@ -393,24 +425,27 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
 
     // ---- residual tiles, phase 1: scores -------------------------------------------------------
     // A fragments come straight from the uncompressed rows: lane (g, c) reads channels
-    // 32c..32c+31 of tokens g and g+8, the same channel order as the q fragments.
+    // 32m + 8c .. +7 (m = 0..3) of tokens g and g+8 and pairs them in the order of the q fragments.
     const T* kres = reinterpret_cast<const T*>(a.k_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
     const T* vres = reinterpret_cast<const T*>(a.v_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
     for (int k = 0; k < my_rt; k++) {
         const int tok0 = (rslot + k * n_warps) << 4;
         const int ta = tok0 + g, tb = tok0 + g + 8;
-        const uint4* pa = reinterpret_cast<const uint4*>(kres + (int64_t)min(ta, a.n_res - 1) * kD + 32 * c);
-        const uint4* pb = reinterpret_cast<const uint4*>(kres + (int64_t)min(tb, a.n_res - 1) * kD + 32 * c);
+        const uint4* pa = reinterpret_cast<const uint4*>(kres + (int64_t)min(ta, a.n_res - 1) * kD + 8 * c);
+        const uint4* pb = reinterpret_cast<const uint4*>(kres + (int64_t)min(tb, a.n_res - 1) * kD + 8 * c);
         uint4 ra[4], rb[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) { ra[i] = __ldg(pa + i); rb[i] = __ldg(pb + i); }
+        for (int m = 0; m < 4; m++) { ra[m] = __ldg(pa + 4 * m); rb[m] = __ldg(pb + 4 * m); }
         float accs[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const unsigned f0[4] = {ra[i].x, rb[i].x, ra[i].y, rb[i].y};
-            const unsigned f1[4] = {ra[i].z, rb[i].z, ra[i].w, rb[i].w};
-            Tr<T>::mma(accs[0], f0, qf[2 * i][0], qf[2 * i][1]);
-            Tr<T>::mma(accs[1], f1, qf[2 * i + 1][0], qf[2 * i + 1][1]);
+        for (int m = 0; m < 4; m++) {
+            unsigned a0[2], a1[2], b0[2], b1[2];
+            pair_shuffle(ra[m], a0, a1);
+            pair_shuffle(rb[m], b0, b1);
+            const unsigned f0[4] = {a0[0], b0[0], a0[1], b0[1]};
+            const unsigned f1[4] = {a1[0], b1[0], a1[1], b1[1]};
+            Tr<T>::mma(accs[0], f0, qf[2 * m][0], qf[2 * m][1]);
+            Tr<T>::mma(accs[1], f1, qf[2 * m + 1][0], qf[2 * m + 1][1]);
         }
         if (col_live) {
             const float ninf = -INFINITY;
@@ -563,48 +598,24 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
                 const unsigned hdr = blk + pos;
                 const unsigned minword = lds_lane_field(hdr, lane, 4 * bits_v);
                 const unsigned lenword = lds_lane_field(hdr + 16 * bits_v, lane, 4 * lbv);
-                unsigned lens4 = 0;
-                int len[4];
-#pragma unroll
-                for (int q4 = 0; q4 < 4; q4++) {
-                    len[q4] = min((int)((lenword >> (q4 * lbv)) & ((1u << lbv) - 1u)), 4);
-                    lens4 |= (unsigned)len[q4] << (8 * q4);
-                }
+                unsigned lens4 = spread_fields(lenword, P.vlen);          // byte q = length of pack q (tokens 16q..16q+15)
+                const unsigned mins4 = spread_fields(minword, P.vmin);
+                if ((lens4 + 0x03030303u) & 0x08080808u) { lens4 = 0; bad_len = true; }
                 const unsigned inc = warp_inclusive_sum(lens4);
                 const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
                 const unsigned exc = inc - lens4;
                 const unsigned packs = hdr + 16 * bits_v + 16 * lbv;
+                const unsigned lidx = lens4 << 5;
                 unsigned before = 0;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; q4++) {
                     unsigned lo, hi;
-                    lds_u64_align2(packs + 2 * (before + ((exc >> (8 * q4)) & 0xFFu)), lo, hi);
-                    before += (tot >> (8 * q4)) & 0xFFu;
-                    const int ln = len[q4];
-                    const unsigned tp = __funnelshift_rc(lo, hi, 8 * ln);
-                    const unsigned mn4 = ((minword >> (q4 * bits_v)) & ((1u << bits_v) - 1u)) * 0x01010101u;
-                    const unsigned m1 = (1u << ln) - 1u;
-                    const unsigned m0 = m1, m8 = m1 << 8, m16 = m1 << 16, m24 = m1 << 24;
-                    // token i' of a word sits at bit len*(7-i'); its byte target is 8*(i'&3):
-                    // start with token 0 at byte 0, then rotate left by 8+len per token
-                    unsigned y = __funnelshift_l(tp, tp, (32 - 7 * ln) & 31);
-                    unsigned z = __funnelshift_l(lo, lo, (32 - 7 * ln) & 31);
-                    unsigned u[4];
-#pragma unroll
-                    for (int k = 0; k < 2; k++) {
-                        unsigned v0 = y & m0; y = __funnelshift_l(y, y, 8 + ln);
-                        v0 |= y & m8; y = __funnelshift_l(y, y, 8 + ln);
-                        v0 |= y & m16; y = __funnelshift_l(y, y, 8 + ln);
-                        v0 |= y & m24; y = __funnelshift_l(y, y, 8 + ln);
-                        u[k] = v0 + mn4;
-                        unsigned v1 = z & m0; z = __funnelshift_l(z, z, 8 + ln);
-                        v1 |= z & m8; z = __funnelshift_l(z, z, 8 + ln);
-                        v1 |= z & m16; z = __funnelshift_l(z, z, 8 + ln);
-                        v1 |= z & m24; z = __funnelshift_l(z, z, 8 + ln);
-                        u[2 + k] = v1 + mn4;
-                    }
-                    // row = lane (channel), logical 16-byte chunk q4, swizzled
-                    sts128(vst + ((q4 << 4) ^ vsw), make_uint4(u[0], u[1], u[2], u[3]));
+                    lds_u64_align2(packs + 2 * (before + byte_of(exc, q4)), lo, hi);
+                    before += byte_of(tot, q4);
+                    const unsigned le = ulut_a + byte_of(lidx, q4);
+                    const uint4 la = lds128(le), lb = lds128(le + 16);
+                    // row = lane (channel), logical 16-byte chunk q4, swizzled; byte p of the chunk is token 16*q4 + (p ^ 3)
+                    sts128(vst + ((q4 << 4) ^ vsw), unpack_pack(lo, hi, la, lb, __byte_perm(mins4, 0, 0x1111 * q4)));
                 }
                 __syncwarp();
                 // per-token scale / zero pairs and probabilities for tokens tok_seg + 16c .. +15
@@ -630,10 +641,11 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
                     const unsigned ub[4] = {xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        afr[mt][j][0] = deq2<T, HP>(__byte_perm(ua[j], Tr<T>::kMagic, 0x4140), as_t2<T2>(vZ[2 * j]), as_t2<T2>(vS[2 * j]));
-                        afr[mt][j][1] = deq2<T, HP>(__byte_perm(ub[j], Tr<T>::kMagic, 0x4140), as_t2<T2>(vZ[2 * j]), as_t2<T2>(vS[2 * j]));
-                        afr[mt][j][2] = deq2<T, HP>(__byte_perm(ua[j], Tr<T>::kMagic, 0x4342), as_t2<T2>(vZ[2 * j + 1]), as_t2<T2>(vS[2 * j + 1]));
-                        afr[mt][j][3] = deq2<T, HP>(__byte_perm(ub[j], Tr<T>::kMagic, 0x4342), as_t2<T2>(vZ[2 * j + 1]), as_t2<T2>(vS[2 * j + 1]));
+                        // bytes of a word are tokens 4j+3, 4j+2, 4j+1, 4j
+                        afr[mt][j][0] = deq2<T, HP>(__byte_perm(ua[j], Tr<T>::kMagic, 0x4243), as_t2<T2>(vZ[2 * j]), as_t2<T2>(vS[2 * j]));
+                        afr[mt][j][1] = deq2<T, HP>(__byte_perm(ub[j], Tr<T>::kMagic, 0x4243), as_t2<T2>(vZ[2 * j]), as_t2<T2>(vS[2 * j]));
+                        afr[mt][j][2] = deq2<T, HP>(__byte_perm(ua[j], Tr<T>::kMagic, 0x4041), as_t2<T2>(vZ[2 * j + 1]), as_t2<T2>(vS[2 * j + 1]));
+                        afr[mt][j][3] = deq2<T, HP>(__byte_perm(ub[j], Tr<T>::kMagic, 0x4041), as_t2<T2>(vZ[2 * j + 1]), as_t2<T2>(vS[2 * j + 1]));
                     }
                 }
                 const int sel = 2 * hh + w;
@@ -654,6 +666,7 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
     }
     cp_async_wait<0>();
     __syncwarp();
+    if (__any_sync(0xffffffffu, bad_len) && lane == 0) atomicOr(a.flags, kFlagBadStream);
 
     // ---- residual tiles, phase 2: probabilities x V ---------------------------------------------
     // The tile's 16 V rows are staged (padded to 272 bytes so that ldmatrix is conflict free) in the
@@ -793,6 +806,10 @@ int launch_attention(const AttnArgs& a, cudaStream_t st) {
     P.cbv_shift = a.n_comp > 0 ? lg2(a.cbv) : 6;
     P.nkb_shift = P.tile_shift - P.cbk_shift;
     P.nvi_shift = P.tile_shift - P.cbv_shift + 1;
+    if (a.n_comp > 0) {
+        P.klen = make_field_spread(len_field_bits(a.bits_k)); P.kmin = make_field_spread(a.bits_k);
+        P.vlen = make_field_spread(len_field_bits(a.bits_v)); P.vmin = make_field_spread(a.bits_v);
+    }
     // cluster size: enough CTAs for ~2 waves of the 148 SMs (3 CTAs each), but at least one
     // tile per warp; a long sequence must also fit its scores in shared memory
     const long pairs = (long)a.batch * a.kv_heads;
