@@ -242,27 +242,56 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
 
     // ---- stream-block fetch ---------------------------------------------------------------------
     // item n < k_items: K block (n % nkb) of local tile n / nkb; else V block of local tile
-    auto issue = [&](int n, int& phase_out, int& size_out) {
-        const uint8_t* base;
+    // (offset, size) of item n's block; loaded one item ahead of the copy that needs it
+    auto load_info = [&](int n) -> uint2 {
         const uint32_t* info;
-        int64_t cap;
-        int bound;
         if (n < k_items) {
             const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
             const int t0 = (gw + tl * n_warps) << P.tile_shift;
             info = kinfo + ((int64_t)((t0 >> P.cbk_shift) + i) * a.kv_heads + h) * 2;
-            base = kbase; cap = a.k_capacity;
-            bound = 2 * k_rounds + k_rounds * (16 * a.bits_k + 16 * lbk + 256 * a.bits_k);
         } else {
             const int m = n - k_items;
             const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
             const int t0 = (gw + tl * n_warps) << P.tile_shift;
             info = vinfo + ((int64_t)((t0 >> P.cbv_shift) + (vi >> 1)) * (2 * a.kv_heads) + 2 * h + (vi & 1)) * 2;
+        }
+        return __ldg(reinterpret_cast<const uint2*>(info));
+    };
+    // Starts the copy of item n's block into its staging slot, together with the quantisation
+    // parameters the item needs: channel-mode K: the block's 128 scales and 128 zero-points
+    // (512 bytes at vsz, free during phase 1); first V block of a tile: the tile's per-token
+    // scales and zero-points into parameter buffer (tile & 1) (vsz / ksz, both free in phase 2).
+    auto issue = [&](int n, uint2 inf, int& phase_out, int& size_out) {
+        const uint8_t* base;
+        int64_t cap;
+        int bound;
+        if (n < k_items) {
+            base = kbase; cap = a.k_capacity;
+            bound = 2 * k_rounds + k_rounds * (16 * a.bits_k + 16 * lbk + 256 * a.bits_k);
+            if (KMODE == kKChannel) {
+                const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
+                const int t0 = (gw + tl * n_warps) << P.tile_shift;
+                const int64_t row = ((int64_t)(b * a.kv_heads + h) * a.param_blocks + ((t0 >> P.cbk_shift) + i)) * kD;
+                const T* src = reinterpret_cast<const T*>(lane < 16 ? a.k_scale : a.k_zero) + row + 8 * (lane & 15);
+                cp_async16(reinterpret_cast<uint8_t*>(vsz) + 16 * lane, reinterpret_cast<const uint8_t*>(src));
+            }
+        } else {
+            const int m = n - k_items;
+            const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
             base = vbase; cap = a.v_capacity;
             const int nseg = a.cbv == 128 ? 4 : 2;
             bound = 2 * nseg + nseg * (16 * a.bits_v + 16 * lbv + 256 * a.bits_v);
+            if (vi == 0) {
+                const int t0 = (gw + tl * n_warps) << P.tile_shift;
+                const int chunks = P.tile >> 3;              // 16-byte chunks per parameter array
+                if (lane < 2 * chunks) {
+                    const T* src = reinterpret_cast<const T*>(lane < chunks ? a.v_scale : a.v_zero) + (int64_t)b * a.param_tokens + t0 +
+                                   8 * (lane < chunks ? lane : lane - chunks);
+                    cp_async16(reinterpret_cast<uint8_t*>(vsz) + (tl & 1) * 4 * P.tile + 16 * lane, reinterpret_cast<const uint8_t*>(src));
+                }
+            }
         }
-        const unsigned off = __ldg(info), size = __ldg(info + 1);
+        const unsigned off = inf.x, size = inf.y;
         uint8_t* dst = wbase + (n & 1) * P.slot;
         if ((int64_t)off + size > cap || (int)size > bound || size < 4) {
             if (lane == 0) atomicOr(a.flags, kFlagBadStream);
@@ -278,7 +307,9 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
     };
 
     int cur_phase = 0, cur_size = 0, nxt_phase = 0, nxt_size = 0;
-    if (total_items > 0) issue(0, nxt_phase, nxt_size);
+    uint2 inf = make_uint2(0, 0);
+    if (total_items > 0) issue(0, load_info(0), nxt_phase, nxt_size);
+    if (total_items > 1) inf = load_info(1);
 
     // unpack table: two 16-byte entries per pack length 0..4 (see unpack_pack)
     __shared__ uint4 ulut[10];
@@ -308,9 +339,32 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
     // ============================================================================ phase 1: K tiles
     for (int n = 0; n < k_items; n++) {
         cur_phase = nxt_phase; cur_size = nxt_size;
-        if (n + 1 < total_items) issue(n + 1, nxt_phase, nxt_size); else cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<0>();
         __syncwarp();
+        // channel mode: per-(block, channel) scale and zero of this lane's channels, in mma order
+        T2 ksc[8][2], kzb[8][2];
+        if (KMODE == kKChannel) {
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                const uint4 sv = lds128(vsz_a + 64 * m + 16 * c), zv = lds128(vsz_a + 256 + 64 * m + 16 * c);
+                unsigned s0[2], s1[2], z0[2], z1[2];
+                pair_shuffle(sv, s0, s1);
+                pair_shuffle(zv, z0, z1);
+                ksc[2 * m][0] = as_t2<T2>(s0[0]); ksc[2 * m][1] = as_t2<T2>(s0[1]);
+                ksc[2 * m + 1][0] = as_t2<T2>(s1[0]); ksc[2 * m + 1][1] = as_t2<T2>(s1[1]);
+                kzb[2 * m][0] = as_t2<T2>(z0[0]); kzb[2 * m][1] = as_t2<T2>(z0[1]);
+                kzb[2 * m + 1][0] = as_t2<T2>(z1[0]); kzb[2 * m + 1][1] = as_t2<T2>(z1[1]);
+            }
+            if (!HP) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) { kzb[j][0] = __hsub2(kzb[j][0], bias2); kzb[j][1] = __hsub2(kzb[j][1], bias2); }
+            }
+            __syncwarp();                              // every lane has its parameters before the next copy lands
+        }
+        if (n + 1 < total_items) {
+            issue(n + 1, inf, nxt_phase, nxt_size);
+            if (n + 2 < total_items) inf = load_info(n + 2);
+        }
         const unsigned blk = wbase_a + (n & 1) * P.slot + cur_phase;
         const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
         const int t0 = (gw + tl * n_warps) << P.tile_shift;
@@ -326,28 +380,6 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
             __syncwarp();
         }
         if (cur_size > 0) {
-            // channel mode: per-(block, channel) scale and zero for this lane's 32 channels
-            T2 ksc[8][2], kzb[8][2];
-            if (KMODE == kKChannel) {
-                const int64_t row = ((int64_t)(b * a.kv_heads + h) * a.param_blocks + ((t0 >> P.cbk_shift) + i)) * kD + 8 * c;
-                const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_scale) + row);
-                const uint4* zp = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.k_zero) + row);
-#pragma unroll
-                for (int m = 0; m < 4; m++) {
-                    const uint4 sv = __ldg(sp + 4 * m), zv = __ldg(zp + 4 * m);
-                    unsigned s0[2], s1[2], z0[2], z1[2];
-                    pair_shuffle(sv, s0, s1);
-                    pair_shuffle(zv, z0, z1);
-                    ksc[2 * m][0] = as_t2<T2>(s0[0]); ksc[2 * m][1] = as_t2<T2>(s0[1]);
-                    ksc[2 * m + 1][0] = as_t2<T2>(s1[0]); ksc[2 * m + 1][1] = as_t2<T2>(s1[1]);
-                    kzb[2 * m][0] = as_t2<T2>(z0[0]); kzb[2 * m][1] = as_t2<T2>(z0[1]);
-                    kzb[2 * m + 1][0] = as_t2<T2>(z1[0]); kzb[2 * m + 1][1] = as_t2<T2>(z1[1]);
-                }
-                if (!HP) {
-#pragma unroll
-                    for (int j = 0; j < 8; j++) { kzb[j][0] = __hsub2(kzb[j][0], bias2); kzb[j][1] = __hsub2(kzb[j][1], bias2); }
-                }
-            }
             const int bits_k = a.bits_k;
             int pos = 2 * k_rounds;
             for (int r = 0; r < k_rounds; r++) {
@@ -555,13 +587,15 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
 
     for (int n = k_items; n < total_items; n++) {
         cur_phase = nxt_phase; cur_size = nxt_size;
-        if (n + 1 < total_items) issue(n + 1, nxt_phase, nxt_size); else cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<0>();
         __syncwarp();
+        if (n + 1 < total_items) {
+            issue(n + 1, inf, nxt_phase, nxt_size);
+            if (n + 2 < total_items) inf = load_info(n + 2);
+        }
         const unsigned blk = wbase_a + (n & 1) * P.slot + cur_phase;
         const int m = n - k_items;
         const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
-        const int t0 = (gw + tl * n_warps) << P.tile_shift;
         const unsigned st_a = stile_a + tl * P.rows * P.prow;
 
         if (vi == 0) {
@@ -576,12 +610,6 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
                         sts32(ad, Tr<T>::pack2(fast_exp(x.x - M) * I, fast_exp(x.y - M) * I));
                     }
                 }
-            }
-            const T* vs = reinterpret_cast<const T*>(a.v_scale) + (int64_t)b * a.param_tokens + t0;
-            const T* vz = reinterpret_cast<const T*>(a.v_zero) + (int64_t)b * a.param_tokens + t0;
-            for (int t = lane; t < P.tile; t += 32) {
-                vsz[t] = vs[t];
-                vsz[P.tile + t] = HP ? vz[t] : Tr<T>::from_float(Tr<T>::to_float(vz[t]) - Tr<T>::kBias);
             }
             __syncwarp();
         }
@@ -620,15 +648,20 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
                 __syncwarp();
                 // per-token scale / zero pairs and probabilities for tokens tok_seg + 16c .. +15
                 const unsigned tok2 = 2 * (tok_seg + 16 * c);      // byte offset of this lane's 16 tokens in a row of halves
-                const uint4 s0 = lds128(vsz_a + tok2), s1 = lds128(vsz_a + tok2 + 16);
-                const uint4 z0 = lds128(vsz_a + 2 * P.tile + tok2), z1 = lds128(vsz_a + 2 * P.tile + tok2 + 16);
+                const unsigned vpar = vsz_a + (tl & 1) * 4 * P.tile + tok2;   // this tile's parameter buffer
+                const uint4 s0 = lds128(vpar), s1 = lds128(vpar + 16);
+                const uint4 z0 = lds128(vpar + 2 * P.tile), z1 = lds128(vpar + 2 * P.tile + 16);
                 uint4 p0 = make_uint4(0, 0, 0, 0), p1 = make_uint4(0, 0, 0, 0);
                 if (g < P.rows) {
                     p0 = lds128(st_a + g * P.prow + tok2);
                     p1 = lds128(st_a + g * P.prow + tok2 + 16);
                 }
                 const unsigned vS[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-                const unsigned vZ[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+                unsigned vZ[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+                if (!HP) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) vZ[j] = as_u(__hsub2(as_t2<T2>(vZ[j]), bias2));
+                }
                 const unsigned pf[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
                 // A fragments for both 16-channel row tiles, then the contraction into the
                 // accumulator group of this (64-channel half, warp half): static register
@@ -788,6 +821,8 @@ int launch_attention(const AttnArgs& a, cudaStream_t st) {
             (a.v_seq_stride & 15) || (a.k_capacity & 15) || (a.v_capacity & 15))
             return kBadArgument;
         if ((reinterpret_cast<uintptr_t>(a.k_scale) & 15) || (reinterpret_cast<uintptr_t>(a.k_zero) & 15)) return kBadArgument;
+        if ((reinterpret_cast<uintptr_t>(a.v_scale) & 15) || (reinterpret_cast<uintptr_t>(a.v_zero) & 15) || (a.param_tokens & 7)) return kBadArgument;
+        if ((reinterpret_cast<uintptr_t>(a.k_info) & 7) || (reinterpret_cast<uintptr_t>(a.v_info) & 7)) return kBadArgument;
     }
     if (a.n_res > 0) {
         if (!a.k_res || !a.v_res) return kBadArgument;
