@@ -108,6 +108,74 @@ __device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const Qua
     return pos;
 }
 
+// The same rounds for blocks whose four quantisers are packable(): two channels per instruction
+// from the conversion to the pack minimum / maximum (16-bit lanes), then one multiply-add per code
+// into the pack words.
+template <typename T, int BITS>
+__device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, const Quantiser<T, false>& q0, const Quantiser<T, false>& q1,
+                                                      const Quantiser<T, false>& q2, const Quantiser<T, false>& q3, const KGeom& g,
+                                                      uint8_t* stage, int lane, bool& bad) {
+    constexpr int LB = len_field_bits(BITS);
+    const unsigned k01 = packed_code_bias(q0, q1), k23 = packed_code_bias(q2, q3);
+    int pos = g.head_bytes;
+    unsigned round_end = 0, over = 0;
+    for (int r = 0; r < g.rounds; r++) {
+        unsigned c01[16], c23[16];
+        unsigned mn01 = 0xFFFFFFFFu, mx01 = 0u, mn23 = 0xFFFFFFFFu, mx23 = 0u;
+#pragma unroll
+        for (int t = 0; t < 16; t++) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)(r * 16 + t) * ss));
+            c01[t] = packed_codes<T>(raw.x, q0, q1, k01);
+            c23[t] = packed_codes<T>(raw.y, q2, q3, k23);
+            mn01 = min_u16x2(mn01, c01[t]); mx01 = max_u16x2(mx01, c01[t]);
+            mn23 = min_u16x2(mn23, c23[t]); mx23 = max_u16x2(mx23, c23[t]);
+        }
+        over |= mx01 | mx23;
+        const unsigned mnj[4] = {mn01 & 0xFFFFu, mn01 >> 16, mn23 & 0xFFFFu, mn23 >> 16};
+        const unsigned d01 = mx01 - mn01, d23 = mx23 - mn23;     // lane-wise: no borrow, max >= min
+        const unsigned dj[4] = {d01 & 0xFFFFu, d01 >> 16, d23 & 0xFFFFu, d23 >> 16};
+        unsigned minword = 0, lenword = 0, lens4 = 0;
+        int len[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            len[j] = min(bit_length_u32(dj[j]), BITS);
+            minword |= (mnj[j] & ((1u << BITS) - 1u)) << (j * BITS);
+            lenword |= (unsigned)len[j] << (j * LB);
+            lens4 |= (unsigned)len[j] << (8 * j);
+        }
+        store_lane_fields(stage + pos, lane, 4 * BITS, minword);
+        store_lane_fields(stage + pos + g.min_bytes, lane, 4 * LB, lenword);
+        const unsigned inc = warp_inclusive_sum(lens4);
+        const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+        const unsigned exc = inc - lens4;
+        uint8_t* packs = stage + pos + g.min_bytes + g.len_bytes;
+        unsigned before = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const unsigned step = 1u << len[j];
+            unsigned wt = 0, wb = 0, ones = 0;
+#pragma unroll
+            for (int t = 0; t < 8; t++) {
+                const unsigned ct = j < 2 ? c01[t] : c23[t], cb = j < 2 ? c01[t + 8] : c23[t + 8];
+                wt = wt * step + ((j & 1) ? ct >> 16 : ct & 0xFFFFu);
+                wb = wb * step + ((j & 1) ? cb >> 16 : cb & 0xFFFFu);
+                ones = ones * step + 1u;
+            }
+            wt -= mnj[j] * ones;
+            wb -= mnj[j] * ones;
+            const uint64_t w = ((uint64_t)wt << (8 * len[j])) | wb;
+            store_pack_smem(packs + 2 * (before + ((exc >> (8 * j)) & 0xFFu)), w, len[j]);
+            before += (tot >> (8 * j)) & 0xFFu;
+        }
+        const unsigned round_size = g.min_bytes + g.len_bytes + 2 * before;
+        round_end += round_size;
+        if (lane == 0) *reinterpret_cast<uint16_t*>(stage + 2 * r) = (uint16_t)round_end;
+        pos += round_size;
+    }
+    bad = bad || (over & ~(((1u << BITS) - 1u) * 0x00010001u)) != 0;
+    return pos;
+}
+
 // one warp per K block (cb tokens x 128 channels of one head); lane owns channels 4l..4l+3, the
 // same ownership as the stream format, so per-channel statistics need no cross-lane step.
 template <typename T, bool HP, int BITS>
@@ -148,9 +216,10 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
         *reinterpret_cast<uint2*>(reinterpret_cast<T*>(a.zero) + pi) = *reinterpret_cast<const uint2*>(zr);
     }
     bool bad = q0.degenerate() || q1.degenerate() || q2.degenerate() || q3.degenerate();
-    const bool all_fast = __all_sync(0xffffffffu, q0.fast && q1.fast && q2.fast && q3.fast);
-    const int pos = all_fast ? k_encode_rounds<T, HP, BITS, true>(x, a.ss, q0, q1, q2, q3, g, stage, lane, bad)
-                             : k_encode_rounds<T, HP, BITS, false>(x, a.ss, q0, q1, q2, q3, g, stage, lane, bad);
+    const bool packable = __all_sync(0xffffffffu, q0.packable() && q1.packable() && q2.packable() && q3.packable());
+    int pos;
+    if (!HP && packable) pos = k_encode_rounds_packed<T, BITS>(x, a.ss, q0, q1, q2, q3, g, stage, lane, bad);
+    else pos = k_encode_rounds<T, HP, BITS, false>(x, a.ss, q0, q1, q2, q3, g, stage, lane, bad);
     __syncwarp();
     store_slot(a.slots + (int64_t)warp * a.slot_stride, stage, pos, lane);
     if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * a.heads + h) * 2 + 1] = (unsigned)pos;

@@ -19,6 +19,16 @@ template <> struct QT<__half> {
     static __device__ __forceinline__ T2 init2(float v) { return __float2half2_rn(v); }
     static __device__ __forceinline__ float lo_f(T2 a) { return __low2float(a); }
     static __device__ __forceinline__ float hi_f(T2 a) { return __high2float(a); }
+    // Packed round-to-integer: adding 1536 to a value in [-512, 512) leaves a result in [1024, 2048),
+    // where one ulp is 1, so the addition itself rounds half to even and the integer sits in the low
+    // mantissa bits: bits = 0x6600 + round(q).
+    static constexpr unsigned kIntBits = 0x6600u;
+    static constexpr float kIntZeroLimit = 480.f;        // |zero| + 16 must stay below 512
+    static __device__ __forceinline__ float2 to_float2(unsigned v) { return __half22float2(*reinterpret_cast<const __half2*>(&v)); }
+    static __device__ __forceinline__ unsigned round2_bits(float a, float b) {
+        const __half2 m = __hadd2(__floats2half2_rn(a, b), __float2half2_rn(1536.f));
+        return *reinterpret_cast<const unsigned*>(&m);
+    }
 };
 template <> struct QT<__nv_bfloat16> {
     static __device__ __forceinline__ float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
@@ -31,7 +41,26 @@ template <> struct QT<__nv_bfloat16> {
     static __device__ __forceinline__ T2 init2(float v) { return __float2bfloat162_rn(v); }
     static __device__ __forceinline__ float lo_f(T2 a) { return __low2float(a); }
     static __device__ __forceinline__ float hi_f(T2 a) { return __high2float(a); }
+    // as above with 192 and [-64, 64): bits = 0x4340 + round(q)
+    static constexpr unsigned kIntBits = 0x4340u;
+    static constexpr float kIntZeroLimit = 40.f;
+    static __device__ __forceinline__ float2 to_float2(unsigned v) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v)); }
+    static __device__ __forceinline__ unsigned round2_bits(float a, float b) {
+        const __nv_bfloat162 m = __hadd2(__floats2bfloat162_rn(a, b), __float2bfloat162_rn(192.f));
+        return *reinterpret_cast<const unsigned*>(&m);
+    }
 };
+
+__device__ __forceinline__ unsigned min_u16x2(unsigned a, unsigned b) {
+    unsigned d;
+    asm("min.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ unsigned max_u16x2(unsigned a, unsigned b) {
+    unsigned d;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
 
 // Quotient x / scale as PyTorch's half/bfloat16 kernels produce it (fp32 division, then rounding
 // to the element type) at a fraction of the cost of an IEEE division per element: with the
@@ -81,9 +110,24 @@ struct Quantiser {
         const int q = HP ? QT<T>::rnd_to_int(quotient_t<FAST>(QT<T>::rnd(x - zero))) : QT<T>::rnd_to_int(quotient_t<FAST>(x)) - zero_i;
         return min((unsigned)q, 255u);
     }
+    // the packed two-element path needs the fast quotient and a zero-point small enough for the
+    // packed round-to-integer (QT<T>::round2_bits)
+    __device__ __forceinline__ bool packable() const { return fast && fabsf(zero) <= QT<T>::kIntZeroLimit; }
     // parameters that cannot produce valid codes (constant channel: scale 0, or NaN / inf input)
     __device__ __forceinline__ bool degenerate() const { return !(scale > 0.f) || !(fabsf(zero) < 3.0e4f) || !(scale < 3.0e38f); }
 };
+
+// Codes of two elements (the two halves of `pair`, quantised by qa and qb) as two 16-bit lanes;
+// kab = packed_code_bias(qa, qb).  Requires qa.packable() && qb.packable().
+template <typename T>
+__device__ __forceinline__ unsigned packed_code_bias(const Quantiser<T, false>& qa, const Quantiser<T, false>& qb) {
+    return (QT<T>::kIntBits + (unsigned)(int)qa.zero) | ((QT<T>::kIntBits + (unsigned)(int)qb.zero) << 16);
+}
+template <typename T>
+__device__ __forceinline__ unsigned packed_codes(unsigned pair, const Quantiser<T, false>& qa, const Quantiser<T, false>& qb, unsigned kab) {
+    const float2 f = QT<T>::to_float2(pair);
+    return QT<T>::round2_bits(qa.template quotient_t<true>(f.x), qb.template quotient_t<true>(f.y)) - kab;
+}
 
 __device__ __forceinline__ unsigned code_byte(float c, float limit, bool& bad) {
     if (!(c >= 0.f && c < limit)) { bad = true; return 0u; }
