@@ -178,8 +178,12 @@ __device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, co
 
 // one warp per K block (cb tokens x 128 channels of one head); lane owns channels 4l..4l+3, the
 // same ownership as the stream format, so per-channel statistics need no cross-lane step.
-template <typename T, bool HP, int BITS>
+// CONTIG: token rows are 128 elements apart (a contiguous (B, H, S, 128) tensor), so every load of a
+// round is the block pointer plus a constant
+template <typename T, bool CONTIG, int BITS>
 __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(FusedArgs a) {
+    constexpr bool HP = false;
+    const int64_t ss = CONTIG ? 128 : a.ss;
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int LB = len_field_bits(BITS);
     const int lane = lane_id(), wic = threadIdx.x >> 5;
@@ -193,14 +197,15 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
     const KGeom g(a.cb, BITS);
     const int slot_smem = (g.head_bytes + g.rounds * (g.min_bytes + g.len_bytes + 128 * 2 * BITS) + 15) & ~15;
     uint8_t* stage = smem + wic * slot_smem;
-    const T* x = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)h * a.sh + (int64_t)cbi * a.cb * a.ss + 4 * lane;
+    const T* x = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)h * a.sh + (int64_t)cbi * a.cb * ss + 4 * lane;
 
     // per-channel min / max over the block, two channels per instruction in the element type
     // (min/max of element-type values is exact, so the fp32 detour is not needed here)
     using T2 = typename QT<T>::T2;
     T2 lo01 = QT<T>::init2(INFINITY), lo23 = lo01, hi01 = QT<T>::init2(-INFINITY), hi23 = hi01;
+#pragma unroll 8
     for (int t = 0; t < a.cb; t++) {
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)t * a.ss));
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)t * ss));
         const T2 v01 = *reinterpret_cast<const T2*>(&raw.x), v23 = *reinterpret_cast<const T2*>(&raw.y);
         lo01 = QT<T>::min2(lo01, v01); hi01 = QT<T>::max2(hi01, v01);
         lo23 = QT<T>::min2(lo23, v23); hi23 = QT<T>::max2(hi23, v23);
@@ -218,8 +223,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
     bool bad = q0.degenerate() || q1.degenerate() || q2.degenerate() || q3.degenerate();
     const bool packable = __all_sync(0xffffffffu, q0.packable() && q1.packable() && q2.packable() && q3.packable());
     int pos;
-    if (!HP && packable) pos = k_encode_rounds_packed<T, BITS>(x, a.ss, q0, q1, q2, q3, g, stage, lane, bad);
-    else pos = k_encode_rounds<T, HP, BITS, false>(x, a.ss, q0, q1, q2, q3, g, stage, lane, bad);
+    if (!HP && packable) pos = k_encode_rounds_packed<T, BITS>(x, ss, q0, q1, q2, q3, g, stage, lane, bad);
+    else pos = k_encode_rounds<T, HP, BITS, false>(x, ss, q0, q1, q2, q3, g, stage, lane, bad);
     __syncwarp();
     store_slot(a.slots + (int64_t)warp * a.slot_stride, stage, pos, lane);
     if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * a.heads + h) * 2 + 1] = (unsigned)pos;
@@ -232,27 +237,70 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
 // quantised as they are loaded (8 channels of one token per lane, so the token's parameters are
 // fetched once per 8 elements) into a uint8 tile in shared memory, from which the lane <-> channel
 // packing reads its columns.
-template <typename T, bool HP, int BITS, bool FAST>
-__device__ __forceinline__ void v_quantise_tile(const T* src, int64_t ss, int cb, const float4* prm, uint8_t* ctile, int lane) {
-    for (int r = lane >> 3; r < cb; r += 4) {          // 8 lanes x 16 B per 128-byte row
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)r * ss + 8 * (lane & 7)));
-        const float4 pr = prm[r];                       // scale, zero, 1/scale
-        Quantiser<T, HP> qz;
-        qz.scale = pr.x; qz.zero = pr.y; qz.rcp = pr.z;
-        const int zi = (int)pr.y;
-        const T* e = reinterpret_cast<const T*>(&raw);
-        unsigned w0 = 0, w1 = 0;
+// Tile of one V block in shared memory, transposed for the packing stage: one row of CB bytes per
+// channel, made of 16-byte chunks (one per pack); chunk p of channel ch is stored at chunk position
+// p ^ v_swz(ch) so that both the word stores of the quantising stage and the 16-byte row reads of the
+// packing stage spread over the banks.  Inside a chunk, byte 4*r0 + k holds token r0 + 4*k of the
+// pack: the quantising lane with r0 = lane >> 3 owns those four tokens.
+template <int CB>
+__device__ __forceinline__ int v_swz(int ch) { return ((ch >> 1) ^ (ch >> 3)) & (CB / 16 - 1); }
+
+// Quantises one V block into the tile.  Lane (r0 = lane >> 3, cg = lane & 7) loads 8 channels
+// (16 bytes) of tokens r0, r0+4, r0+8, ... and, per pack, turns its 4 tokens x 8 channels into one
+// 4-token word per channel.  PACKED: two channels per instruction (all tokens packable()).
+// Returns the OR of all codes in 16-bit lanes for the range check.
+template <typename T, int CB, bool PACKED>
+__device__ __forceinline__ unsigned v_quantise_tile(const T* src, int64_t ss, const float4* prm, uint8_t* tile, int lane) {
+    const int r0 = lane >> 3, cg = lane & 7;
+    unsigned seen = 0;
+    uint8_t* wr[4];                                        // row of channel 8cg + 2i at this lane's word, before the chunk swizzle
+    int sw[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            w0 |= qz.template code_u8<FAST>(QT<T>::ld(e + j), zi) << (8 * j);
-            w1 |= qz.template code_u8<FAST>(QT<T>::ld(e + 4 + j), zi) << (8 * j);
-        }
-        *reinterpret_cast<uint2*>(ctile + r * 64 + 8 * (lane & 7)) = make_uint2(w0, w1);
+    for (int i = 0; i < 4; i++) {
+        wr[i] = tile + (8 * cg + 2 * i) * CB + 4 * r0;
+        sw[i] = v_swz<CB>(8 * cg + 2 * i) << 4;           // channels 8cg + 2i and + 1 share the swizzle
     }
+    const T* lsrc = src + (int64_t)r0 * ss + 8 * cg;
+#pragma unroll 1
+    for (int p = 0; p < CB / 16; p++) {
+        unsigned c[4][4];                                  // [token k][channel pair i] as 16-bit lanes
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int tok = 16 * p + 4 * k + r0;
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(lsrc + (int64_t)(16 * p + 4 * k) * ss));
+            const float4 pr = prm[tok];                    // scale, zero, 1/scale
+            Quantiser<T, false> qz;
+            qz.scale = pr.x; qz.zero = pr.y; qz.rcp = pr.z;
+            const unsigned rw[4] = {raw.x, raw.y, raw.z, raw.w};
+            if (PACKED) {
+                const unsigned kab = __float_as_uint(pr.w);
+#pragma unroll
+                for (int i = 0; i < 4; i++) c[k][i] = packed_codes<T>(rw[i], qz, qz, kab);
+            } else {
+                const int zi = (int)pr.y;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = QT<T>::to_float2(rw[i]);
+                    c[k][i] = qz.template code_u8<false>(f.x, zi) | (qz.template code_u8<false>(f.y, zi) << 16);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) seen |= c[k][i];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            // (even channel | odd channel) x tokens 0..3 -> one word per channel
+            const unsigned x = __byte_perm(c[0][i], c[1][i], 0x6240), y = __byte_perm(c[2][i], c[3][i], 0x6240);
+            uint8_t* at = wr[i] + ((p << 4) ^ sw[i]);
+            *reinterpret_cast<unsigned*>(at) = __byte_perm(x, y, 0x5410);
+            *reinterpret_cast<unsigned*>(at + CB) = __byte_perm(x, y, 0x7632);
+        }
+    }
+    return seen;
 }
 
 template <typename T, bool HP, int BITS, int CB>
-__global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
+__global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int LB = len_field_bits(BITS);
     const int lane = lane_id(), wic = threadIdx.x >> 5;
@@ -269,53 +317,55 @@ __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
 
     // pass 1: per-token statistics across every head and channel
     bool bad = false;
-    for (int t = wic; t < CB; t += 8) {
-        const T* xt = xb + (int64_t)t * a.ss + 4 * lane;
+    for (int t = 2 * wic + (lane >> 4); t < CB; t += 16) {     // half a warp per token, 8 channels per lane
+        const T* xt = xb + (int64_t)t * a.ss + 8 * (lane & 15);
         using T2 = typename QT<T>::T2;
         T2 lo2 = QT<T>::init2(INFINITY), hi2 = QT<T>::init2(-INFINITY);
+#pragma unroll 4
         for (int h = 0; h < a.heads; h++) {
-            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(xt + (int64_t)h * a.sh));
-            const T2 v01 = *reinterpret_cast<const T2*>(&raw.x), v23 = *reinterpret_cast<const T2*>(&raw.y);
-            lo2 = QT<T>::min2(lo2, QT<T>::min2(v01, v23));
-            hi2 = QT<T>::max2(hi2, QT<T>::max2(v01, v23));
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xt + (int64_t)h * a.sh));
+            const T2 v0 = *reinterpret_cast<const T2*>(&raw.x), v1 = *reinterpret_cast<const T2*>(&raw.y);
+            const T2 v2 = *reinterpret_cast<const T2*>(&raw.z), v3 = *reinterpret_cast<const T2*>(&raw.w);
+            lo2 = QT<T>::min2(lo2, QT<T>::min2(QT<T>::min2(v0, v1), QT<T>::min2(v2, v3)));
+            hi2 = QT<T>::max2(hi2, QT<T>::max2(QT<T>::max2(v0, v1), QT<T>::max2(v2, v3)));
         }
         float lo = fminf(QT<T>::lo_f(lo2), QT<T>::hi_f(lo2)), hi = fmaxf(QT<T>::lo_f(hi2), QT<T>::hi_f(hi2));
 #pragma unroll
-        for (int s = 16; s > 0; s >>= 1) {
+        for (int s = 8; s > 0; s >>= 1) {
             lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, s));
             hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, s));
         }
         const Quantiser<T, HP> qz(lo, hi, a.rel);
         bad = bad || qz.degenerate();
-        if (lane == 0) {
-            prm[t] = make_float4(qz.scale, qz.zero, qz.rcp, qz.fast ? 1.f : 0.f);
+        if ((lane & 15) == 0) {
+            prm[t] = make_float4(qz.scale, qz.zero, qz.rcp, __uint_as_float(qz.packable() ? packed_code_bias(qz, qz) : 0u));   // bias 0 = not packable
             const int64_t pi = (int64_t)b * a.param_tokens + a.first_token + cbi * CB + t;
             reinterpret_cast<T*>(a.scale)[pi] = QT<T>::cvt(qz.scale);
             reinterpret_cast<T*>(a.zero)[pi] = QT<T>::cvt(qz.zero);
         }
     }
-    // one decision for the whole CTA: the cheap quotient needs every token's scale in range
+    // one decision for the whole CTA: the packed conversion needs every token's parameters in range
     __syncthreads();
     bool mine_ok = true;
-    for (int t = threadIdx.x; t < CB; t += 256) mine_ok = mine_ok && prm[t].w != 0.f;
-    const bool all_fast = __syncthreads_and(mine_ok);
+    for (int t = threadIdx.x; t < CB; t += 256) mine_ok = mine_ok && __float_as_uint(prm[t].w) != 0u;
+    const bool all_packed = __syncthreads_and(mine_ok);
 
     // pass 2: quantise + pack, one warp per V block
-    constexpr unsigned kOver = 0xFFu ^ ((1u << BITS) - 1u);
-    unsigned over = 0;
+    unsigned seen = 0;
     const int nvb = 2 * a.heads;
     for (int vb = wic; vb < nvb; vb += 8) {
         const int h = vb >> 1, half = vb & 1;
         const T* src = xb + (int64_t)h * a.sh + 64 * half;
         __syncwarp();
-        if (all_fast) v_quantise_tile<T, HP, BITS, true>(src, a.ss, CB, prm, ctile, lane);
-        else v_quantise_tile<T, HP, BITS, false>(src, a.ss, CB, prm, ctile, lane);
+        seen |= all_packed ? v_quantise_tile<T, CB, true>(src, a.ss, prm, ctile, lane) : v_quantise_tile<T, CB, false>(src, a.ss, prm, ctile, lane);
         __syncwarp();
         int pos = g.head_bytes;
         unsigned seg_end = 0;
-        for (int w = 0; w < 2; w++)
+        for (int w = 0; w < 2; w++) {
+            const int ch = 32 * w + lane;
+            const uint8_t* row = ctile + ch * CB;
+            const int swz = v_swz<CB>(ch);
             for (int r = 0; r < RPW; r++) {
-                const uint8_t* col = ctile + (r * PPT * 16) * 64 + w * 32 + lane;
                 unsigned minword = 0, lenword = 0, lens4 = 0;
                 uint64_t wd[4];
                 int len[4];
@@ -323,21 +373,31 @@ __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
                 for (int q = 0; q < 4; q++) {
                     len[q] = 0; wd[q] = 0;
                     if (q < PPT) {
-                        unsigned c[16];
-                        unsigned mn = 255, mx = 0;
+                        // word r0 of the chunk: bytes k = tokens r0 + 4k of the pack
+                        const uint4 cw = *reinterpret_cast<const uint4*>(row + (((r * PPT + q) ^ swz) << 4));
+                        unsigned wv[4] = {cw.x, cw.y, cw.z, cw.w};
+                        unsigned mn = 0xFFFFFFFFu, mx = 0u;
 #pragma unroll
-                        for (int t = 0; t < 16; t++) {
-                            c[t] = col[(q * 16 + t) * 64];
-                            mn = min(mn, c[t]); mx = max(mx, c[t]);
+                        for (int i = 0; i < 4; i++) {
+                            const unsigned ev = wv[i] & 0x00FF00FFu, od = (wv[i] >> 8) & 0x00FF00FFu;
+                            mn = min_u16x2(mn, min_u16x2(ev, od));
+                            mx = max_u16x2(mx, max_u16x2(ev, od));
                         }
-                        over |= mx & kOver;
-                        len[q] = min(bit_length_u32(mx - mn), BITS);
-                        const unsigned step = 1u << len[q];
-                        unsigned wt = 0, wb = 0;
+                        const unsigned mn1 = min(mn & 0xFFFFu, mn >> 16), mx1 = max(mx & 0xFFFFu, mx >> 16);
+                        len[q] = min(bit_length_u32(mx1 - mn1), BITS);
+                        const unsigned step = 1u << len[q], rep = mn1 * 0x01010101u;
+                        // 16-bit slots: slot k collects tokens 4k..4k+3 (r0 = 0 highest) by Horner steps over the words
+                        unsigned zlo = 0, zhi = 0;
 #pragma unroll
-                        for (int t = 0; t < 8; t++) { wt = wt * step + (c[t] - mn); wb = wb * step + (c[t + 8] - mn); }
+                        for (int i = 0; i < 4; i++) {
+                            const unsigned v = wv[i] - rep;
+                            zlo = zlo * step + __byte_perm(v, 0, 0x4140);
+                            zhi = zhi * step + __byte_perm(v, 0, 0x4342);
+                        }
+                        const unsigned wt = ((zlo & 0xFFFFu) << (4 * len[q])) | (zlo >> 16);     // tokens 0..7
+                        const unsigned wb = ((zhi & 0xFFFFu) << (4 * len[q])) | (zhi >> 16);     // tokens 8..15
                         wd[q] = ((uint64_t)wt << (8 * len[q])) | wb;
-                        minword |= (mn & ((1u << BITS) - 1u)) << (q * BITS);
+                        minword |= (mn1 & ((1u << BITS) - 1u)) << (q * BITS);
                         lenword |= (unsigned)len[q] << (q * LB);
                         lens4 |= (unsigned)len[q] << (8 * q);
                     }
@@ -360,12 +420,14 @@ __global__ void __launch_bounds__(256) v_fused_encode_kernel(FusedArgs a) {
                 if (lane == 0) *reinterpret_cast<uint16_t*>(stage + 2 * (w * RPW + r)) = (uint16_t)seg_end;
                 pos += seg_size;
             }
+        }
         __syncwarp();
         const int64_t blk = ((int64_t)b * nctx + cbi) * nvb + vb;
         store_slot(a.slots + blk * a.slot_stride, stage, pos, lane);
         if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * nvb + vb) * 2 + 1] = (unsigned)pos;
     }
-    if (__any_sync(0xffffffffu, bad || over != 0) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
+    bad = bad || (seen & ~(((1u << BITS) - 1u) * 0x00010001u)) != 0;
+    if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
 }
 
 // ------------------------------------------------------------------------------------ compact
@@ -449,9 +511,16 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
         blocks_per_seq = nctx * r.heads;
         const int64_t nwarps = (int64_t)blocks_per_seq * r.batch;
         const int smem = kWarpsPerCta * bound16;
-        auto kern = k_fused_encode_kernel<T, HP, BITS>;
-        if (opt_in_smem(kern, smem)) return kCudaError;
-        kern<<<(unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta), kWarpsPerCta * 32, smem, st>>>(a);
+        const unsigned grid = (unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta);
+        if (r.stride_s == 128) {
+            auto kern = k_fused_encode_kernel<T, true, BITS>;
+            if (opt_in_smem(kern, smem)) return kCudaError;
+            kern<<<grid, kWarpsPerCta * 32, smem, st>>>(a);
+        } else {
+            auto kern = k_fused_encode_kernel<T, false, BITS>;
+            if (opt_in_smem(kern, smem)) return kCudaError;
+            kern<<<grid, kWarpsPerCta * 32, smem, st>>>(a);
+        }
     } else {
         const VGeom g(r.cb, BITS);
         bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * g.ppt * 2 * BITS) + 15) & ~15;
