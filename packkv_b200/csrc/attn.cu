@@ -439,12 +439,13 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
                     Tr<T>::mma(accs[j & 1], af, qf[j][0], qf[j][1]);
                 }
                 // scores rounded like the reference: matmul output, then * scaling; tokens T0, T0+1 share a store
-                if (col_live) {
+                // (lanes whose head columns are not kept compute too: only the stores are predicated, no branch)
+                {
                     const unsigned row0 = st + (2 * c) * P.prow + 2 * tk;
                     const unsigned p0 = Tr<T>::pack2(Tr<T>::round(accs[0][0] + accs[1][0]) * a.scaling, Tr<T>::round(accs[0][2] + accs[1][2]) * a.scaling);
                     const unsigned p1 = Tr<T>::pack2(Tr<T>::round(accs[0][1] + accs[1][1]) * a.scaling, Tr<T>::round(accs[0][3] + accs[1][3]) * a.scaling);
-                    sts32(row0, p0);
-                    sts32(row0 + P.prow, p1);
+                    if (col_live) sts32(row0, p0);
+                    if (col_live) sts32(row0 + P.prow, p1);
                     const float2 f0 = Tr<T>::unpack2(p0), f1 = Tr<T>::unpack2(p1);
                     mloc0 = fmaxf(mloc0, fmaxf(f0.x, f0.y));
                     mloc1 = fmaxf(mloc1, fmaxf(f1.x, f1.y));
@@ -651,11 +652,9 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
                 const unsigned vpar = vsz_a + (tl & 1) * 4 * P.tile + tok2;   // this tile's parameter buffer
                 const uint4 s0 = lds128(vpar), s1 = lds128(vpar + 16);
                 const uint4 z0 = lds128(vpar + 2 * P.tile), z1 = lds128(vpar + 2 * P.tile + 16);
-                uint4 p0 = make_uint4(0, 0, 0, 0), p1 = make_uint4(0, 0, 0, 0);
-                if (g < P.rows) {
-                    p0 = lds128(st_a + g * P.prow + tok2);
-                    p1 = lds128(st_a + g * P.prow + tok2 + 16);
-                }
+                // head columns beyond the kept rows read a kept row: their output columns are never used
+                const unsigned prow_a = st_a + min(g, P.rows - 1) * P.prow + tok2;
+                const uint4 p0 = lds128(prow_a), p1 = lds128(prow_a + 16);
                 const unsigned vS[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
                 unsigned vZ[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
                 if (!HP) {

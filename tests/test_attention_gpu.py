@@ -93,3 +93,45 @@ def test_permutation_invariance(cuda_device):
         outs.append(ops.decode_attention(q, layer, None, None, 0).float().cpu())
     torch.cuda.synchronize()
     assert ((outs[0] - outs[1]).abs().max() / outs[0].abs().max()).item() <= TOL
+
+
+@pytest.mark.parametrize("shape", [
+    # (B, Hkv, G, n_comp, n_res, block, bits_k, bits_v, dtype): the decode configurations of the benchmark at full size
+    (16, 8, 4, 8064, 128, 64, 4, 4, torch.bfloat16),
+    (8, 8, 4, 32640, 128, 128, 2, 4, torch.bfloat16),
+])
+def test_full_size_weights_sum_to_one(cuda_device, shape):
+    """Size-independent property at the benchmark's sizes: if every token carries the same V row,
+    the output is that row whatever the scores are (the probabilities sum to one).  Compressed
+    tokens contribute the dequantised row d, residual tokens the original row v, so every output
+    element lies between d and v (up to the rounding tolerance); with no residual it equals d.
+    Every probability is rounded to the element type (as in the reference), so their sum is one
+    only up to a relative 2^-8: that slack is part of the bound."""
+    from packkv_b200 import encode
+    from packkv_b200.config import QuantMode
+    B, Hkv, G, n_comp, n_res, block, bits_k, bits_v, dtype = shape
+    dev = cuda_device
+    g = torch.Generator().manual_seed(41)
+    k, _ = synth.synth_kv(B, Hkv, n_comp + n_res, 128, seed=41, dtype=dtype, device=dev, apply_rope=True)
+    v_row = torch.randn(B, Hkv, 1, 128, generator=g).to(dtype)
+    q = synth.synth_q(B, Hkv * G, 128, seed=41, dtype=dtype)[:, :, 0].contiguous().to(dev)
+    rel_v = synth.rel_for_bits(bits_v)
+    # the dequantised row, from the oracle on one block of identical tokens
+    vc, vz, vs = Q.quant_ints(v_row.expand(B, Hkv, block, 128).contiguous(), block, rel_v, "token")
+    d = Q.dequant(vc, vz, vs)[:, :, 0].float()                   # (B, Hkv, 128)
+    v = v_row.expand(B, Hkv, n_comp + n_res, 128).contiguous().to(dev)
+    layer = encode.compress_kv(k[:, :, :n_comp], v[:, :, :n_comp], block=block, bits_k=bits_k, bits_v=bits_v,
+                               k_rel=synth.rel_for_bits(bits_k), v_rel=rel_v, k_mode=QuantMode.ChannelQuant)
+    flags = ops.new_flags(dev)
+    lo = torch.minimum(d, v_row[:, :, 0].float()).repeat_interleave(G, dim=1)
+    hi = torch.maximum(d, v_row[:, :, 0].float()).repeat_interleave(G, dim=1)
+    tol = TOL * float(v_row.float().abs().max())
+    eps = 2.0 ** -8
+    lo, hi = torch.minimum(lo * (1 - eps), lo * (1 + eps)), torch.maximum(hi * (1 - eps), hi * (1 + eps))
+    out = ops.decode_attention(q, layer, k[:, :, n_comp:].contiguous(), v[:, :, n_comp:].contiguous(), n_res, flags=flags, kv_heads=Hkv).float().cpu()
+    assert int(flags.item()) == 0
+    assert bool(((out >= lo - tol) & (out <= hi + tol)).all())
+    out0 = ops.decode_attention(q, layer, None, None, 0, flags=flags, kv_heads=Hkv).float().cpu()
+    assert int(flags.item()) == 0
+    dd = d.repeat_interleave(G, dim=1)
+    assert bool(((out0 - dd).abs() <= tol + eps * dd.abs()).all())
