@@ -299,25 +299,42 @@ __device__ __forceinline__ unsigned v_quantise_tile(const T* src, int64_t ss, co
     return seen;
 }
 
-template <typename T, bool HP, int BITS, int CB>
-__global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    constexpr int LB = len_field_bits(BITS);
-    const int lane = lane_id(), wic = threadIdx.x >> 5;
-    const int cbi = blockIdx.x, b = blockIdx.y;
-    const int nctx = a.tokens / CB;
-    constexpr int PPT = CB == 32 ? 2 : 4, RPW = CB == 128 ? 2 : 1;
-    const VGeom g(CB, BITS);
-    const int bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * PPT * 2 * BITS) + 15) & ~15;
-    float4* prm = reinterpret_cast<float4*>(smem);           // [cb] (scale, zero, 1/scale, fast)
-    uint8_t* wbase = smem + 16 * CB + wic * (CB * 64 + bound16);
-    uint8_t* ctile = wbase;                                  // [cb][64] codes
-    uint8_t* stage = wbase + CB * 64;
-    const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
+// One 16-byte tile chunk (word r0: bytes k = codes of tokens r0 + 4k of the pack) -> the pack's
+// minimum, bit length and 2*len-byte word (token 0 in the top bits).
+template <int BITS>
+__device__ __forceinline__ void chunk_to_pack(const uint4& cw, int& len, uint64_t& wd, unsigned& mn1) {
+    const unsigned wv[4] = {cw.x, cw.y, cw.z, cw.w};
+    unsigned mn = 0xFFFFFFFFu, mx = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const unsigned ev = wv[i] & 0x00FF00FFu, od = (wv[i] >> 8) & 0x00FF00FFu;
+        mn = min_u16x2(mn, min_u16x2(ev, od));
+        mx = max_u16x2(mx, max_u16x2(ev, od));
+    }
+    mn1 = min(mn & 0xFFFFu, mn >> 16);
+    const unsigned mx1 = max(mx & 0xFFFFu, mx >> 16);
+    len = min(bit_length_u32(mx1 - mn1), BITS);
+    const unsigned step = 1u << len, rep = mn1 * 0x01010101u;
+    // 16-bit slots: slot k collects tokens 4k..4k+3 (r0 = 0 highest) by Horner steps over the words
+    unsigned zlo = 0, zhi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const unsigned v = wv[i] - rep;
+        zlo = zlo * step + __byte_perm(v, 0, 0x4140);
+        zhi = zhi * step + __byte_perm(v, 0, 0x4342);
+    }
+    const unsigned wt = ((zlo & 0xFFFFu) << (4 * len)) | (zlo >> 16);     // tokens 0..7
+    const unsigned wb = ((zhi & 0xFFFFu) << (4 * len)) | (zhi >> 16);     // tokens 8..15
+    wd = ((uint64_t)wt << (8 * len)) | wb;
+}
 
-    // pass 1: per-token statistics across every head and channel
+// Per-token quantisation parameters of one token block over all heads and channels (the
+// reference's token mode reduces over dims [1, 4], utils/compute.py:405-410): half a warp per token.
+// Writes (scale, zero, 1/scale, packed code bias or 0) to prm[] and scale / zero to the caller's arrays.
+template <typename T, int CB>
+__device__ __forceinline__ bool token_params_pass(const FusedArgs& a, const T* xb, float4* prm, int b, int cbi, int lane, int wic) {
     bool bad = false;
-    for (int t = 2 * wic + (lane >> 4); t < CB; t += 16) {     // half a warp per token, 8 channels per lane
+    for (int t = 2 * wic + (lane >> 4); t < CB; t += 16) {     // 8 channels per lane
         const T* xt = xb + (int64_t)t * a.ss + 8 * (lane & 15);
         using T2 = typename QT<T>::T2;
         T2 lo2 = QT<T>::init2(INFINITY), hi2 = QT<T>::init2(-INFINITY);
@@ -335,7 +352,7 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
             lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, s));
             hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, s));
         }
-        const Quantiser<T, HP> qz(lo, hi, a.rel);
+        const Quantiser<T, false> qz(lo, hi, a.rel);
         bad = bad || qz.degenerate();
         if ((lane & 15) == 0) {
             prm[t] = make_float4(qz.scale, qz.zero, qz.rcp, __uint_as_float(qz.packable() ? packed_code_bias(qz, qz) : 0u));   // bias 0 = not packable
@@ -344,6 +361,27 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
             reinterpret_cast<T*>(a.zero)[pi] = QT<T>::cvt(qz.zero);
         }
     }
+    return bad;
+}
+
+template <typename T, bool HP, int BITS, int CB>
+__global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int LB = len_field_bits(BITS);
+    const int lane = lane_id(), wic = threadIdx.x >> 5;
+    const int cbi = blockIdx.x, b = blockIdx.y;
+    const int nctx = a.tokens / CB;
+    constexpr int PPT = CB == 32 ? 2 : 4, RPW = CB == 128 ? 2 : 1;
+    const VGeom g(CB, BITS);
+    const int bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * PPT * 2 * BITS) + 15) & ~15;
+    float4* prm = reinterpret_cast<float4*>(smem);           // [cb] (scale, zero, 1/scale, fast)
+    uint8_t* wbase = smem + 16 * CB + wic * (CB * 64 + bound16);
+    uint8_t* ctile = wbase;                                  // [cb][64] codes
+    uint8_t* stage = wbase + CB * 64;
+    const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
+
+    // pass 1: per-token statistics across every head and channel
+    bool bad = token_params_pass<T, CB>(a, xb, prm, b, cbi, lane, wic);
     // one decision for the whole CTA: the packed conversion needs every token's parameters in range
     __syncthreads();
     bool mine_ok = true;
@@ -375,28 +413,8 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
                     if (q < PPT) {
                         // word r0 of the chunk: bytes k = tokens r0 + 4k of the pack
                         const uint4 cw = *reinterpret_cast<const uint4*>(row + (((r * PPT + q) ^ swz) << 4));
-                        unsigned wv[4] = {cw.x, cw.y, cw.z, cw.w};
-                        unsigned mn = 0xFFFFFFFFu, mx = 0u;
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const unsigned ev = wv[i] & 0x00FF00FFu, od = (wv[i] >> 8) & 0x00FF00FFu;
-                            mn = min_u16x2(mn, min_u16x2(ev, od));
-                            mx = max_u16x2(mx, max_u16x2(ev, od));
-                        }
-                        const unsigned mn1 = min(mn & 0xFFFFu, mn >> 16), mx1 = max(mx & 0xFFFFu, mx >> 16);
-                        len[q] = min(bit_length_u32(mx1 - mn1), BITS);
-                        const unsigned step = 1u << len[q], rep = mn1 * 0x01010101u;
-                        // 16-bit slots: slot k collects tokens 4k..4k+3 (r0 = 0 highest) by Horner steps over the words
-                        unsigned zlo = 0, zhi = 0;
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const unsigned v = wv[i] - rep;
-                            zlo = zlo * step + __byte_perm(v, 0, 0x4140);
-                            zhi = zhi * step + __byte_perm(v, 0, 0x4342);
-                        }
-                        const unsigned wt = ((zlo & 0xFFFFu) << (4 * len[q])) | (zlo >> 16);     // tokens 0..7
-                        const unsigned wb = ((zhi & 0xFFFFu) << (4 * len[q])) | (zhi >> 16);     // tokens 8..15
-                        wd[q] = ((uint64_t)wt << (8 * len[q])) | wb;
+                        unsigned mn1;
+                        chunk_to_pack<BITS>(cw, len[q], wd[q], mn1);
                         minword |= (mn1 & ((1u << BITS) - 1u)) << (q * BITS);
                         lenword |= (unsigned)len[q] << (q * LB);
                         lens4 |= (unsigned)len[q] << (8 * q);
@@ -425,6 +443,90 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
         const int64_t blk = ((int64_t)b * nctx + cbi) * nvb + vb;
         store_slot(a.slots + blk * a.slot_stride, stage, pos, lane);
         if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * nvb + vb) * 2 + 1] = (unsigned)pos;
+    }
+    bad = bad || (seen & ~(((1u << BITS) - 1u) * 0x00010001u)) != 0;
+    if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
+}
+
+// ------------------------------------------------------------------------- K, token mode
+// K with per-token parameters (the reference's QuantMethod.PackKV pairing): the parameter pass and
+// the quantising stage are V's; each warp then packs one K block (CB tokens x 128 channels of one
+// head) in the K layout, lane = channels 4*lane..4*lane+3, one round per 16 tokens.
+template <typename T, int BITS, int CB>
+__global__ void __launch_bounds__(256, 2) kt_fused_encode_kernel(FusedArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int LB = len_field_bits(BITS);
+    const int lane = lane_id(), wic = threadIdx.x >> 5;
+    const int cbi = blockIdx.x, b = blockIdx.y;
+    const int nctx = a.tokens / CB;
+    const KGeom g(CB, BITS);
+    const int bound16 = (g.head_bytes + g.rounds * (g.min_bytes + g.len_bytes + 128 * 2 * BITS) + 15) & ~15;
+    float4* prm = reinterpret_cast<float4*>(smem);
+    uint8_t* wbase = smem + 16 * CB + wic * (CB * 128 + bound16);
+    uint8_t* ctile = wbase;                                  // two 64-channel halves of [64][CB] codes
+    uint8_t* stage = wbase + CB * 128;
+    const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
+
+    bool bad = token_params_pass<T, CB>(a, xb, prm, b, cbi, lane, wic);
+    __syncthreads();
+    bool mine_ok = true;
+    for (int t = threadIdx.x; t < CB; t += 256) mine_ok = mine_ok && __float_as_uint(prm[t].w) != 0u;
+    const bool all_packed = __syncthreads_and(mine_ok);
+
+    unsigned seen = 0;
+    for (int h = wic; h < a.heads; h += 8) {
+        const T* src = xb + (int64_t)h * a.sh;
+        __syncwarp();
+#pragma unroll 1
+        for (int half = 0; half < 2; half++)
+            seen |= all_packed ? v_quantise_tile<T, CB, true>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane)
+                               : v_quantise_tile<T, CB, false>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane);
+        __syncwarp();
+        // this lane's four channel rows and their chunk swizzles
+        const uint8_t* row[4];
+        int swz[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int ch = 4 * lane + j;
+            row[j] = ctile + (ch >> 6) * 64 * CB + (ch & 63) * CB;
+            swz[j] = v_swz<CB>(ch & 63);
+        }
+        int pos = g.head_bytes;
+        unsigned round_end = 0;
+        for (int r = 0; r < g.rounds; r++) {
+            unsigned minword = 0, lenword = 0, lens4 = 0;
+            uint64_t wd[4];
+            int len[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint4 cw = *reinterpret_cast<const uint4*>(row[j] + ((r ^ swz[j]) << 4));
+                unsigned mn1;
+                chunk_to_pack<BITS>(cw, len[j], wd[j], mn1);
+                minword |= (mn1 & ((1u << BITS) - 1u)) << (j * BITS);
+                lenword |= (unsigned)len[j] << (j * LB);
+                lens4 |= (unsigned)len[j] << (8 * j);
+            }
+            store_lane_fields(stage + pos, lane, 4 * BITS, minword);
+            store_lane_fields(stage + pos + g.min_bytes, lane, 4 * LB, lenword);
+            const unsigned inc = warp_inclusive_sum(lens4);
+            const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+            const unsigned exc = inc - lens4;
+            uint8_t* packs = stage + pos + g.min_bytes + g.len_bytes;
+            unsigned before = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                store_pack_smem(packs + 2 * (before + ((exc >> (8 * j)) & 0xFFu)), wd[j], len[j]);
+                before += (tot >> (8 * j)) & 0xFFu;
+            }
+            const unsigned round_size = g.min_bytes + g.len_bytes + 2 * before;
+            round_end += round_size;
+            if (lane == 0) *reinterpret_cast<uint16_t*>(stage + 2 * r) = (uint16_t)round_end;
+            pos += round_size;
+        }
+        __syncwarp();
+        const int64_t blk = ((int64_t)b * nctx + cbi) * a.heads + h;
+        store_slot(a.slots + blk * a.slot_stride, stage, pos, lane);
+        if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * a.heads + h) * 2 + 1] = (unsigned)pos;
     }
     bad = bad || (seen & ~(((1u << BITS) - 1u) * 0x00010001u)) != 0;
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
@@ -479,7 +581,8 @@ bool fused_encode_applicable(const FusedEncodeRequest& r) {
     if (r.bits < 2 || r.bits > 4) return false;
     if (r.cb != 32 && r.cb != 64 && r.cb != 128) return false;
     if (r.tokens % r.cb) return false;
-    if (r.which == 0 && (r.mode != 0 || r.qblock != r.cb)) return false;   // K: per-channel parameters per stream block
+    if (r.which == 0 && r.mode == 0 && r.qblock != r.cb) return false;       // K, channel mode: parameters per stream block
+    if (r.which == 0 && r.mode != 0 && r.mode != 1) return false;
     if (r.which == 1 && r.mode != 1) return false;                           // V: per-token parameters
     if ((reinterpret_cast<uintptr_t>(r.x) & 15) || (r.stride_b & 7) || (r.stride_h & 7) || (r.stride_s & 7)) return false;
     return true;
@@ -512,7 +615,19 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
         const int64_t nwarps = (int64_t)blocks_per_seq * r.batch;
         const int smem = kWarpsPerCta * bound16;
         const unsigned grid = (unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta);
-        if (r.stride_s == 128) {
+        if (r.mode == 1) {                       // per-token parameters: CTA per (sequence, token block)
+            const int smem_t = 16 * r.cb + 8 * (r.cb * 128 + bound16);
+            auto launch_kt = [&](auto kern) {
+                if (opt_in_smem(kern, smem_t)) return (int)kCudaError;
+                kern<<<dim3(nctx, r.batch), 256, smem_t, st>>>(a);
+                return (int)kOk;
+            };
+            int rc = kOk;
+            if (r.cb == 32) rc = launch_kt(kt_fused_encode_kernel<T, BITS, 32>);
+            else if (r.cb == 64) rc = launch_kt(kt_fused_encode_kernel<T, BITS, 64>);
+            else rc = launch_kt(kt_fused_encode_kernel<T, BITS, 128>);
+            if (rc != kOk) return rc;
+        } else if (r.stride_s == 128) {
             auto kern = k_fused_encode_kernel<T, true, BITS>;
             if (opt_in_smem(kern, smem)) return kCudaError;
             kern<<<grid, kWarpsPerCta * 32, smem, st>>>(a);
