@@ -130,6 +130,29 @@ __device__ __forceinline__ void store_lane_fields(uint8_t* hdr, int lane, int wi
     }
 }
 
+// Same with the width known at compile time: 8- and 16-bit words are stored directly, 12-bit words
+// pair up two lanes per three bytes (one shuffle); other widths take the generic routine.
+// hdr must be 2-byte aligned.  Must be called by all 32 lanes.
+template <int W>
+__device__ __forceinline__ void store_lane_fields_w(uint8_t* hdr, int lane, unsigned word) {
+    if (W == 8) {
+        hdr[lane] = (uint8_t)word;
+    } else if (W == 16) {
+        *reinterpret_cast<uint16_t*>(hdr + 2 * lane) = (uint16_t)word;
+    } else if (W == 12) {
+        const unsigned other = __shfl_xor_sync(0xffffffffu, word, 1);
+        uint8_t* p = hdr + 3 * (lane >> 1);
+        if (lane & 1) {
+            p[2] = (uint8_t)(word >> 4);
+        } else {
+            p[0] = (uint8_t)word;
+            p[1] = (uint8_t)((word >> 8) | ((other & 0xFu) << 4));
+        }
+    } else {
+        store_lane_fields(hdr, lane, W, word);
+    }
+}
+
 // 64-bit window of a byte string at an even byte offset; p must be 2-byte aligned.
 __device__ __forceinline__ uint64_t load_u64_align2(const uint8_t* p) {
     const uint16_t* q = reinterpret_cast<const uint16_t*>(p);

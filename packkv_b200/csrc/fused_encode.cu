@@ -74,8 +74,8 @@ __device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const Qua
             lenword |= (unsigned)len[j] << (j * LB);
             lens4 |= (unsigned)len[j] << (8 * j);
         }
-        store_lane_fields(stage + pos, lane, 4 * BITS, minword);
-        store_lane_fields(stage + pos + g.min_bytes, lane, 4 * LB, lenword);
+        store_lane_fields_w<4 * BITS>(stage + pos, lane, minword);
+        store_lane_fields_w<4 * LB>(stage + pos + g.min_bytes, lane, lenword);
         const unsigned inc = warp_inclusive_sum(lens4);
         const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
         const unsigned exc = inc - lens4;
@@ -143,8 +143,8 @@ __device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, co
             lenword |= (unsigned)len[j] << (j * LB);
             lens4 |= (unsigned)len[j] << (8 * j);
         }
-        store_lane_fields(stage + pos, lane, 4 * BITS, minword);
-        store_lane_fields(stage + pos + g.min_bytes, lane, 4 * LB, lenword);
+        store_lane_fields_w<4 * BITS>(stage + pos, lane, minword);
+        store_lane_fields_w<4 * LB>(stage + pos + g.min_bytes, lane, lenword);
         const unsigned inc = warp_inclusive_sum(lens4);
         const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
         const unsigned exc = inc - lens4;
@@ -420,8 +420,8 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
                         lens4 |= (unsigned)len[q] << (8 * q);
                     }
                 }
-                store_lane_fields(stage + pos, lane, PPT * BITS, minword);
-                store_lane_fields(stage + pos + g.min_bytes, lane, PPT * LB, lenword);
+                store_lane_fields_w<PPT * BITS>(stage + pos, lane, minword);
+                store_lane_fields_w<PPT * LB>(stage + pos + g.min_bytes, lane, lenword);
                 const unsigned inc = warp_inclusive_sum(lens4);
                 const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
                 const unsigned exc = inc - lens4;
@@ -506,8 +506,8 @@ __global__ void __launch_bounds__(256, 2) kt_fused_encode_kernel(FusedArgs a) {
                 lenword |= (unsigned)len[j] << (j * LB);
                 lens4 |= (unsigned)len[j] << (8 * j);
             }
-            store_lane_fields(stage + pos, lane, 4 * BITS, minword);
-            store_lane_fields(stage + pos + g.min_bytes, lane, 4 * LB, lenword);
+            store_lane_fields_w<4 * BITS>(stage + pos, lane, minword);
+            store_lane_fields_w<4 * LB>(stage + pos + g.min_bytes, lane, lenword);
             const unsigned inc = warp_inclusive_sum(lens4);
             const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
             const unsigned exc = inc - lens4;
