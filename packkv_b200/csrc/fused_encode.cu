@@ -111,12 +111,13 @@ __device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const Qua
 // The same rounds for blocks whose four quantisers are packable(): two channels per instruction
 // from the conversion to the pack minimum / maximum (16-bit lanes), then one multiply-add per code
 // into the pack words.
-template <typename T, int BITS>
+template <typename T, int BITS, bool HALF>
 __device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, const Quantiser<T, false>& q0, const Quantiser<T, false>& q1,
                                                       const Quantiser<T, false>& q2, const Quantiser<T, false>& q3, const KGeom& g,
                                                       uint8_t* stage, int lane, bool& bad) {
     constexpr int LB = len_field_bits(BITS);
     const unsigned k01 = packed_code_bias(q0, q1), k23 = packed_code_bias(q2, q3);
+    const HalfQuotient<T> h01(q0, q1), h23(q2, q3);      // used when every quantiser is in the half domain
     int pos = g.head_bytes;
     unsigned round_end = 0, over = 0;
     for (int r = 0; r < g.rounds; r++) {
@@ -125,8 +126,8 @@ __device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, co
 #pragma unroll
         for (int t = 0; t < 16; t++) {
             const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)(r * 16 + t) * ss));
-            c01[t] = packed_codes<T>(raw.x, q0, q1, k01);
-            c23[t] = packed_codes<T>(raw.y, q2, q3, k23);
+            c01[t] = HALF ? h01.codes(raw.x) : packed_codes<T>(raw.x, q0, q1, k01);
+            c23[t] = HALF ? h23.codes(raw.y) : packed_codes<T>(raw.y, q2, q3, k23);
             mn01 = min_u16x2(mn01, c01[t]); mx01 = max_u16x2(mx01, c01[t]);
             mn23 = min_u16x2(mn23, c23[t]); mx23 = max_u16x2(mx23, c23[t]);
         }
@@ -223,7 +224,9 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
     bool bad = q0.degenerate() || q1.degenerate() || q2.degenerate() || q3.degenerate();
     const bool packable = __all_sync(0xffffffffu, q0.packable() && q1.packable() && q2.packable() && q3.packable());
     int pos;
-    if (!HP && packable) pos = k_encode_rounds_packed<T, BITS>(x, ss, q0, q1, q2, q3, g, stage, lane, bad);
+    const bool half_ok = __all_sync(0xffffffffu, q0.half_domain() && q1.half_domain() && q2.half_domain() && q3.half_domain());
+    if (!HP && half_ok) pos = k_encode_rounds_packed<T, BITS, true>(x, ss, q0, q1, q2, q3, g, stage, lane, bad);
+    else if (!HP && packable) pos = k_encode_rounds_packed<T, BITS, false>(x, ss, q0, q1, q2, q3, g, stage, lane, bad);
     else pos = k_encode_rounds<T, HP, BITS, false>(x, ss, q0, q1, q2, q3, g, stage, lane, bad);
     __syncwarp();
     store_slot(a.slots + (int64_t)warp * a.slot_stride, stage, pos, lane);
