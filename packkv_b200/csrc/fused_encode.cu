@@ -252,8 +252,10 @@ __device__ __forceinline__ int v_swz(int ch) { return ((ch >> 1) ^ (ch >> 3)) & 
 // (16 bytes) of tokens r0, r0+4, r0+8, ... and, per pack, turns its 4 tokens x 8 channels into one
 // 4-token word per channel.  PACKED: two channels per instruction (all tokens packable()).
 // Returns the OR of all codes in 16-bit lanes for the range check.
-template <typename T, int CB, bool PACKED>
+template <typename T, int CB, int MODE>     // MODE 0: scalar conversion, 1: two elements per instruction in fp32, 2: in the element type
 __device__ __forceinline__ unsigned v_quantise_tile(const T* src, int64_t ss, const float4* prm, uint8_t* tile, int lane) {
+    constexpr bool PACKED = MODE == 1;
+    const uint4* prmh = reinterpret_cast<const uint4*>(prm + CB);   // per token: r, -128*scale, r/128 (element-type pairs), code bias
     const int r0 = lane >> 3, cg = lane & 7;
     unsigned seen = 0;
     uint8_t* wr[4];                                        // row of channel 8cg + 2i at this lane's word, before the chunk swizzle
@@ -271,10 +273,25 @@ __device__ __forceinline__ unsigned v_quantise_tile(const T* src, int64_t ss, co
         for (int k = 0; k < 4; k++) {
             const int tok = 16 * p + 4 * k + r0;
             const uint4 raw = __ldg(reinterpret_cast<const uint4*>(lsrc + (int64_t)(16 * p + 4 * k) * ss));
+            const unsigned rw[4] = {raw.x, raw.y, raw.z, raw.w};
+            if (MODE == 2) {
+                const uint4 ph = prmh[tok];
+                HalfQuotient<T> hq;
+                hq.r = *reinterpret_cast<const typename QT<T>::T2*>(&ph.x);
+                hq.nsp = *reinterpret_cast<const typename QT<T>::T2*>(&ph.y);
+                hq.rp = *reinterpret_cast<const typename QT<T>::T2*>(&ph.z);
+                hq.kab = ph.w;
+                hq.magic = QT<T>::dup((float)(QT<T>::kIntBits == 0x6600u ? 1536 : 192));
+                hq.pre = QT<T>::dup(QT<T>::kPre);
+#pragma unroll
+                for (int i = 0; i < 4; i++) c[k][i] = hq.codes(rw[i]);
+#pragma unroll
+                for (int i = 0; i < 4; i++) seen |= c[k][i];
+                continue;
+            }
             const float4 pr = prm[tok];                    // scale, zero, 1/scale
             Quantiser<T, false> qz;
             qz.scale = pr.x; qz.zero = pr.y; qz.rcp = pr.z;
-            const unsigned rw[4] = {raw.x, raw.y, raw.z, raw.w};
             if (PACKED) {
                 const unsigned kab = __float_as_uint(pr.w);
 #pragma unroll
@@ -359,6 +376,9 @@ __device__ __forceinline__ bool token_params_pass(const FusedArgs& a, const T* x
         bad = bad || qz.degenerate();
         if ((lane & 15) == 0) {
             prm[t] = make_float4(qz.scale, qz.zero, qz.rcp, __uint_as_float(qz.packable() ? packed_code_bias(qz, qz) : 0u));   // bias 0 = not packable
+            const HalfQuotient<T> hq(qz, qz);
+            reinterpret_cast<uint4*>(prm + CB)[t] = make_uint4(*reinterpret_cast<const unsigned*>(&hq.r), *reinterpret_cast<const unsigned*>(&hq.nsp),
+                                                               *reinterpret_cast<const unsigned*>(&hq.rp), qz.half_domain() ? hq.kab : 0u);
             const int64_t pi = (int64_t)b * a.param_tokens + a.first_token + cbi * CB + t;
             reinterpret_cast<T*>(a.scale)[pi] = QT<T>::cvt(qz.scale);
             reinterpret_cast<T*>(a.zero)[pi] = QT<T>::cvt(qz.zero);
@@ -378,7 +398,7 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
     const VGeom g(CB, BITS);
     const int bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * PPT * 2 * BITS) + 15) & ~15;
     float4* prm = reinterpret_cast<float4*>(smem);           // [cb] (scale, zero, 1/scale, fast)
-    uint8_t* wbase = smem + 16 * CB + wic * (CB * 64 + bound16);
+    uint8_t* wbase = smem + 32 * CB + wic * (CB * 64 + bound16);
     uint8_t* ctile = wbase;                                  // [cb][64] codes
     uint8_t* stage = wbase + CB * 64;
     const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
@@ -387,9 +407,13 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
     bool bad = token_params_pass<T, CB>(a, xb, prm, b, cbi, lane, wic);
     // one decision for the whole CTA: the packed conversion needs every token's parameters in range
     __syncthreads();
-    bool mine_ok = true;
-    for (int t = threadIdx.x; t < CB; t += 256) mine_ok = mine_ok && __float_as_uint(prm[t].w) != 0u;
+    bool mine_ok = true, mine_half = true;
+    for (int t = threadIdx.x; t < CB; t += 256) {
+        mine_ok = mine_ok && __float_as_uint(prm[t].w) != 0u;
+        mine_half = mine_half && reinterpret_cast<const uint4*>(prm + CB)[t].w != 0u;
+    }
     const bool all_packed = __syncthreads_and(mine_ok);
+    const bool all_half = __syncthreads_and(mine_half);
 
     // pass 2: quantise + pack, one warp per V block
     unsigned seen = 0;
@@ -398,7 +422,8 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
         const int h = vb >> 1, half = vb & 1;
         const T* src = xb + (int64_t)h * a.sh + 64 * half;
         __syncwarp();
-        seen |= all_packed ? v_quantise_tile<T, CB, true>(src, a.ss, prm, ctile, lane) : v_quantise_tile<T, CB, false>(src, a.ss, prm, ctile, lane);
+        seen |= all_half ? v_quantise_tile<T, CB, 2>(src, a.ss, prm, ctile, lane)
+                         : all_packed ? v_quantise_tile<T, CB, 1>(src, a.ss, prm, ctile, lane) : v_quantise_tile<T, CB, 0>(src, a.ss, prm, ctile, lane);
         __syncwarp();
         int pos = g.head_bytes;
         unsigned seg_end = 0;
@@ -465,16 +490,20 @@ __global__ void __launch_bounds__(256, 2) kt_fused_encode_kernel(FusedArgs a) {
     const KGeom g(CB, BITS);
     const int bound16 = (g.head_bytes + g.rounds * (g.min_bytes + g.len_bytes + 128 * 2 * BITS) + 15) & ~15;
     float4* prm = reinterpret_cast<float4*>(smem);
-    uint8_t* wbase = smem + 16 * CB + wic * (CB * 128 + bound16);
+    uint8_t* wbase = smem + 32 * CB + wic * (CB * 128 + bound16);
     uint8_t* ctile = wbase;                                  // two 64-channel halves of [64][CB] codes
     uint8_t* stage = wbase + CB * 128;
     const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
 
     bool bad = token_params_pass<T, CB>(a, xb, prm, b, cbi, lane, wic);
     __syncthreads();
-    bool mine_ok = true;
-    for (int t = threadIdx.x; t < CB; t += 256) mine_ok = mine_ok && __float_as_uint(prm[t].w) != 0u;
+    bool mine_ok = true, mine_half = true;
+    for (int t = threadIdx.x; t < CB; t += 256) {
+        mine_ok = mine_ok && __float_as_uint(prm[t].w) != 0u;
+        mine_half = mine_half && reinterpret_cast<const uint4*>(prm + CB)[t].w != 0u;
+    }
     const bool all_packed = __syncthreads_and(mine_ok);
+    const bool all_half = __syncthreads_and(mine_half);
 
     unsigned seen = 0;
     for (int h = wic; h < a.heads; h += 8) {
@@ -482,8 +511,9 @@ __global__ void __launch_bounds__(256, 2) kt_fused_encode_kernel(FusedArgs a) {
         __syncwarp();
 #pragma unroll 1
         for (int half = 0; half < 2; half++)
-            seen |= all_packed ? v_quantise_tile<T, CB, true>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane)
-                               : v_quantise_tile<T, CB, false>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane);
+            seen |= all_half ? v_quantise_tile<T, CB, 2>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane)
+                             : all_packed ? v_quantise_tile<T, CB, 1>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane)
+                                          : v_quantise_tile<T, CB, 0>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane);
         __syncwarp();
         // this lane's four channel rows and their chunk swizzles
         const uint8_t* row[4];
@@ -619,7 +649,7 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
         const int smem = kWarpsPerCta * bound16;
         const unsigned grid = (unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta);
         if (r.mode == 1) {                       // per-token parameters: CTA per (sequence, token block)
-            const int smem_t = 16 * r.cb + 8 * (r.cb * 128 + bound16);
+            const int smem_t = 32 * r.cb + 8 * (r.cb * 128 + bound16);
             auto launch_kt = [&](auto kern) {
                 if (opt_in_smem(kern, smem_t)) return (int)kCudaError;
                 kern<<<dim3(nctx, r.batch), 256, smem_t, st>>>(a);
@@ -644,7 +674,7 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
         bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * g.ppt * 2 * BITS) + 15) & ~15;
         a.slot_stride = bound16;
         blocks_per_seq = nctx * 2 * r.heads;
-        const int smem = 16 * r.cb + 8 * (r.cb * 64 + bound16);
+        const int smem = 32 * r.cb + 8 * (r.cb * 64 + bound16);
         auto launch_v = [&](auto kern) {
             if (opt_in_smem(kern, smem)) return (int)kCudaError;
             kern<<<dim3(nctx, r.batch), 256, smem, st>>>(a);
