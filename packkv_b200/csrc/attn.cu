@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
         }
         const unsigned off = inf.x, size = inf.y;
         uint8_t* dst = wbase + (n & 1) * P.slot;
-        if ((int64_t)off + size > cap || (int)size > bound || size < 4) {
+        if ((int64_t)off + size > cap || (int)size > bound || size < 4 || ((off | size) & 1u)) {   // blocks start and end on even bytes
             if (lane == 0) atomicOr(a.flags, kFlagBadStream);
             phase_out = 0; size_out = 0;
         } else {

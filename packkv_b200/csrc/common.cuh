@@ -73,8 +73,8 @@ __device__ __forceinline__ unsigned lane_id() { return threadIdx.x & 31u; }
 __device__ __forceinline__ unsigned warp_inclusive_sum(unsigned v) {
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-        unsigned n = __shfl_up_sync(0xffffffffu, v, d);
-        if ((int)lane_id() >= d) v += n;
+        // the shuffle's own predicate says whether the source lane exists: no lane compare needed
+        asm volatile("{ .reg .pred p; .reg .b32 n; shfl.sync.up.b32 n|p, %0, %1, 0, 0xffffffff; @p add.u32 %0, %0, n; }" : "+r"(v) : "r"(d));
     }
     return v;
 }
@@ -200,6 +200,7 @@ __device__ __forceinline__ void sts128(unsigned a, uint4 v) {
 // hdr (any alignment): two aligned 32-bit loads and a funnel shift.  May read up to 7 bytes past
 // the header.
 __device__ __forceinline__ unsigned lds_lane_field(unsigned hdr, int lane, int width) {
+    if (width == 16) return lds16(hdr + 2 * lane);     // headers start at even addresses: one aligned load
     const unsigned bit = hdr * 8u + (unsigned)(lane * width);
     const unsigned wa = (bit >> 5) << 2;
     return __funnelshift_r(lds32(wa), lds32(wa + 4), bit & 31u) & ((1u << width) - 1u);
