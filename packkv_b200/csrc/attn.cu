@@ -612,6 +612,11 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
                     }
                 }
             }
+            if (!HP) {
+                // the tile's zero-points take the conversion bias once here instead of in every segment
+                const unsigned zb = vsz_a + (tl & 1) * 4 * P.tile + 2 * P.tile;
+                for (int t = lane; t < (P.tile >> 1); t += 32) sts32(zb + 4 * t, as_u(__hsub2(as_t2<T2>(lds32(zb + 4 * t)), bias2)));
+            }
             __syncwarp();
         }
         if (cur_size > 0) {
@@ -656,11 +661,7 @@ __global__ void __launch_bounds__(kAW * 32, 4) attn_decode_kernel(const AttnDev 
                 const unsigned prow_a = st_a + min(g, P.rows - 1) * P.prow + tok2;
                 const uint4 p0 = lds128(prow_a), p1 = lds128(prow_a + 16);
                 const unsigned vS[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-                unsigned vZ[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
-                if (!HP) {
-#pragma unroll
-                    for (int j = 0; j < 8; j++) vZ[j] = as_u(__hsub2(as_t2<T2>(vZ[j]), bias2));
-                }
+                const unsigned vZ[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
                 const unsigned pf[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
                 // A fragments for both 16-channel row tiles, then the contraction into the
                 // accumulator group of this (64-channel half, warp half): static register
