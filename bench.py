@@ -309,7 +309,7 @@ def cpu_reference_path(w, sample_batch: int, repeats: int, threads: int):
 def run_reference(args, w):
     threads = os.cpu_count() or 1
     sample_batch = 2 if w["ctx"] <= 8192 else 1
-    tok_s, kind, t_layer, _ = cpu_reference_path(w, sample_batch, repeats=max(1, min(args.steps, 3)), threads=threads)
+    tok_s, kind, t_layer, _ = cpu_reference_path(w, sample_batch, repeats=max(5, min(args.steps, 100)), threads=threads)
     n_comp, n_res = split_context(w["ctx"], w["block"])
     sample = (f"1 layer x {sample_batch} sequences of the workload per step (median {t_layer * 1e3:.0f} ms): C++ bit-unpack "
               f"(1 thread) + torch dequantise + eager attention ({threads} threads); tok/s = sequences / (layer time x {w['layers']} layers)")
@@ -446,11 +446,13 @@ def main():
     if rank == 0:
         if not args.no_cpu_baseline:
             t0 = time.perf_counter()
-            tok_s, kind, t_layer, _ = cpu_reference_path(w, 1, repeats=1, threads=os.cpu_count() or 1)
+            nseq = 2 if w["ctx"] <= 8192 else 1
+            reps = 120 if w["ctx"] <= 8192 else 30                     # ~10 s of CPU work: a stable median
+            tok_s, kind, t_layer, _ = cpu_reference_path(w, nseq, repeats=reps, threads=os.cpu_count() or 1)
             line["cpu_baseline"] = {
                 "value": tok_s, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": kind,
-                "sample": f"1 layer x 1 sequence ({t_layer * 1e3:.0f} ms, setup {time.perf_counter() - t0:.0f} s): C++ bit-unpack (1 thread) + "
-                          f"torch dequantise + eager attention (all threads); scaled by {w['layers']} layers"}
+                "sample": f"1 layer x {nseq} sequences, median of {reps} runs ({t_layer * 1e3:.0f} ms each, {time.perf_counter() - t0:.0f} s in all "
+                          f"with set-up): C++ bit-unpack (1 thread) + torch dequantise + eager attention (all threads); scaled by {w['layers']} layers"}
         print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.barrier()
