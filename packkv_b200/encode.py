@@ -49,13 +49,14 @@ def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bi
     if k_mode not in (QuantMode.ChannelQuant, QuantMode.TokenQuant):
         raise RuntimeError("not supported")
     k_shape = (B, H, cap_tok // block, D) if km == ops.K_CHANNEL else (B, cap_tok)
-    k_scale, k_zero = torch.zeros(k_shape, dtype=k.dtype, device=dev), torch.zeros(k_shape, dtype=k.dtype, device=dev)
-    v_scale, v_zero = torch.zeros(B, cap_tok, dtype=k.dtype, device=dev), torch.zeros(B, cap_tok, dtype=k.dtype, device=dev)
+    # parameters and block tables are written by the encoder for every token / block that is ever read: no clearing
+    k_scale, k_zero = torch.empty(k_shape, dtype=k.dtype, device=dev), torch.empty(k_shape, dtype=k.dtype, device=dev)
+    v_scale, v_zero = torch.empty(B, cap_tok, dtype=k.dtype, device=dev), torch.empty(B, cap_tok, dtype=k.dtype, device=dev)
     # streams need no clearing: every byte that is ever read has been written by an encoder
     k_stream = torch.empty(B, stream_capacity("k", cap_tok, H, cbk, bits_k), dtype=torch.uint8, device=dev)
     v_stream = torch.empty(B, stream_capacity("v", cap_tok, H, cbv, bits_v), dtype=torch.uint8, device=dev)
-    k_info = torch.zeros(B, (cap_tok // cbk) * H, 2, dtype=torch.int32, device=dev)
-    v_info = torch.zeros(B, (cap_tok // cbv) * 2 * H, 2, dtype=torch.int32, device=dev)
+    k_info = torch.empty(B, (cap_tok // cbk) * H, 2, dtype=torch.int32, device=dev)
+    v_info = torch.empty(B, (cap_tok // cbv) * 2 * H, 2, dtype=torch.int32, device=dev)
     k_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
     v_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
     if repack_method in (RepackMethod.MEDIAN, RepackMethod.GREEDY):
