@@ -43,8 +43,10 @@ def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bi
     cbv = block if cbv is None else cbv
     cap_tok = max(S, capacity_tokens or 0)
     dev = k.device
+    # one cleared allocation for everything that must start at zero: the two byte counters and the flag word
+    zeros = torch.zeros(2 * B + 1, dtype=torch.int32, device=dev)
     if flags is None:
-        flags = ops.new_flags(dev)
+        flags = zeros[2 * B:]
     km = ops.K_CHANNEL if k_mode == QuantMode.ChannelQuant else ops.K_TOKEN
     if k_mode not in (QuantMode.ChannelQuant, QuantMode.TokenQuant):
         raise RuntimeError("not supported")
@@ -57,8 +59,7 @@ def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bi
     v_stream = torch.empty(B, stream_capacity("v", cap_tok, H, cbv, bits_v), dtype=torch.uint8, device=dev)
     k_info = torch.empty(B, (cap_tok // cbk) * H, 2, dtype=torch.int32, device=dev)
     v_info = torch.empty(B, (cap_tok // cbv) * 2 * H, 2, dtype=torch.int32, device=dev)
-    k_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
-    v_bytes = torch.zeros(B, dtype=torch.int32, device=dev)
+    k_bytes, v_bytes = zeros[:B], zeros[B:2 * B]
     if repack_method in (RepackMethod.MEDIAN, RepackMethod.GREEDY):
         kq = ops.quantize(k, block, k_rel, km, bits=bits_k, high_precision_zero=high_precision_zero, flags=flags,
                           scale=k_scale, zero=k_zero)
