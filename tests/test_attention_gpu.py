@@ -135,3 +135,25 @@ def test_full_size_weights_sum_to_one(cuda_device, shape):
     assert int(flags.item()) == 0
     dd = d.repeat_interleave(G, dim=1)
     assert bool(((out0 - dd).abs() <= tol + eps * dd.abs()).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shift", [4.0, 12.0])
+def test_offset_data_large_zero_points(cuda_device, dtype, shift):
+    """K and V with a common offset: zero-points of a few tens to ~100 (the in-kernel dequantisation adds
+    the zero-point in the element type exactly as the reference does, including its rounding)."""
+    dev = cuda_device
+    B, Hkv, G, n_comp, n_res = 1, 2, 4, 512, 128
+    k, v = synth.synth_kv(B, Hkv, n_comp + n_res, 128, seed=9, dtype=torch.float32, apply_rope=False)
+    k, v = (k + shift).to(dtype), (v - shift).to(dtype)
+    q = synth.synth_q(B, Hkv * G, 128, seed=9, dtype=dtype)
+    layer, kd, vd = layer_from_oracle(k[:, :, :n_comp], v[:, :, :n_comp], block=64, bits_k=4, bits_v=4, k_mode="channel", cbk=64, cbv=64,
+                                      rel_k=1 / 14, rel_v=1 / 14, device=dev)
+    ref = Q.eager_attention(q, torch.cat([kd, k[:, :, n_comp:]], 2), torch.cat([vd, v[:, :, n_comp:]], 2))[:, 0].float()
+    flags = ops.new_flags(dev)
+    out = ops.decode_attention(q[:, :, 0].contiguous().to(dev), layer, k[:, :, n_comp:].contiguous().to(dev), v[:, :, n_comp:].contiguous().to(dev),
+                               n_res, flags=flags, kv_heads=Hkv)
+    torch.cuda.synchronize()
+    assert int(flags.item()) == 0
+    err = ((out.float().cpu() - ref).abs().max() / ref.abs().max()).item()
+    assert err <= TOL, err
