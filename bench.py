@@ -113,7 +113,8 @@ def build_layers(w, device, dtype, head_shard=None):
     for li in range(w["layers"]):
         k, v = synth.synth_kv(w["batch"], w["kv_heads"], w["ctx"], 128, seed=1000 + li, dtype=dtype, device=device, apply_rope=True)
         kw = dict(block=w["block"], bits_k=w["bits_k"], bits_v=w["bits_v"], k_rel=synth.rel_for_bits(w["bits_k"]),
-                  v_rel=synth.rel_for_bits(w["bits_v"]), k_mode=QuantMode.ChannelQuant, cbk=w["cbk"], cbv=w["cbv"])
+                  v_rel=synth.rel_for_bits(w["bits_v"]), k_mode=QuantMode.TokenQuant if w.get("k_mode") == "token" else QuantMode.ChannelQuant,
+                  cbk=w["cbk"], cbv=w["cbv"])
         if head_shard is None:
             layer = encode.compress_kv(k[:, :, :n_comp], v[:, :, :n_comp], **kw)
         else:
@@ -239,7 +240,8 @@ def run_ours(args, w, rank, world, device):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong" if by_heads else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
         "config": {"workload": w["name"], "layers": w["layers"], "batch_per_gpu": B, "context": w["ctx"],
-                   "compressed_tokens": n_comp, "residual_tokens": n_res, "k_quant": "channel", "v_quant": "token",
+                   "compressed_tokens": n_comp, "residual_tokens": n_res, "k_quant": w.get("k_mode", "channel"), "v_quant": "token",
+                   "bits_k": w["bits_k"], "bits_v": w["bits_v"], "block": w["block"],
                    "l2": f"working set {alg_bytes / 1e9:.2f} GB per step and GPU >> 126 MB L2 (no flush needed)",
                    "sharding": "KV heads per rank + NCCL all-gather of outputs" if by_heads else "batch (independent sequences, no collective)"},
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tok/s",
@@ -412,11 +414,17 @@ def main():
     ap.add_argument("--encode-bits", type=int, default=4)
     ap.add_argument("--encode-block", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decode-bits-k", type=int, default=None, help="override the decode workload's K bit width (sweeps)")
+    ap.add_argument("--decode-bits-v", type=int, default=None, help="override the decode workload's V bit width (sweeps)")
+    ap.add_argument("--decode-k-mode", default="channel", choices=["channel", "token"], help="K quantisation parameters (sweeps)")
     ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
                     help="multi-GPU split: independent sequences per rank (weak scaling, no collective) or KV heads per "
                          "rank with an all-gather of the outputs (strong scaling)")
     args = ap.parse_args()
     w = WORKLOADS.get(args.workload)
+    if w is not None and (args.decode_bits_k or args.decode_bits_v or args.decode_k_mode != "channel"):
+        w = dict(w, bits_k=args.decode_bits_k or w["bits_k"], bits_v=args.decode_bits_v or w["bits_v"], k_mode=args.decode_k_mode)
+        w["name"] += f" [override: K {w['bits_k']}-bit {w['k_mode']}, V {w['bits_v']}-bit]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
