@@ -8,7 +8,7 @@ Two artefacts:
   (``packkv_cuda_ext/src/{k,v}_{encode,decode}_cpu.cpp`` and ``src/utils.cpp``) compiled
   with g++ from where the sources lie in the reference checkout, through
   ``oracle/ref_shim.cpp``.  Built only when the checkout is present (environment variable
-  ``PACKKV_REFERENCE``, default ``/root/reference``); a prebuilt copy is reused otherwise.
+  ``PACKKV_REFERENCE`` names it); a prebuilt copy is reused otherwise.
   The reference sources include ``<torch/torch.h>``, so torch's headers and libraries are
   on the compile and link lines; the reference's own build system is not run.
 

@@ -5,7 +5,7 @@
 // (evaluation/evaluation.py:1040-1049), wv_mat_vec_mul + fused_wv (kernels.cu:632-765,
 // fused_kernels.cu:187-261) and, for numerics, the model path's dequantise-then-attend
 // (models/cache/packkv_quant.py:45-85 + models/llama.py:177-212).  Decompressed K/V never go
-// to HBM, and neither do scores or split-K partials.
+// to HBM, and neither do scores or partial results.
 //
 // Numerics follow the reference's rounding points so the result can be compared with its
 // decompress-then-attend path: every K and V element is dequantised to the element type
@@ -15,7 +15,7 @@
 // before the second contraction (llama.py:208-210), which accumulates in fp32.
 //
 // Because the probabilities need the global max and sum before they can be rounded, the
-// sequence is split over a thread-block CLUSTER instead of over independent split-K CTAs:
+// sequence is split over a thread-block CLUSTER instead of over independent CTAs with a later merge:
 // grid = (cluster_size, kv_heads, batch), one cluster per (sequence, KV head).
 //   phase 1  every warp of the cluster walks its 128-token (or 64-token) tiles: K blocks are
 //            staged with cp.async, unpacked, dequantised and contracted with q on the tensor
