@@ -100,7 +100,9 @@ __device__ __forceinline__ unsigned deq2(unsigned biased, typename Tr<T>::T2 z, 
     using T2 = typename Tr<T>::T2;
     T2 x = as_t2<T2>(biased);
     if (!HP) return as_u(__hmul2(__hadd2(x, z), s));          // z = zero - bias
-    return as_u(__hadd2(__hmul2(__hsub2(x, Tr<T>::bias2()), s), z));   // z = min
+    // the product must be rounded before the addition, as in the reference: _rn keeps the compiler from
+    // contracting the pair into one fused multiply-add
+    return as_u(__hadd2(__hmul2_rn(__hsub2(x, Tr<T>::bias2()), s), z));   // z = min
 }
 
 __device__ __forceinline__ void cp_async16(uint8_t* smem_dst, const uint8_t* gsrc) {

@@ -157,3 +157,37 @@ def test_offset_data_large_zero_points(cuda_device, dtype, shift):
     assert int(flags.item()) == 0
     err = ((out.float().cpu() - ref).abs().max() / ref.abs().max()).item()
     assert err <= TOL, err
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k_mode", ["channel", "token"])
+@pytest.mark.parametrize("bits", [4, 3])
+def test_high_precision_zero_point_all_modes(cuda_device, dtype, k_mode, bits):
+    """code * scale + min (utils/compute.py:173-176): the product is rounded before the addition, so the
+    kernel must not let the pair become one fused multiply-add (that alone moves bf16 outputs by 1e-2)."""
+    err = _run_case(cuda_device, dtype, 1, 2, 2, 512, 130, block=64, cbk=64, cbv=64, bits_k=bits, bits_v=bits, k_mode=k_mode, seed=5, hp=True)
+    assert err <= TOL, err
+
+
+def _random_case(it):
+    import random
+    r = random.Random(1000 + it)
+    dtype = r.choice([torch.float16, torch.bfloat16])
+    block = r.choice([64, 64, 128])
+    cbv = r.choice([64, 128]) if block == 64 else 128
+    tile = 128 if (block == 128 or cbv == 128) else 64
+    n_comp = tile * r.choice([0, 1, 2, 3, 5, 8, 13, 24])
+    n_res = r.choice([0, 1, 15, 16, 17, 128, 130, 160, 191]) if n_comp else r.choice([1, 16, 33, 128, 191])
+    return dict(dtype=dtype, B=r.choice([1, 1, 2, 3, 5]), Hkv=r.choice([1, 2, 4, 8]), G=r.choice([1, 2, 3, 4, 5, 7, 8]), n_comp=n_comp,
+                n_res=n_res, block=block, cbk=block, cbv=cbv, bits_k=r.choice([2, 3, 4]), bits_v=r.choice([2, 3, 4]),
+                k_mode=r.choice(["channel", "token"]), hp=r.random() < 0.25)
+
+
+@pytest.mark.parametrize("it", range(24))
+def test_random_shapes(cuda_device, it):
+    """Seeded random draws over batch, heads, group size, lengths (every cluster size and the residual-only
+    and compressed-only corners), block sizes, bit widths, K mode and zero-point mode."""
+    c = _random_case(it)
+    err = _run_case(cuda_device, c["dtype"], c["B"], c["Hkv"], c["G"], c["n_comp"], c["n_res"], block=c["block"], cbk=c["cbk"], cbv=c["cbv"],
+                    bits_k=c["bits_k"], bits_v=c["bits_v"], k_mode=c["k_mode"], seed=200 + it, hp=c["hp"])
+    assert err <= TOL, (c, err)
