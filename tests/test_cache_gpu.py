@@ -59,6 +59,38 @@ def test_prefill_then_decode_matches_reference_cache(cuda_device, method, repack
         C.PackKVCacheConfigStatic.config = None
 
 
+@pytest.mark.parametrize("method", [QuantMethod.KIVI, QuantMethod.PackKV])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_high_precision_zero_and_three_bit_cache(cuda_device, method, dtype):
+    """high_precision_zero_point=True (zero = block minimum, utils/compute.py:97-101) with 3-bit scales:
+    dense views bit-identical to the reference cache, fused attention within 2e-3."""
+    dev = cuda_device
+    B, H, G, S0, steps = 1, 2, 4, 260, 70
+    cfg = _cfg(method, k_rel=1 / 6, v_rel=1 / 6, hp=True)
+    C.PackKVCacheConfigStatic.config = cfg
+    try:
+        cache = C.PackKVCache(B, H * G, 128, 1, materialize=True)
+        km, vm = _modes(method)
+        oracle = Q.CacheLayerOracle(64, 192, 1 / 6, 1 / 6, km, vm, high_precision_zero=True)
+        k, v = synth.synth_kv(B, H, S0 + steps, 128, seed=37, dtype=dtype)
+        cos, sin = synth.rope_tables(S0 + steps, 128, dtype=dtype)
+        Ko, Vo = oracle.update(k[:, :, :S0], v[:, :, :S0], cos[:, :S0], sin[:, :S0])
+        Kg, Vg = cache.update(k[:, :, :S0].to(dev), v[:, :, :S0].to(dev), 0, {"cos": cos[:, :S0].to(dev), "sin": sin[:, :S0].to(dev)})
+        assert torch.equal(Kg.cpu(), Ko) and torch.equal(Vg.cpu(), Vo)
+        for t in range(S0, S0 + steps):
+            Ko, Vo = oracle.update(k[:, :, t:t + 1], v[:, :, t:t + 1], cos[:, t:t + 1], sin[:, t:t + 1])
+            Kg, Vg = cache.update(k[:, :, t:t + 1].to(dev), v[:, :, t:t + 1].to(dev), 0,
+                                  {"cos": cos[:, t:t + 1].to(dev), "sin": sin[:, t:t + 1].to(dev)})
+        assert torch.equal(Kg.cpu(), Ko) and torch.equal(Vg.cpu(), Vo)
+        q = synth.synth_q(B, H * G, 128, seed=3, dtype=dtype)
+        ref = Q.eager_attention(q, Ko, Vo).float()
+        out = cache.attend(q.to(dev), 0).float().cpu()
+        assert ((out - ref).abs().max() / ref.abs().max()).item() <= 2e-3
+        cache._check_flags()
+    finally:
+        C.PackKVCacheConfigStatic.config = None
+
+
 def test_append_streams_equal_one_shot_encode(cuda_device):
     """Blocks appended one at a time give the same bytes as encoding the history in one call."""
     from packkv_b200 import encode, ops
