@@ -80,3 +80,33 @@ def test_append_in_pieces_equals_one_call_and_flags(cuda_device):
     ops.encode_tensor("k", k, 64, 1 / 14, ops.K_CHANNEL, 4, 64, **small)
     torch.cuda.synchronize()
     assert int(bufs["flags"].item()) & 2 and int(small["flags"].item()) & 1
+
+
+@pytest.mark.parametrize("layout", ["bshd", "sliced", "padded_heads"])
+@pytest.mark.parametrize("which,mode", [("k", ops.K_CHANNEL), ("k", ops.K_TOKEN), ("v", ops.K_TOKEN)])
+def test_strided_inputs(cuda_device, layout, which, mode):
+    """Inputs that are views of larger or differently ordered buffers (token-major memory, a window of a
+    longer sequence, a subset of heads): same bytes as for the contiguous tensor."""
+    dev, dtype = cuda_device, torch.bfloat16
+    B, H, S, cb, bits = 2, 3, 192, 64, 4
+    k, v = synth.synth_kv(B, H, S, 128, seed=47, dtype=dtype, apply_rope=True)
+    x = (k if which == "k" else v).to(dev)
+    if layout == "bshd":
+        xs = x.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    elif layout == "sliced":
+        big = torch.zeros(B, H, S + 2 * cb, 128, dtype=dtype, device=dev)
+        big[:, :, cb:cb + S] = x
+        xs = big[:, :, cb:cb + S]
+    else:
+        big = torch.zeros(B, H + 2, S, 128, dtype=dtype, device=dev)
+        big[:, 1:H + 1] = x
+        xs = big[:, 1:H + 1]
+    assert not xs.is_contiguous() and torch.equal(xs, x)
+    rel = synth.rel_for_bits(bits)
+    a, b = _bufs(B, H, S, cb, bits, which, mode, dtype, dev), _bufs(B, H, S, cb, bits, which, mode, dtype, dev)
+    ops.encode_tensor(which, x, cb, rel, mode, bits, cb, **a)
+    ops.encode_tensor(which, xs, cb, rel, mode, bits, cb, **b)
+    torch.cuda.synchronize()
+    assert int(a["flags"].item()) == 0 and int(b["flags"].item()) == 0
+    for name in ("stream", "info", "stream_bytes", "scale", "zero"):
+        assert torch.equal(a[name].view(torch.uint8), b[name].view(torch.uint8)), name
