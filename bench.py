@@ -2,11 +2,12 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload llama8b]
 
-Workload (default, N=1): Llama-3.1-8B-shaped decode attention -- 32 layers, 32 q heads / 8 KV
-heads, head_dim 128, bf16, batch 16, context 8192 (8064 compressed tokens + 128 uncompressed
-residual tokens per the cache's cut rule), K per-channel 4 bit, V per-token 4 bit, block 64.
-Synthetic KV (packkv_b200.synth) stands in for real-model caches.  One STEP = one decode step's
-attention for all layers = 32 launches of the fused kernel producing `batch` tokens.
+Workload (default): Llama-3.1-8B-shaped decode attention -- 32 layers, 32 q heads / 8 KV heads,
+head_dim 128, bf16, batch 16, context 8192 (8064 compressed tokens + 128 uncompressed residual
+tokens per the cache's cut rule), K per-channel 4 bit in 64-token blocks, V per-token 4 bit packed
+in 128-token blocks: the stream layouts the reference's codec writes and reads.  Synthetic KV
+(packkv_b200.synth) stands in for real-model caches.  One STEP = one decode step's attention for
+all layers = 32 launches of the fused kernel producing `batch` tokens.
 
 Multi-GPU (torchrun, one rank per GPU): sequences are independent, so the batch is sharded with
 no data-path collective; every rank holds a full `batch` of sequences (weak scaling) and the
@@ -14,8 +15,13 @@ reported value is (all ranks' tokens) / (max over ranks of the device time).
 
 JSON line: metric decode tok/s; `value` with q/out resident in HBM; `e2e` through the public
 API with q in pinned host memory and the output read back every layer; `roofline` on the
-algorithmic compressed bytes of the fused kernel; `cpu_baseline` = the reference's own CPU path
-(C++ bit-unpack + torch dequantise + eager attention) on a bounded sample.
+algorithmic compressed bytes of the fused kernel; `cpu_baseline` (one GPU only) = the reference's
+own CPU path (C++ bit-unpack + torch dequantise + eager attention) on a bounded sample.  The
+default workload's line also carries the other parts of the metric as extra keys:
+`v_block_64` (the same decode with 64-token V blocks), `encode` (Mistral-7B-shaped KV encode, 64
+sequences x 16384 tokens split over the ranks, with and without the median reorder, and the
+single-token append) and, on more than one GPU, `head_sharded` (the long-context workload split
+by KV heads with the output exchange).
 """
 from __future__ import annotations
 
@@ -35,21 +41,23 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     # name: layers, batch, q_heads, kv_heads, ctx, dtype, bits_k, bits_v, block, cbk, cbv
     "llama8b": dict(layers=32, batch=16, q_heads=32, kv_heads=8, ctx=8192, dtype="bf16", bits_k=4, bits_v=4,
-                    block=64, cbk=64, cbv=64, name="llama-3.1-8b-shaped decode attention, batch 16, ctx 8192, 4-bit K/V, block 64"),
+                    block=64, cbk=64, cbv=128, name="llama-3.1-8b-shaped decode attention, batch 16, ctx 8192, 4-bit K/V, block 64"),
     "qwen8b-long": dict(layers=36, batch=8, q_heads=32, kv_heads=8, ctx=32768, dtype="bf16", bits_k=2, bits_v=4,
                         block=128, cbk=128, cbv=128, name="qwen3-8b-shaped decode attention, batch 8, ctx 32768, 2-bit K / 4-bit V, block 128"),
     "llama8b-2l": dict(layers=2, batch=16, q_heads=32, kv_heads=8, ctx=8192, dtype="bf16", bits_k=4, bits_v=4,
-                       block=64, cbk=64, cbv=64, name="2 layers of the llama-3.1-8b-shaped workload (profiling case)"),
+                       block=64, cbk=64, cbv=128, name="2 layers of the llama-3.1-8b-shaped workload (profiling case)"),
     "tiny": dict(layers=2, batch=2, q_heads=8, kv_heads=2, ctx=1024, dtype="bf16", bits_k=4, bits_v=4,
                  block=64, cbk=64, cbv=64, name="tiny smoke workload"),
 }
 RECENT = 192   # buffer_size of every reference script (128 + 64)
+MIN_TIMED_S = 1.0   # the timed region is repeated until it is at least this long
 
-# dram__bytes_read.sum + dram__bytes_write.sum from the ncu captures summarised under profiles/
-# (per launch for the attention kernel, per step for the encoder); only captured shapes have an entry
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch (attention) or one step (encoder) from the ncu
+# captures summarised under profiles/.  An entry is valid for one revision of the kernel only (the revision is
+# a constant of packkv_b200.ops that changes with the kernel): other revisions report null.
 NCU_TRAFFIC_BYTES = {
-    ("attn", 16, 8192, 8, 4, 4, 64): 158.5e6,        # profiles/attn_decode_kernel_llama8b.md
-    ("mistral7b-encode", 16, 4, 64): 1836e6,          # profiles/fused_encode_kernels_mistral7b.md
+    ("attn", 2, 16, 8192, 8, 4, 4, 64, 128): None,
+    ("encode", 1, 16, 4, 64): 1836e6,
 }
 
 
@@ -104,6 +112,33 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def timed_batches(fn, steps: int, world: int, device, min_seconds: float = MIN_TIMED_S, max_batches: int = 400):
+    """Times batches of `steps` calls of fn with CUDA events on the current stream (barrier and synchronize on
+    both sides of every batch, max over ranks) until the batches add up to min_seconds.  Returns
+    (median batch ms, number of batches, total ms)."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    batches = []
+    while len(batches) < max_batches:
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        batches.append(ms)
+        if sum(batches) >= min_seconds * 1e3:       # the same decision on every rank: ms is the max over ranks
+            break
+    s = sorted(batches)
+    return s[len(s) // 2], len(batches), sum(batches)
+
+
 # ------------------------------------------------------------------------------------------------
 def build_layers(w, device, dtype, head_shard=None):
     from packkv_b200 import encode, parallel, synth
@@ -115,6 +150,7 @@ def build_layers(w, device, dtype, head_shard=None):
         kw = dict(block=w["block"], bits_k=w["bits_k"], bits_v=w["bits_v"], k_rel=synth.rel_for_bits(w["bits_k"]),
                   v_rel=synth.rel_for_bits(w["bits_v"]), k_mode=QuantMode.TokenQuant if w.get("k_mode") == "token" else QuantMode.ChannelQuant,
                   cbk=w["cbk"], cbv=w["cbv"])
+        # the V token block may exceed the quantisation block: only whole V blocks are compressed
         if head_shard is None:
             layer = encode.compress_kv(k[:, :, :n_comp], v[:, :, :n_comp], **kw)
         else:
@@ -141,129 +177,129 @@ def layer_bytes(layer, k_res, v_res, n_res, batch, q_heads):
     return n
 
 
-def run_ours(args, w, rank, world, device):
-    from packkv_b200 import ops
-    from packkv_b200 import parallel
+def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e2e=True, sample_clocks=True, exchange="nccl"):
+    """Builds the workload's compressed layers on this rank and times decode steps.  Returns a dict of raw
+    measurements (milliseconds are per step, max over ranks)."""
+    from packkv_b200 import ops, parallel
     dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
-    by_heads = args.shard == "heads" and world > 1
+    by_heads = by_heads and world > 1
     layers, n_comp, n_res = build_layers(w, device, dtype, head_shard=(rank, world) if by_heads else None)
     B, Hq = w["batch"], w["q_heads"] // (world if by_heads else 1)
-    gather_buf = torch.empty(world, B, Hq, 128, dtype=dtype, device=device) if by_heads else None
-    g = torch.Generator(device=device).manual_seed(77 + rank)
-    q_dev = [torch.randn(B, Hq, 128, generator=g, device=device, dtype=torch.float32).to(dtype) for _ in layers]
+    g = torch.Generator(device=device).manual_seed(77 + (0 if by_heads else rank))
+    q_full = [torch.randn(B, w["q_heads"] if by_heads else Hq, 128, generator=g, device=device, dtype=torch.float32).to(dtype) for _ in layers]
+    q_dev = [q[:, rank * Hq:(rank + 1) * Hq].contiguous() if by_heads else q for q in q_full]
     out_dev = [torch.empty_like(q) for q in q_dev]
     flags = ops.new_flags(device)
     alg_bytes = sum(layer_bytes(L, kr, vr, n_res, B, Hq) for L, kr, vr in layers)
+    xchg = parallel.HeadExchange(B, Hq, world, dtype, device, mode=exchange) if by_heads else None
 
     def step_resident():
         for (L, kr, vr), q, o in zip(layers, q_dev, out_dev):
             ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags)
             if by_heads:
-                parallel.gather_heads(o, buffer=gather_buf)
+                xchg.gather(o)
 
-    q_host = [q.cpu().pin_memory() for q in q_dev]
-    out_host = [torch.empty(B, Hq, 128, dtype=dtype).pin_memory() for _ in layers]
-    # End to end: every layer's q comes from pinned host memory and every layer's output goes back to
-    # it.  The copies run on two side streams (double-buffered staging of q), so the upload of layer
-    # l+1 and the download of layer l-1 overlap the kernel of layer l; all of them are inside the
-    # timed region, which ends only after the last download.
-    q_stage = [torch.empty(B, Hq, 128, dtype=dtype, device=device) for _ in range(2)]
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_free = [torch.cuda.Event() for _ in range(2)]
-    ev_done = [torch.cuda.Event() for _ in layers]
-
-    def upload(i):
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(ev_free[i % 2])                  # the kernel that last read this staging buffer
-            q_stage[i % 2].copy_(q_host[i], non_blocking=True)
-            ev_in[i % 2].record(s_in)
-
-    def step_e2e():
-        main = torch.cuda.current_stream()
-        for e in ev_free:
-            e.record(main)
-        upload(0)
-        for i, ((L, kr, vr), oh, o) in enumerate(zip(layers, out_host, out_dev)):
-            if i + 1 < len(layers):
-                upload(i + 1)
-            main.wait_event(ev_in[i % 2])
-            ops.decode_attention(q_stage[i % 2], L, kr, vr, n_res, out=o, flags=flags)
-            ev_free[i % 2].record(main)
-            if by_heads:
-                parallel.gather_heads(o, buffer=gather_buf)
-            ev_done[i].record(main)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_done[i])
-                oh.copy_(o, non_blocking=True)
-        main.wait_stream(s_out)
-
-    def timed(fn, steps):
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-        start.record()
-        for _ in range(steps):
-            fn()
-        end.record()
-        torch.cuda.synchronize()
-        ms = start.elapsed_time(end)
-        if world > 1:
-            t = torch.tensor([ms], device=device)
-            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    for _ in range(max(args.warmup, 3)):
+    res = {"n_comp": n_comp, "n_res": n_res, "layers": len(layers), "batch": B, "q_heads_local": Hq, "alg_bytes": alg_bytes}
+    for _ in range(max(warmup, 3)):
         step_resident()
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    ms = timed(step_resident, args.steps)
-    clocks = sampler.stop()
-    if clocks["samples"] < 2:
-        # the timed region was shorter than the sampling period: sample an untimed repeat of the same steps
+    sampler = None
+    if sample_clocks:
         sampler = ClockSampler(torch.cuda.current_device())
         sampler.start()
-        t_end = time.perf_counter() + 0.8
-        while time.perf_counter() < t_end:
-            step_resident()
-            torch.cuda.synchronize()
-        clocks = sampler.stop()
-        clocks["note"] = "sampled during an untimed repeat of the timed steps (the timed region was shorter than the sampling period)"
-    for _ in range(2):
-        step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
+    ms, nb, total = timed_batches(step_resident, steps, world, device)
+    if sampler is not None:
+        res["clocks"] = sampler.stop()
+        res["clocks"]["timed_region_s"] = round(total / 1e3, 3)
+    res.update(ms_per_step=ms / steps, batches=nb, launches=len(layers) * steps * nb)
+
+    if by_heads:
+        # the exchange alone (same buffers, no kernels), and the sharded result against one full-head layer
+        ms_x, _, _ = timed_batches(lambda: [xchg.gather(o) for o in out_dev], steps, world, device, min_seconds=0.2)
+        res["exchange_ms_per_step"] = ms_x / steps
+        res["check"] = parallel.check_against_full(w, rank, world, device, dtype, layers[0], q_full[0], n_comp, n_res, xchg, flags)
+
+    if with_e2e:
+        # End to end: every layer's q comes from pinned host memory and every layer's output goes back to
+        # it.  The copies run on two side streams (double-buffered staging of q), so the upload of layer
+        # l+1 and the download of layer l-1 overlap the kernel of layer l; all of them are inside the
+        # timed region, which ends only after the last download.
+        q_host = [q.cpu().pin_memory() for q in q_dev]
+        out_host = [torch.empty(B, Hq, 128, dtype=dtype).pin_memory() for _ in layers]
+        q_stage = [torch.empty(B, Hq, 128, dtype=dtype, device=device) for _ in range(2)]
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_free = [torch.cuda.Event() for _ in range(2)]
+        ev_done = [torch.cuda.Event() for _ in layers]
+
+        def upload(i):
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_free[i % 2])                  # the kernel that last read this staging buffer
+                q_stage[i % 2].copy_(q_host[i], non_blocking=True)
+                ev_in[i % 2].record(s_in)
+
+        def step_e2e():
+            main = torch.cuda.current_stream()
+            for e in ev_free:
+                e.record(main)
+            upload(0)
+            for i, ((L, kr, vr), oh, o) in enumerate(zip(layers, out_host, out_dev)):
+                if i + 1 < len(layers):
+                    upload(i + 1)
+                main.wait_event(ev_in[i % 2])
+                ops.decode_attention(q_stage[i % 2], L, kr, vr, n_res, out=o, flags=flags)
+                ev_free[i % 2].record(main)
+                if by_heads:
+                    xchg.gather(o)
+                ev_done[i].record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[i])
+                    oh.copy_(o, non_blocking=True)
+            main.wait_stream(s_out)
+
+        for _ in range(2):
+            step_e2e()
+        ms_e, _, _ = timed_batches(step_e2e, steps, world, device)
+        res["ms_per_step_e2e"] = ms_e / steps
     torch.cuda.synchronize()
     if int(flags.item()) != 0:
         raise RuntimeError(f"device flags set: {int(flags.item())}")
+    return res
 
+
+def decode_line(args, w, rank, world, device):
+    from packkv_b200 import ops
+    m = time_decode(w, args.steps, args.warmup, rank, world, device, by_heads=args.shard == "heads", with_e2e=True)
     if rank != 0:
         return None
-    ms_per_step = ms / args.steps
+    by_heads = args.shard == "heads" and world > 1
+    B, L = m["batch"], m["layers"]
     tokens = B if by_heads else B * world
     peak, peak_kind = measured_peak_gbs()
-    per_launch_ms = ms_per_step / len(layers)
-    achieved = (alg_bytes / len(layers)) / (per_launch_ms * 1e-3) / 1e9
+    per_launch_ms = m["ms_per_step"] / L
+    achieved = (m["alg_bytes"] / L) / (per_launch_ms * 1e-3) / 1e9
+    traffic = None if by_heads else NCU_TRAFFIC_BYTES.get(
+        ("attn", ops.ATTN_KERNEL_REVISION, B, w["ctx"], w["kv_heads"], w["bits_k"], w["bits_v"], w["cbk"], w["cbv"]))
     line = {
-        "metric": "fused decompress-attention decode throughput", "value": tokens / (ms_per_step * 1e-3), "unit": "tok/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "metric": "fused decompress-attention decode throughput", "value": tokens / (m["ms_per_step"] * 1e-3), "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": m["ms_per_step"],
         "higher_is_better": True, "scaling": "strong" if by_heads else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-        "config": {"workload": w["name"], "layers": w["layers"], "batch_per_gpu": B, "context": w["ctx"],
-                   "compressed_tokens": n_comp, "residual_tokens": n_res, "k_quant": w.get("k_mode", "channel"), "v_quant": "token",
+        "config": {"workload": w["name"], "layers": L, "batch_per_gpu": B, "context": w["ctx"],
+                   "compressed_tokens": m["n_comp"], "residual_tokens": m["n_res"], "k_quant": w.get("k_mode", "channel"), "v_quant": "token",
                    "bits_k": w["bits_k"], "bits_v": w["bits_v"], "block": w["block"],
-                   "l2": f"working set {alg_bytes / 1e9:.2f} GB per step and GPU >> 126 MB L2 (no flush needed)",
-                   "sharding": "KV heads per rank + NCCL all-gather of outputs" if by_heads else "batch (independent sequences, no collective)"},
-        "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tok/s",
-                "h2d_bytes_per_step": len(layers) * B * Hq * 128 * 2, "d2h_bytes_per_step": len(layers) * B * Hq * 128 * 2},
-        "gpu_launches": len(layers) * args.steps,
+                   "stream_layout": f"K blocks of {w['cbk']} tokens x 128 channels, V blocks of {w['cbv']} tokens x 64 channels"
+                                    + (" (the reference codec's V layout)" if w["cbv"] == 128 else " (no reference bitstream for this V layout)"),
+                   "timed_batches": m["batches"],
+                   "l2": f"working set {m['alg_bytes'] / 1e9:.2f} GB per step and GPU >> 126 MB L2 (no flush needed)",
+                   "sharding": "KV heads per rank + exchange of outputs" if by_heads else "batch (independent sequences, no collective)"},
+        "e2e": {"value": tokens / (m["ms_per_step_e2e"] * 1e-3), "unit": "tok/s",
+                "h2d_bytes_per_step": L * B * m["q_heads_local"] * 128 * 2, "d2h_bytes_per_step": L * B * m["q_heads_local"] * 128 * 2},
+        "gpu_launches": m["launches"],
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_source": peak_kind,
-                     "traffic": None if by_heads else NCU_TRAFFIC_BYTES.get(("attn", B, w["ctx"], w["kv_heads"], w["bits_k"], w["bits_v"], w["block"])),
-                     "algorithmic_bytes_per_launch": alg_bytes // len(layers), "kernel": "attn_decode_kernel",
+                     "peak_source": peak_kind, "traffic": traffic,
+                     "algorithmic_bytes_per_launch": m["alg_bytes"] // L, "kernel": "attn_decode_kernel",
                      "avg_launch_ms": per_launch_ms},
         "compressed_kv_gbs": achieved,
-        "clocks": clocks,
+        "clocks": m["clocks"],
     }
     return line
 
@@ -271,7 +307,8 @@ def run_ours(args, w, rank, world, device):
 # ------------------------------------------------------------------------------------------------
 def cpu_reference_path(w, sample_batch: int, repeats: int, threads: int):
     """The reference's CPU path for one layer of `sample_batch` sequences: bit-unpack with its
-    C++ codec (single-threaded by construction), dequantise and eager attention in torch."""
+    C++ codec (single-threaded by construction), dequantise and eager attention in torch.
+    Returns (codec kind, list of seconds per run)."""
     import numpy as np
     from oracle import codec
     from oracle import quant as Q
@@ -310,24 +347,27 @@ def cpu_reference_path(w, sample_batch: int, repeats: int, threads: int):
         vq = torch.stack(vd_list).to(dtype).reshape(sample_batch, w["kv_heads"], -1, w["block"], 128)
         K = torch.cat([Q.dequant(kq, kz, ks), k[:, :, n_comp:]], 2)
         V = torch.cat([Q.dequant(vq, vz, vs), v[:, :, n_comp:]], 2)
-        out = Q.eager_attention(q, K, V)
+        Q.eager_attention(q, K, V)
         times.append(time.perf_counter() - t0)
-    times.sort()
-    t_layer = times[len(times) // 2]
-    tok_s = sample_batch / (t_layer * w["layers"])
-    return tok_s, kind, t_layer, float(out.float().abs().max())
+    return kind, times
 
 
 def run_reference(args, w):
+    """The reference arm: one STEP = the reference's CPU path over ALL sequences of ONE layer of the workload
+    (that is what ms_per_step times); the decode rate of the whole model is that time times the layer count."""
     threads = os.cpu_count() or 1
-    sample_batch = 2 if w["ctx"] <= 8192 else 1
-    tok_s, kind, t_layer, _ = cpu_reference_path(w, sample_batch, repeats=max(5, min(args.steps, 100)), threads=threads)
+    seqs = w["batch"]
+    kind, times = cpu_reference_path(w, seqs, repeats=max(1, args.warmup) + args.steps, threads=threads)
+    times = sorted(times[max(1, args.warmup):])
+    t_layer = times[len(times) // 2]
+    tok_s = seqs / (t_layer * w["layers"])
     n_comp, n_res = split_context(w["ctx"], w["block"])
-    sample = (f"1 layer x {sample_batch} sequences of the workload per step (median {t_layer * 1e3:.0f} ms): C++ bit-unpack "
-              f"(1 thread) + torch dequantise + eager attention ({threads} threads); tok/s = sequences / (layer time x {w['layers']} layers)")
+    sample = (f"one step = 1 layer x all {seqs} sequences of the workload (median {t_layer * 1e3:.0f} ms over {len(times)} steps): C++ bit-unpack "
+              f"(1 thread) + torch dequantise + eager attention ({threads} threads); tok/s = sequences / (step time x {w['layers']} layers)")
     return {
         "impl": "reference", "metric": "fused decompress-attention decode throughput", "value": tok_s, "unit": "tok/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_layer * w["layers"] * 1e3,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_layer * 1e3,
+        "step_is": "one layer of the workload", "layers_per_token": w["layers"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
         "config": {"workload": w["name"], "layers": w["layers"], "batch_per_gpu": w["batch"], "context": w["ctx"],
                    "compressed_tokens": n_comp, "residual_tokens": n_res, "k_quant": "channel", "v_quant": "token"},
@@ -337,124 +377,122 @@ def run_reference(args, w):
     }
 
 
-def run_encode(args, rank, world, device):
-    """Encoder / append throughput on Mistral-7B-shaped KV: prefill-encode `batch` sequences of
-    16384 tokens (K per-channel, V per-token, fp16), then append one token per step through the
-    cache class.  Algorithmic bytes = fp16 K and V read + streams, block tables and parameters
-    written.  Sequences are sharded over ranks (weak scaling, no collective)."""
+# ------------------------------------------------------------------------------------------------
+def encode_leg(steps, warmup, rank, world, device, *, total_seqs=64, bits=4, block=64, with_median=True, with_e2e=True, with_append=True):
+    """Encoder / append throughput on Mistral-7B-shaped KV (8 KV heads x 128, fp16): prefill-encode `total_seqs`
+    sequences of 16384 tokens split evenly over the ranks (K per-channel, V per-token), without and with the
+    median token reorder, then append one token per step for 512 steps through the cache class.  Algorithmic
+    bytes = fp16 K and V read + streams, block tables and parameters written.  No collective: the value is
+    (all ranks' bytes) / (max over ranks of the device time)."""
     from packkv_b200 import cache as C
     from packkv_b200 import encode, synth
     from packkv_b200.config import PackKVCacheConfig, QuantMethod, QuantMode, RepackMethod
-    B, H, S, bits, block = args.encode_batch, 8, 16384, args.encode_bits, args.encode_block
+    B, H, S = max(1, total_seqs // world), 8, 16384
     dtype = torch.float16
     k, v = synth.synth_kv(B, H, S, 128, seed=3000 + rank, dtype=dtype, device=device, apply_rope=True)
     rel = synth.rel_for_bits(bits)
     kw = dict(block=block, bits_k=bits, bits_v=bits, k_rel=rel, v_rel=rel, k_mode=QuantMode.ChannelQuant)
-
-    def timed(fn, steps):
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-        start.record()
-        for _ in range(steps):
-            fn()
-        end.record()
-        torch.cuda.synchronize()
-        ms = start.elapsed_time(end)
-        if world > 1:
-            t = torch.tensor([ms], device=device)
-            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    layer = None
-    for _ in range(max(args.warmup, 3)):
-        layer = encode.compress_kv(k, v, **kw)
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    ms = timed(lambda: encode.compress_kv(k, v, **kw), args.steps) / args.steps
-    clocks = sampler.stop()
-    src_bytes = 2 * k.numel() * 2
-    out_bytes = layer.stream_bytes()
-    alg = src_bytes + out_bytes
-    # append: 512 single-token steps on a cache prefilled with 1024 tokens
-    C.PackKVCacheConfigStatic.config = PackKVCacheConfig("synthetic", QuantMethod.KIVI, RepackMethod.NONE, False, block, 128 + block, 16, rel, rel)
-    cache = C.PackKVCache(B, H, 128, 1)
-    cos, sin = synth.rope_tables(1024 + 512, 128, device=device, dtype=dtype)
-    cache.update(k[:, :, :1024], v[:, :, :1024], 0, {"cos": cos[:, :1024], "sin": sin[:, :1024]})
-    pos = [1024]
-
-    def append_step():
-        t = pos[0]
-        cache.update(k[:, :, t:t + 1], v[:, :, t:t + 1], 0, {"cos": cos[:, t:t + 1], "sin": sin[:, t:t + 1]})
-        pos[0] += 1
-    ms_append = timed(append_step, 512) / 512
-    cache._check_flags()
-    C.PackKVCacheConfigStatic.config = None
-    # end to end: K and V start in pinned host memory, the streams and their byte counts go back to it
-    k_host, v_host = k.cpu().pin_memory(), v.cpu().pin_memory()
-    ks_host = torch.empty(layer.k_stream.shape, dtype=torch.uint8).pin_memory()
-    vs_host = torch.empty(layer.v_stream.shape, dtype=torch.uint8).pin_memory()
-    nb_host = torch.empty(2, B, dtype=torch.int32).pin_memory()
-    k_dev, v_dev = torch.empty_like(k), torch.empty_like(v)
-
-    def step_e2e():
-        k_dev.copy_(k_host, non_blocking=True)
-        v_dev.copy_(v_host, non_blocking=True)
-        L = encode.compress_kv(k_dev, v_dev, **kw)
-        ks_host.copy_(L.k_stream, non_blocking=True)
-        vs_host.copy_(L.v_stream, non_blocking=True)
-        nb_host[0].copy_(L.k_bytes, non_blocking=True)
-        nb_host[1].copy_(L.v_bytes, non_blocking=True)
-    step_e2e()
-    e2e_steps = max(1, min(args.steps, 5))
-    ms_e2e = timed(step_e2e, e2e_steps) / e2e_steps
-    if rank != 0:
-        return None
     peak, peak_kind = measured_peak_gbs()
-    achieved = alg / (ms * 1e-3) / 1e9
-    return {
-        "metric": "KV encode throughput", "value": world * alg / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"mistral-7b-shaped KV encode: {B} sequences x 16384 tokens x 8 KV heads x 128 per GPU, {bits}-bit, block {block}",
-                   "l2": f"{alg / 1e9:.2f} GB per step >> 126 MB L2"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                     "traffic": NCU_TRAFFIC_BYTES.get(("mistral7b-encode", B, bits, block)), "algorithmic_bytes_per_step": alg,
-                     "kernel": "k/v_fused_encode_kernel + scan_sizes_kernel + compact_kernel (K and V): 6 launches per step"},
-        "source_fp16_gbs": world * src_bytes / (ms * 1e-3) / 1e9,
-        "compressed_over_fp16": out_bytes / src_bytes,
-        "append": {"ms_per_token_step": ms_append, "sequences": B, "steps": 512,
-                   "tokens_per_s": world * B / (ms_append * 1e-3)},
-        "e2e": {"value": world * alg / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": src_bytes,
-                "d2h_bytes_per_step": int(layer.k_stream.numel() + layer.v_stream.numel() + 8 * B)},
-        "gpu_launches": 7 * args.steps, "clocks": clocks,
-    }
+    src_bytes = 2 * k.numel() * 2
+    out = {"config": {"workload": f"mistral-7b-shaped KV encode: {B * world} sequences x 16384 tokens x 8 KV heads x 128 over {world} GPU(s), "
+                                  f"fp16, {bits}-bit, block {block}", "sequences_per_gpu": B,
+                      "l2": f"{2 * src_bytes / 1e9:.2f} GB per step and GPU >> 126 MB L2"}}
+    for name, method in (("plain", RepackMethod.NONE), ("median", RepackMethod.MEDIAN)):
+        if method == RepackMethod.MEDIAN and not with_median:
+            continue
+        layer = None
+        for _ in range(max(warmup, 3)):
+            layer = encode.compress_kv(k, v, repack_method=method, **kw)
+        ms, nb, _ = timed_batches(lambda: encode.compress_kv(k, v, repack_method=method, **kw), max(1, min(steps, 10)), world, device, min_seconds=0.5)
+        ms /= max(1, min(steps, 10))
+        out_bytes = layer.stream_bytes() + (0 if layer.order is None else layer.order.numel())
+        alg = src_bytes + out_bytes
+        achieved = alg / (ms * 1e-3) / 1e9
+        out[name] = {"value": world * achieved, "unit": "GB/s", "ms_per_step": ms, "source_fp16_gbs": world * src_bytes / (ms * 1e-3) / 1e9,
+                     "compressed_over_fp16": out_bytes / src_bytes,
+                     "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                                  "peak_source": peak_kind, "algorithmic_bytes_per_step": alg,
+                                  "traffic": NCU_TRAFFIC_BYTES.get(("encode", ENCODE_REVISION, B, bits, block)) if method == RepackMethod.NONE else None}}
+        del layer
+    if with_append:
+        # append: 512 single-token steps on a cache prefilled with 1024 tokens
+        C.PackKVCacheConfigStatic.config = PackKVCacheConfig("synthetic", QuantMethod.KIVI, RepackMethod.NONE, False, block, 128 + block, 16, rel, rel)
+        cache = C.PackKVCache(B, H, 128, 1)
+        cos, sin = synth.rope_tables(1024 + 512 + 4, 128, device=device, dtype=dtype)
+        cache.update(k[:, :, :1024], v[:, :, :1024], 0, {"cos": cos[:, :1024], "sin": sin[:, :1024]})
+        pos = [1024]
+
+        def append_step():
+            t = pos[0]
+            cache.update(k[:, :, t:t + 1], v[:, :, t:t + 1], 0, {"cos": cos[:, t:t + 1], "sin": sin[:, t:t + 1]})
+            pos[0] += 1
+        for _ in range(3):
+            append_step()
+        ms_append, _, _ = timed_batches(append_step, 512, world, device, min_seconds=0.0, max_batches=1)
+        ms_append /= 512
+        cache.check_flags()
+        C.PackKVCacheConfigStatic.config = None
+        out["append"] = {"us_per_token_step": ms_append * 1e3, "sequences_per_gpu": B, "steps": 512,
+                         "token_appends_per_s": world * B / (ms_append * 1e-3)}
+    if with_e2e:
+        # end to end: K and V start in pinned host memory, the streams and their byte counts go back to it
+        layer = encode.compress_kv(k, v, **kw)
+        k_host, v_host = k.cpu().pin_memory(), v.cpu().pin_memory()
+        ks_host = torch.empty(layer.k_stream.shape, dtype=torch.uint8).pin_memory()
+        vs_host = torch.empty(layer.v_stream.shape, dtype=torch.uint8).pin_memory()
+        nb_host = torch.empty(2, B, dtype=torch.int32).pin_memory()
+        k_dev, v_dev = torch.empty_like(k), torch.empty_like(v)
+
+        def step_e2e():
+            k_dev.copy_(k_host, non_blocking=True)
+            v_dev.copy_(v_host, non_blocking=True)
+            L = encode.compress_kv(k_dev, v_dev, **kw)
+            ks_host.copy_(L.k_stream, non_blocking=True)
+            vs_host.copy_(L.v_stream, non_blocking=True)
+            nb_host[0].copy_(L.k_bytes, non_blocking=True)
+            nb_host[1].copy_(L.v_bytes, non_blocking=True)
+        step_e2e()
+        ms_e2e, _, _ = timed_batches(step_e2e, 2, world, device, min_seconds=0.0, max_batches=1)
+        ms_e2e /= 2
+        alg = src_bytes + layer.stream_bytes()
+        out["e2e"] = {"value": world * alg / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": src_bytes,
+                      "d2h_bytes_per_step": int(layer.k_stream.numel() + layer.v_stream.numel() + 8 * B)}
+    return out if rank == 0 else None
+
+
+ENCODE_REVISION = 1   # changes when the encoder kernels change (keys NCU_TRAFFIC_BYTES)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS) + ["mistral7b-encode"])
-    ap.add_argument("--encode-batch", type=int, default=16)
+    ap.add_argument("--encode-batch", type=int, default=64, help="sequences in all (split over the ranks)")
     ap.add_argument("--encode-bits", type=int, default=4)
     ap.add_argument("--encode-block", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="default workload: skip the v_block_64 / encode / head_sharded legs")
     ap.add_argument("--decode-bits-k", type=int, default=None, help="override the decode workload's K bit width (sweeps)")
     ap.add_argument("--decode-bits-v", type=int, default=None, help="override the decode workload's V bit width (sweeps)")
+    ap.add_argument("--decode-cbv", type=int, default=None, choices=[64, 128], help="override the V token block (sweeps)")
+    ap.add_argument("--decode-batch", type=int, default=None, help="override the batch (sweeps)")
+    ap.add_argument("--decode-ctx", type=int, default=None, help="override the context length (sweeps)")
     ap.add_argument("--decode-k-mode", default="channel", choices=["channel", "token"], help="K quantisation parameters (sweeps)")
     ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
                     help="multi-GPU split: independent sequences per rank (weak scaling, no collective) or KV heads per "
-                         "rank with an all-gather of the outputs (strong scaling)")
+                         "rank with an exchange of the outputs (strong scaling)")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl"], help="output exchange of --shard heads")
     args = ap.parse_args()
     w = WORKLOADS.get(args.workload)
-    if w is not None and (args.decode_bits_k or args.decode_bits_v or args.decode_k_mode != "channel"):
-        w = dict(w, bits_k=args.decode_bits_k or w["bits_k"], bits_v=args.decode_bits_v or w["bits_v"], k_mode=args.decode_k_mode)
-        w["name"] += f" [override: K {w['bits_k']}-bit {w['k_mode']}, V {w['bits_v']}-bit]"
+    overridden = w is not None and (args.decode_bits_k or args.decode_bits_v or args.decode_k_mode != "channel" or args.decode_cbv
+                                    or args.decode_batch or args.decode_ctx)
+    if overridden:
+        w = dict(w, bits_k=args.decode_bits_k or w["bits_k"], bits_v=args.decode_bits_v or w["bits_v"], k_mode=args.decode_k_mode,
+                 cbv=args.decode_cbv or w["cbv"], batch=args.decode_batch or w["batch"], ctx=args.decode_ctx or w["ctx"])
+        w["name"] += f" [override: batch {w['batch']}, ctx {w['ctx']}, K {w['bits_k']}-bit {w['k_mode']}, V {w['bits_v']}-bit, V block {w['cbv']}]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -472,29 +510,67 @@ def main():
     device = torch.device("cuda", local)
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=device)
-    if args.workload == "mistral7b-encode":
-        line = run_encode(args, rank, world, device)
+    try:
+        if args.workload == "mistral7b-encode":
+            leg = encode_leg(args.steps, args.warmup, rank, world, device, total_seqs=args.encode_batch, bits=args.encode_bits,
+                             block=args.encode_block)
+            if rank == 0:
+                p = leg["plain"]
+                line = {"metric": "KV encode throughput", "value": p["value"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+                        "warmup": max(args.warmup, 3), "ms_per_step": p["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": leg["config"], "roofline": p["roofline"],
+                        "e2e": leg.get("e2e"), "median_reorder": leg.get("median"), "append": leg.get("append"),
+                        "source_fp16_gbs": p["source_fp16_gbs"], "compressed_over_fp16": p["compressed_over_fp16"], "gpu_launches": 7 * args.steps}
+                print(json.dumps(line), flush=True)
+            return
+        line = decode_line(args, w, rank, world, device)
+        extras = args.workload == "llama8b" and not overridden and not args.no_extras and args.shard == "batch"
+        if extras:
+            torch.cuda.empty_cache()
+            # the same decode with 64-token V blocks (this library's own layout; 8 layers are enough for a per-layer time)
+            w64 = dict(w, cbv=64, layers=8)
+            m = time_decode(w64, args.steps, args.warmup, rank, world, device, with_e2e=False, sample_clocks=False)
+            if rank == 0:
+                peak, _ = measured_peak_gbs()
+                us = m["ms_per_step"] / m["layers"] * 1e3
+                gbs = m["alg_bytes"] / m["layers"] / (us * 1e-6) / 1e9
+                line["v_block_64"] = {"us_per_layer": us, "tok_s_at_32_layers": w["batch"] * world / (us * 1e-6 * 32), "compressed_kv_gbs": gbs,
+                                      "roofline_frac": gbs / peak, "layers_timed": m["layers"]}
+            torch.cuda.empty_cache()
+            leg = encode_leg(args.steps, args.warmup, rank, world, device)
+            if rank == 0:
+                line["encode"] = leg
+            torch.cuda.empty_cache()
+            if world > 1:
+                wq = dict(WORKLOADS["qwen8b-long"], layers=6)
+                mh = time_decode(wq, max(5, args.steps), args.warmup, rank, world, device, by_heads=True, with_e2e=False, sample_clocks=False,
+                                 exchange=args.exchange)
+                m1 = time_decode(wq, max(5, args.steps), args.warmup, rank, 1, device, with_e2e=False, sample_clocks=False) if rank == 0 else None
+                torch.distributed.barrier()
+                if rank == 0:
+                    us_n = mh["ms_per_step"] / mh["layers"] * 1e3
+                    us_1 = m1["ms_per_step"] / m1["layers"] * 1e3
+                    line["head_sharded"] = {
+                        "workload": wq["name"], "layers_timed": mh["layers"], "exchange": args.exchange,
+                        "tok_s_at_36_layers": wq["batch"] / (us_n * 1e-6 * 36), "us_per_layer": us_n,
+                        "exchange_us_per_layer": mh["exchange_ms_per_step"] / mh["layers"] * 1e3,
+                        "one_gpu_us_per_layer": us_1, "speedup": us_1 / us_n, "efficiency": us_1 / us_n / world, "check": mh["check"]}
         if rank == 0:
+            if not args.no_cpu_baseline and world == 1:
+                t0 = time.perf_counter()
+                nseq = 2 if w["ctx"] <= 8192 else 1
+                reps = 60 if w["ctx"] <= 8192 else 15                      # a few seconds of CPU work: a stable median
+                kind, times = cpu_reference_path(w, nseq, repeats=reps, threads=os.cpu_count() or 1)
+                t_layer = sorted(times)[len(times) // 2]
+                line["cpu_baseline"] = {
+                    "value": nseq / (t_layer * w["layers"]), "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": kind,
+                    "sample": f"1 layer x {nseq} sequences, median of {reps} runs ({t_layer * 1e3:.0f} ms each, {time.perf_counter() - t0:.0f} s in all "
+                              f"with set-up): C++ bit-unpack (1 thread) + torch dequantise + eager attention (all threads); scaled by {w['layers']} layers"}
             print(json.dumps(line), flush=True)
+    finally:
         if world > 1:
             torch.distributed.barrier()
             torch.distributed.destroy_process_group()
-        return
-    line = run_ours(args, w, rank, world, device)
-    if rank == 0:
-        if not args.no_cpu_baseline:
-            t0 = time.perf_counter()
-            nseq = 2 if w["ctx"] <= 8192 else 1
-            reps = 120 if w["ctx"] <= 8192 else 30                     # ~10 s of CPU work: a stable median
-            tok_s, kind, t_layer, _ = cpu_reference_path(w, nseq, repeats=reps, threads=os.cpu_count() or 1)
-            line["cpu_baseline"] = {
-                "value": tok_s, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": kind,
-                "sample": f"1 layer x {nseq} sequences, median of {reps} runs ({t_layer * 1e3:.0f} ms each, {time.perf_counter() - t0:.0f} s in all "
-                          f"with set-up): C++ bit-unpack (1 thread) + torch dequantise + eager attention (all threads); scaled by {w['layers']} layers"}
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        torch.distributed.barrier()
-        torch.distributed.destroy_process_group()
 
 
 if __name__ == "__main__":

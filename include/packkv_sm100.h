@@ -31,6 +31,7 @@ extern "C" {
 #define PKV_FLAG_CODE_RANGE 2u
 #define PKV_FLAG_BAD_STREAM 4u
 #define PKV_FLAG_TIMEOUT 8u
+#define PKV_FLAG_ZERO_RANGE 16u   /* pkv_decode_attention: a zero-point too large for the exact in-kernel dequantisation */
 
 /* quantisation modes (the reference's QuantMode.ChannelQuant / QuantMode.TokenQuant) */
 #define PKV_K_CHANNEL 0

@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("PACKKV_SM100_LIB") or os.path.join(_PKG, "libpackkv_s
 
 PKV_OK, PKV_ERR_BAD_ARGUMENT, PKV_ERR_UNSUPPORTED, PKV_ERR_CUDA, PKV_ERR_TOO_LARGE = 0, 1, 2, 3, 4
 STATIC_SCRATCH_BYTES = 16 << 20
-FLAG_STREAM_OVERFLOW, FLAG_CODE_RANGE, FLAG_BAD_STREAM, FLAG_TIMEOUT = 1, 2, 4, 8
+FLAG_STREAM_OVERFLOW, FLAG_CODE_RANGE, FLAG_BAD_STREAM, FLAG_TIMEOUT, FLAG_ZERO_RANGE = 1, 2, 4, 8, 16
 
 _i32, _i64, _p, _f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
 

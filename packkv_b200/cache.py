@@ -97,10 +97,16 @@ class PackKVCache(_HFCache):
             raise ValueError("TComCacheConfigStatic.config is not set. Please set it before using TComCache.")
         return cfg
 
-    def _check_flags(self):
+    def check_flags(self):
+        """Reads the device status word (synchronises) and raises if a kernel reported a condition that makes
+        the cache's contents or an attention result wrong.  update() and attend() are asynchronous and do not
+        call this; compressed_bytes() does, and callers should at points where they synchronise anyway."""
         f = int(self.flags.item()) if self.flags is not None else 0
         if f:
-            raise RuntimeError(f"PackKV device status flags set: {f} (1=stream overflow, 2=code range, 4=bad stream)")
+            raise RuntimeError(f"PackKV device status flags set: {f} (1=stream overflow, 2=code range, 4=bad stream, "
+                               "8=wait timed out, 16=zero-point outside the exact range of the attention kernel)")
+
+    _check_flags = check_flags
 
     def _ensure_store(self, L: _Layer, kv_heads: int, need_tokens: int, dtype, device, cfg: PackKVCacheConfig):
         if L.comp is not None and L.capacity >= need_tokens:
@@ -287,7 +293,8 @@ class PackKVCache(_HFCache):
         return self.get_seq_length(layer_idx) + int(query_length), 0
 
     def compressed_bytes(self) -> int:
-        """Bytes of packed streams held by all layers (synchronises)."""
+        """Bytes of packed streams held by all layers (synchronises, and checks the device status word)."""
+        self.check_flags()
         n = 0
         for L in self._layers:
             if L.comp is not None:

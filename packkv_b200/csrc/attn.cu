@@ -17,23 +17,26 @@
 // Because the probabilities need the global max and sum before they can be rounded, the
 // sequence is split over a thread-block CLUSTER instead of over independent CTAs with a later merge:
 // grid = (cluster_size, kv_heads, batch), one cluster per (sequence, KV head).
-//   phase 1  every warp of the cluster walks its 128-token (or 64-token) tiles: K blocks are
-//            staged with cp.async, unpacked, dequantised and contracted with q on the tensor
-//            cores; scores stay in the warp's shared memory.  Residual (uncompressed) tokens
-//            are 16-token tiles handed to the same warps and contracted by the same mma
-//            (K rows straight from global memory as A fragments, V rows staged in shared
-//            memory and transposed on load with ldmatrix).
+//   phase 1  every warp of the cluster walks its token tiles: K blocks are staged in shared memory
+//            by bulk copies (one instruction of one lane per block, completion on an mbarrier),
+//            unpacked and dequantised by the lane that owns the channel, transposed through a
+//            small shared-memory tile into mma fragments and contracted with q on the tensor cores;
+//            scores stay in the warp's shared memory.
 //   exchange per-CTA (max, sum) go through distributed shared memory, one cluster barrier.
-//   phase 2  scores -> probabilities in place, V blocks are unpacked and contracted.
+//   phase 2  scores -> probabilities in place; V packs are fetched by the lane whose mma fragment
+//            needs them (a pack is 16 tokens of one channel = one row segment of the A operand), so
+//            V needs no transposition at all.
 //   reduce   warps -> CTA in shared memory, CTAs -> rank 0 through distributed shared memory.
 //
-// Per warp, K: read the per-round headers, warp-scan the pack sizes into byte offsets, unpack
-// 4 channels x 16 tokens per lane with one rotate + one mask per code, exchange through a
-// swizzled 16x128-byte tile so that each lane holds the mma A fragment (tokens x channels),
-// dequantise two codes per instruction, mma.sync m16n8k16 against the q fragments (the 8
-// columns of the n-tile are the q heads of the group).  V: same unpack (1 channel x 64 tokens
-// per lane), 32x64-byte exchange tile, A = channels x tokens, B = probabilities.
+// Unpack, per pack (16 codes of `len` bits, token 0 in the top bits): one 8-byte window at a 2-byte
+// aligned offset (warp scan of the lengths), then per 8 codes one shift-and-select that puts codes
+// i and i+4 sixteen bits apart and four shift-mask-or steps that yield the element-type pairs
+// (bias + code_i, bias + code_{i+4}) directly (the bias is the exponent pattern under which the
+// code bits are the low mantissa bits).  The pairing (i, i+4) fixes a token order inside each group
+// of 16, which the score / probability / parameter arrays in shared memory follow.
 #include <cooperative_groups.h>
+#include <cstdlib>
+#include <type_traits>
 
 #include "attn.cuh"
 #include "common.cuh"
@@ -43,21 +46,30 @@ namespace cg = cooperative_groups;
 namespace pkv {
 
 constexpr int kAW = 4;            // warps per CTA
-// staging slots per warp: 2 = the copy of the next block overlaps the work on this one; 1 = the next block is
-// only prefetched to L2 (9 KB less shared memory per CTA, measured 5 % slower at the same 4 CTAs per SM; a fifth
-// CTA would also need 96 registers per thread, which spills and is slower still)
-constexpr int kSlots = 2;
-constexpr int kCtasPerSm = 4;
+#ifndef PKV_ATTN_CTAS
+#define PKV_ATTN_CTAS 4
+#endif
+constexpr int kMaxCtasPerSm = PKV_ATTN_CTAS;  // register budget: 65536 / (128 * 4) -> 128 per thread, 96 for 5
 constexpr int kD = 128;           // head dimension
+constexpr int kSmCount = 148;
+constexpr unsigned kWaitSpins = 1u << 22;
+#ifndef PKV_ONE_CHAIN
+#define PKV_ONE_CHAIN 0
+#endif
+#ifndef PKV_ABL
+#define PKV_ABL 0
+#endif   // bounded mbarrier wait (each try suspends for a while by itself)
 
 // ---- element-type traits --------------------------------------------------------------------
 template <typename T> struct Tr;
 
 template <> struct Tr<__half> {
     using T2 = __half2;
-    static constexpr unsigned kMagic = 0x64646464u;   // 0x6400 | b == 1024 + b, exact
+    static constexpr unsigned kMagic2 = 0x64006400u;  // 0x6400 | b == 1024 + b, exact
+    static constexpr unsigned kMagicB = 0x64646464u;
     static constexpr float kBias = 1024.f;
     static __device__ __forceinline__ T2 bias2() { return __float2half2_rn(1024.f); }
+    static __device__ __forceinline__ T2 zmax2() { return __float2half2_rn(2048.f - 16.f); }
     static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
     static __device__ __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
     static __device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
@@ -74,9 +86,11 @@ template <> struct Tr<__half> {
 
 template <> struct Tr<__nv_bfloat16> {
     using T2 = __nv_bfloat162;
-    static constexpr unsigned kMagic = 0x43434343u;   // 0x4300 | b == 128 + b, exact
+    static constexpr unsigned kMagic2 = 0x43004300u;  // 0x4300 | b == 128 + b, exact
+    static constexpr unsigned kMagicB = 0x43434343u;
     static constexpr float kBias = 128.f;
     static __device__ __forceinline__ T2 bias2() { return __float2bfloat162_rn(128.f); }
+    static __device__ __forceinline__ T2 zmax2() { return __float2bfloat162_rn(256.f - 16.f); }
     static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
     static __device__ __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
     static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
@@ -94,23 +108,33 @@ template <> struct Tr<__nv_bfloat16> {
 template <typename T2> __device__ __forceinline__ unsigned as_u(T2 v) { return *reinterpret_cast<unsigned*>(&v); }
 template <typename T2> __device__ __forceinline__ T2 as_t2(unsigned v) { return *reinterpret_cast<T2*>(&v); }
 
-// two biased codes (bias + code, exact) -> two dequantised elements, rounded like the reference
-template <typename T, bool HP>
-__device__ __forceinline__ unsigned deq2(unsigned biased, typename Tr<T>::T2 z, typename Tr<T>::T2 s) {
-    using T2 = typename Tr<T>::T2;
-    T2 x = as_t2<T2>(biased);
-    if (!HP) return as_u(__hmul2(__hadd2(x, z), s));          // z = zero - bias
-    // the product must be rounded before the addition, as in the reference: _rn keeps the compiler from
-    // contracting the pair into one fused multiply-add
-    return as_u(__hadd2(__hmul2_rn(__hsub2(x, Tr<T>::bias2()), s), z));   // z = min
-}
-
-__device__ __forceinline__ void cp_async16(uint8_t* smem_dst, const uint8_t* gsrc) {
-    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gsrc));
-}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void cp_async16_zfill(unsigned smem_dst, const void* gsrc, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_dst), "l"(gsrc), "r"(valid ? 16 : 0));
+}
+
+// ---- mbarrier + bulk copy (global -> this CTA's shared memory, no multicast) ------------------
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, unsigned bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 
 // exp(x) for x <= 0 (softmax arguments): one multiply and one MUFU; results below the normal
 // range flush to zero, which the rounding to the element type does anyway
@@ -119,14 +143,22 @@ __device__ __forceinline__ float fast_exp(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
     return y;
 }
-__device__ __forceinline__ void cp_async16_zfill(unsigned smem_dst, const void* gsrc, bool valid) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_dst), "l"(gsrc), "r"(valid ? 16 : 0));
-}
 // four 8x8 b16 matrices, transposed on load: lane l passes the address of row l%8 of matrix l/8
 __device__ __forceinline__ void ldmatrix_x4_trans(unsigned addr, unsigned (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
 }
+__device__ __forceinline__ uint2 lds64(unsigned a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned lds8(unsigned a) {
+    unsigned v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts64(unsigned a, unsigned x, unsigned y) { asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(x), "r"(y) : "memory"); }
 
 // header fields of width w at bits 0, w, 2w, 3w of a lane word -> one byte each
 struct FieldSpread { int s1, s2; unsigned m1, m2; };
@@ -137,28 +169,66 @@ __device__ __forceinline__ unsigned spread_fields(unsigned x, const FieldSpread&
 __host__ inline FieldSpread make_field_spread(int w) {
     return FieldSpread{16 - 2 * w, 8 - w, ((1u << (2 * w)) - 1u) * 0x00010001u, ((1u << w) - 1u) * 0x01010101u};
 }
-
-// One pack (16 codes of `len` bits, token 0 in the top bits of the 2*len-byte word) -> 16 bytes.
-// la = {2^(4 len) - 1, (2^(2 len) - 1) * 0x00010001, (2^len - 1) * 0x01010101, 4 len},
-// lb = {16 - 2 len, 8 - len, 8 len, -}: the table entry of this length.  Fields are spread by two
-// shift-or-mask steps per four codes; byte p of the result holds token p ^ 3 (the consumers pick
-// their byte pairs accordingly), each plus the pack minimum replicated in `minrep`.
-__device__ __forceinline__ uint4 unpack_pack(unsigned lo, unsigned hi, const uint4& la, const uint4& lb, unsigned minrep) {
-    const unsigned tp = __funnelshift_rc(lo, hi, lb.z);
-    unsigned w[4] = {(tp >> la.w) & la.x, tp & la.x, (lo >> la.w) & la.x, lo & la.x};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const unsigned y = (w[i] | (w[i] << lb.x)) & la.y;
-        w[i] = ((y | (y << lb.y)) & la.z) + minrep;
-    }
-    return make_uint4(w[0], w[1], w[2], w[3]);
-}
 __device__ __forceinline__ unsigned byte_of(unsigned x, int j) { return __byte_perm(x, 0, 0x4440 + j); }
 
-// Channel order of the K contraction.  mma step j = 2m + b covers, for the lanes with c = lane & 3,
-// the channels 32m + 8c + {2b, 2b+4} (k = 2c, 2c+1) and 32m + 8c + {2b+1, 2b+5} (k = 2c+8, 2c+9): the
-// order in which ldmatrix.trans delivers the exchange tile.  From the 8 consecutive elements
-// x0..x7 of channels 32m + 8c.. this forms the four operand registers of steps 2m and 2m+1:
+// Reads of data that nothing writes while it is being read (a staged stream block, the length table): no
+// "memory" clobber and not volatile, so the compiler may schedule them across the exchange-tile traffic.  The
+// address must be derived from a value defined after the wait that made the data visible.
+__device__ __forceinline__ unsigned ldp32(unsigned a) { unsigned v; asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ unsigned ldp16(unsigned a) { unsigned short v; asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a)); return v; }
+__device__ __forceinline__ unsigned ldp8(unsigned a) { unsigned v; asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+// 64-bit window at shared address a (2-byte aligned): three aligned 32-bit loads, two funnel shifts
+__device__ __forceinline__ void ldp_u64_align2(unsigned a, unsigned& lo, unsigned& hi) {
+    const unsigned wa = a & ~3u, sh = (a & 2u) * 8u;
+    const unsigned w0 = ldp32(wa), w1 = ldp32(wa + 4), w2 = ldp32(wa + 8);
+    lo = __funnelshift_r(w0, w1, sh);
+    hi = __funnelshift_r(w1, w2, sh);
+}
+// lane word of W bits (8, 12 or 16) at bit lane * W of a header field that starts at a 2-byte aligned address
+template <int W> __device__ __forceinline__ unsigned lane_word(unsigned hdr, int lane) {
+    if (W == 16) return ldp16(hdr + 2 * lane);
+    if (W == 8) return ldp8(hdr + lane);
+    const unsigned ad = hdr + 2 * ((3 * lane) >> 2);
+    const unsigned w = ldp16(ad) | (ldp16(ad + 2) << 16);
+    return (w >> (4 * ((3 * lane) & 3))) & 0xFFFu;
+}
+// four fields of W bits at bits 0, W, 2W, 3W -> one byte each
+template <int W> __device__ __forceinline__ unsigned spread_const(unsigned x) {
+    constexpr unsigned m1 = ((1u << (2 * W)) - 1u) * 0x00010001u, m2 = ((1u << W) - 1u) * 0x01010101u;
+    const unsigned y = (x | (x << (16 - 2 * W))) & m1;
+    return (y | (y << (8 - W))) & m2;
+}
+
+// Eight codes of `len` bits (code 0 in the top bits of x, garbage above bit 8*len allowed) -> four
+// registers of element-type pairs: r[k] = (bias + code_{7-k}, bias + code_{3-k}) as (low, high) halves.
+// s1 = 16 - 4 len, m16 = (2^len - 1) * 0x00010001.
+template <unsigned MAGIC>
+__device__ __forceinline__ void unpack8(unsigned x, unsigned s1, unsigned len, unsigned m16, unsigned (&r)[4]) {
+    // codes 4..7 stay in the low half, codes 0..3 move to the high half: code i and i+4 end up 16 bits apart
+    unsigned y = ((x << s1) & 0xFFFF0000u) | (x & 0x0000FFFFu);
+    r[0] = (y & m16) | MAGIC;
+    y >>= len;
+    r[1] = (y & m16) | MAGIC;
+    y >>= len;
+    r[2] = (y & m16) | MAGIC;
+    y >>= len;
+    r[3] = (y & m16) | MAGIC;
+}
+// Token held by the (low, high) halves of register k of the group of eight that starts at token 8*grp:
+//   k:      0      1      2      3
+//   pair: (7,3)  (6,2)  (5,1)  (4,0)
+// The shared-memory arrays that are read as such pairs (V scales, zero-points, probabilities; token-mode K
+// parameters) store, per group of 16 tokens, the words [(7,3) (6,2) (5,1) (4,0) (15,11) (14,10) (13,9) (12,8)].
+// A lane that holds the natural-order words n_e = (2e, 2e+1) and n_{e+2} = (2e+4, 2e+5) of a group of eight
+// (e = 0, 1) forms the two paired words it owns; they are adjacent: word index 2 - 2e and 3 - 2e.
+__device__ __forceinline__ void pair_words(unsigned ne, unsigned ne2, unsigned& w_first, unsigned& w_second) {
+    w_first = __byte_perm(ne, ne2, 0x3276);    // (2e+5, 2e+1): word 2 - 2e
+    w_second = __byte_perm(ne, ne2, 0x1054);   // (2e+4, 2e):   word 3 - 2e
+}
+
+// q fragments for the residual (uncompressed) tiles.  mma step j = 2m + b covers, for the lanes with c = lane & 3,
+// the channels 32m + 8c + {2b, 2b+4} (k = 2c, 2c+1) and 32m + 8c + {2b+1, 2b+5} (k = 2c+8, 2c+9).  From the 8
+// consecutive elements x0..x7 of channels 32m + 8c.. this forms the operand registers of steps 2m and 2m+1:
 // f[b][0] = (x[2b], x[2b+4]), f[b][1] = (x[2b+1], x[2b+5]).
 __device__ __forceinline__ void pair_shuffle(const uint4& v, unsigned (&f0)[2], unsigned (&f1)[2]) {
     f0[0] = __byte_perm(v.x, v.z, 0x5410); f0[1] = __byte_perm(v.x, v.z, 0x7632);
@@ -174,8 +244,12 @@ struct AttnDev {
     int rtw;             // max residual tiles (16 tokens) per warp
     int rows;            // score rows kept per tile (q heads of the group, rounded up to even)
     int slot;            // bytes of one staging slot
+    int nslots;          // staging slots per warp: 2 = the next block is copied while this one is unpacked
+    int vpair;           // 64-token V blocks: an item is the pair of blocks of one token block (both channel halves)
+    int kbound, vbound;  // largest legal block size in bytes
     int prow;            // bytes of one row of the score / probability tile
     int warp_smem;       // bytes of per-warp shared memory
+    int off_xch, off_raw, off_perm, off_desc, off_stile, off_rst;   // byte offsets inside a warp's region
     int cta_off;         // byte offset of the CTA-shared block
     int out_off;         // byte offset, inside a warp's region, of its rows of the CTA's reduced output
     int tile_shift, cbk_shift, cbv_shift;   // log2 of tile, cbk, cbv
@@ -189,18 +263,32 @@ struct CtaShared {
     float cl_l[8];       // this CTA's sum of exp(s - cl_m) per head
     float wm[kAW][8];    // per-warp scratch
     float gM[8], gInvL[8];
+    unsigned lutm[8];    // (2^len - 1) * 0x00010001 per pack length 0..4 (see unpack8)
+    unsigned long long mbar[kAW][2];
 };
 // The CTA's reduced accumulators out[head][channel] (read by rank 0 through distributed shared
-// memory) live in the warps' exchange tiles, which are idle by then: head hd -> warp hd & 3,
+// memory) live in the warps' regions, which are idle by then: head hd -> warp hd & 3,
 // float offset (hd >> 2) * kD.
 __device__ __forceinline__ float* cta_out_row(uint8_t* smem, int warp_smem, int out_off, int hd) {
     return reinterpret_cast<float*>(smem + (hd & 3) * warp_smem + out_off) + (hd >> 2) * kD;
 }
 
+// dequantise one register of two biased codes.  NORMAL: (code + zero) * scale with zadd = zero - bias (+ pack minimum);
+// HP: code * scale + min, the product rounded before the addition as in the reference (_rn keeps the compiler
+// from contracting the pair into one fused multiply-add), with cadd = pack minimum - bias.
+template <typename T, bool HP>
+__device__ __forceinline__ unsigned deq(unsigned biased, typename Tr<T>::T2 add, typename Tr<T>::T2 s, typename Tr<T>::T2 zmin) {
+    using T2 = typename Tr<T>::T2;
+    const T2 x = __hadd2(as_t2<T2>(biased), add);
+    if (!HP) return as_u(__hmul2(x, s));
+    return as_u(__hadd2(__hmul2_rn(x, s), zmin));
+}
+
 // =================================================================================================
 template <typename T, int KMODE, bool HP>
-__global__ void __launch_bounds__(kAW * 32, kCtasPerSm) attn_decode_kernel(const AttnDev P) {
+__global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(const AttnDev P) {
     using T2 = typename Tr<T>::T2;
+    constexpr unsigned MAGIC = Tr<T>::kMagic2;
     extern __shared__ __align__(16) uint8_t smem[];
     cg::cluster_group cluster = cg::this_cluster();
     const AttnArgs& a = P.a;
@@ -213,22 +301,29 @@ __global__ void __launch_bounds__(kAW * 32, kCtasPerSm) attn_decode_kernel(const
     const int gw = rank * kAW + wic;                   // warp index inside the cluster
 
     uint8_t* wbase = smem + wic * P.warp_smem;
-    uint8_t* xch = wbase + kSlots * P.slot;            // 2048 B exchange tile
-    T* vsz = reinterpret_cast<T*>(xch + 2048);         // [tile] V scale, [tile] V zero(-bias)
-    T* ksz = vsz + 2 * P.tile;                         // token mode: [tile] K scale, [tile] K zero(-bias)
-    uint8_t* stile = reinterpret_cast<uint8_t*>(ksz + 2 * P.tile);   // [tpw][rows][prow] scores -> probabilities
-    const unsigned rst_a = smem_addr(stile + P.tpw * P.rows * P.prow);      // [rtw][rows][16] residual scores -> probabilities
     CtaShared* cs = reinterpret_cast<CtaShared*>(smem + P.cta_off);
     // 32-bit shared-window addresses for the hot loops
-    const unsigned wbase_a = smem_addr(wbase), xch_a = smem_addr(xch), vsz_a = smem_addr(vsz), stile_a = smem_addr(stile);
-    // K exchange tile: one 16-byte row (16 tokens) per channel; channel 4*lane + i lives in row
-    // lane + 32*i, so the four row stores of a warp are contiguous and the 8x8 matrices that
-    // ldmatrix.trans turns into fragments (plane i, rows 8m..8m+7) are contiguous too.
-    const unsigned kst = xch_a + lane * 16;
-    const unsigned kldm = xch_a + (32 * (lane >> 3) + (lane & 7)) * 16;
-    // V exchange: row = lane (channel), chunk swizzle by (row >> 1) & 3; fragment rows g, g+8, g+16, g+24 share that swizzle
-    const unsigned vst = xch_a + lane * 64, vsw = ((lane >> 1) & 3) << 4;
-    const unsigned vld = xch_a + g * 64 + ((c ^ ((g >> 1) & 3)) << 4);
+    const unsigned wbase_a = smem_addr(wbase);
+    const unsigned xch_a = wbase_a + P.off_xch;        // K exchange: two tiles of 32 rows x 32 bytes
+    const unsigned raw_a = wbase_a + P.off_raw;        // parameters as copied from global memory
+    const unsigned perm_a = wbase_a + P.off_perm;      // per-token parameters in pair order: [tile] scale, [tile] zero
+    const unsigned desc_a = wbase_a + P.off_desc;      // V: per channel-owner lane (pack offsets, lengths, minima)
+    const unsigned stile_a = wbase_a + P.off_stile;    // [tpw][rows][prow] scores -> probabilities
+    const unsigned rst_a = wbase_a + P.off_rst;        // [rtw][rows][16] residual scores -> probabilities
+    unsigned lutm_a = smem_addr(cs->lutm);
+    const unsigned bar_a = smem_addr(&cs->mbar[wic][0]);
+
+    if (threadIdx.x < 5) {
+        const unsigned L = threadIdx.x;
+        cs->lutm[L] = ((1u << L) - 1u) * 0x00010001u;
+    }
+    if (lane == 0) {
+        mbar_init(bar_a, 1);
+        mbar_init(bar_a + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    asm volatile("" : "+r"(lutm_a) :: "memory");        // reads of the table stay behind the barrier
 
     const int my_tiles = gw < P.tiles_total ? (P.tiles_total - gw + n_warps - 1) / n_warps : 0;
     // residual tiles are dealt from the last warp backwards (the compressed tiles are dealt from
@@ -242,278 +337,358 @@ __global__ void __launch_bounds__(kAW * 32, kCtasPerSm) attn_decode_kernel(const
     const int lbk = len_field_bits(a.bits_k), lbv = len_field_bits(a.bits_v);
     const uint8_t* kbase = a.k_stream + (int64_t)b * a.k_seq_stride;
     const uint8_t* vbase = a.v_stream + (int64_t)b * a.v_seq_stride;
-    const uint32_t* kinfo = a.k_info + (int64_t)b * a.k_info_seq_stride * 2;
-    const uint32_t* vinfo = a.v_info + (int64_t)b * a.v_info_seq_stride * 2;
     const T2 bias2 = Tr<T>::bias2();
+    const T2 nbias2 = __hneg2(bias2);
+    const T2 zmax2 = Tr<T>::zmax2();                   // largest zero-point for which (bias + code) + (zero - bias) is exact
     const bool col_live = 2 * c < P.rows;              // this lane's score columns (heads 2c, 2c+1) are kept
+    const int ns_mask = P.nslots - 1;
+    bool dead = false;                                 // a bounded wait gave up: this warp stops touching the stream
+    bool bad_len = false, bad_zero = false;
 
     // ---- stream-block fetch ---------------------------------------------------------------------
-    // item n < k_items: K block (n % nkb) of local tile n / nkb; else V block of local tile
-    // (offset, size) of item n's block; loaded one item ahead of the copy that needs it
-    auto load_info = [&](int n) -> uint2 {
-        const uint32_t* info;
+    // Item n < k_items: K block (n % nkb) of local tile n / nkb.  Later items: V.  With 64-token V blocks an item is
+    // the pair of blocks (both 64-channel halves of the head) of one token block, copied into the two halves of
+    // the slot; with 128-token V blocks an item is one block.  An item's table entries are loaded one item ahead
+    // of the copy that needs them.
+    const uint2* kinfo_h = reinterpret_cast<const uint2*>(a.k_info) + (int64_t)b * a.k_info_seq_stride + h;
+    const uint2* vinfo_h = reinterpret_cast<const uint2*>(a.v_info) + (int64_t)b * a.v_info_seq_stride + 2 * h;
+    const T* kpar_s = reinterpret_cast<const T*>(a.k_scale) +
+                      (KMODE == kKChannel ? (int64_t)(b * a.kv_heads + h) * a.param_blocks * kD : (int64_t)b * a.param_tokens);
+    const T* kpar_z = reinterpret_cast<const T*>(a.k_zero) + (kpar_s - reinterpret_cast<const T*>(a.k_scale));
+    const T* vpar_s = reinterpret_cast<const T*>(a.v_scale) + (int64_t)b * a.param_tokens;
+    const T* vpar_z = reinterpret_cast<const T*>(a.v_zero) + (int64_t)b * a.param_tokens;
+    const unsigned half_slot = (unsigned)P.slot >> 1;
+    auto load_info = [&](int n) -> uint4 {
         if (n < k_items) {
             const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
-            const int t0 = (gw + tl * n_warps) << P.tile_shift;
-            info = kinfo + ((int64_t)((t0 >> P.cbk_shift) + i) * a.kv_heads + h) * 2;
-        } else {
-            const int m = n - k_items;
-            const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
-            const int t0 = (gw + tl * n_warps) << P.tile_shift;
-            info = vinfo + ((int64_t)((t0 >> P.cbv_shift) + (vi >> 1)) * (2 * a.kv_heads) + 2 * h + (vi & 1)) * 2;
+            const uint2 e = __ldg(kinfo_h + (((gw + tl * n_warps) << P.nkb_shift) + i) * a.kv_heads);
+            return make_uint4(e.x, e.y, 0, 0);
         }
-        return __ldg(reinterpret_cast<const uint2*>(info));
+        const int m = n - k_items;
+        const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
+        if (P.vpair) {
+            const uint2* p = vinfo_h + (((gw + tl * n_warps) << P.nvi_shift) + vi) * (2 * a.kv_heads);
+            const uint2 e0 = __ldg(p), e1 = __ldg(p + 1);
+            return make_uint4(e0.x, e0.y, e1.x, e1.y);
+        }
+        const uint2 e = __ldg(vinfo_h + (gw + tl * n_warps) * (2 * a.kv_heads) + vi);   // one 128-token block per tile: vi = half
+        return make_uint4(e.x, e.y, 0, 0);
     };
-    // Starts the copy of item n's block into its staging slot, together with the quantisation
-    // parameters the item needs: channel-mode K: the block's 128 scales and 128 zero-points
-    // (512 bytes at vsz, free during phase 1); first V block of a tile: the tile's per-token
-    // scales and zero-points into parameter buffer (tile & 1) (vsz / ksz, both free in phase 2).
-    auto issue = [&](int n, uint2 inf, int& phase_out, int& size_out) {
-        const uint8_t* base;
-        int64_t cap;
-        int bound;
-        if (n < k_items) {
-            base = kbase; cap = a.k_capacity;
-            bound = 2 * k_rounds + k_rounds * (16 * a.bits_k + 16 * lbk + 256 * a.bits_k);
+    // (size << 4 | 16-byte phase) of a block that can be copied, 0 for a table entry that points outside the stream
+    auto check_block = [&](unsigned off, unsigned size, const uint8_t* base, int64_t cap, int bound) -> unsigned {
+        const bool bad = (int64_t)off + size > cap || (int)size > bound || size < 4 || ((off | size) & 1u);   // blocks start and end on even bytes
+        return bad ? 0u : (size << 4) | (unsigned)(reinterpret_cast<uintptr_t>(base + off) & 15);
+    };
+    // Starts the copies of item n into its staging slot (same 16-byte phase as the source: block offsets are
+    // arbitrary even bytes), together with the quantisation parameters the item needs: channel-mode K: the
+    // block's 128 scales and 128 zero-points; token-mode K, first block of a tile: the tile's per-token scales
+    // and zero-points; first V item of a tile: the same for V.  One lane issues, completion is counted in
+    // bytes on the slot's mbarrier.
+    auto issue = [&](int n, uint4 inf, unsigned& pk0, unsigned& pk1) {
+        const T *p0 = nullptr, *p1 = nullptr;          // parameter sources
+        unsigned pbytes = 0;
+        const bool is_k = n < k_items;
+        const uint8_t* base = is_k ? kbase : vbase;
+        const int64_t cap = is_k ? a.k_capacity : a.v_capacity;
+        const int bound = is_k ? P.kbound : P.vbound;
+        if (is_k) {
+            const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
             if (KMODE == kKChannel) {
-                const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
+                const int off_e = (((gw + tl * n_warps) << P.nkb_shift) + i) * kD;
+                p0 = kpar_s + off_e; p1 = kpar_z + off_e; pbytes = 2 * kD;
+            } else if (i == 0) {
                 const int t0 = (gw + tl * n_warps) << P.tile_shift;
-                const int64_t row = ((int64_t)(b * a.kv_heads + h) * a.param_blocks + ((t0 >> P.cbk_shift) + i)) * kD;
-                const T* src = reinterpret_cast<const T*>(lane < 16 ? a.k_scale : a.k_zero) + row + 8 * (lane & 15);
-                cp_async16(reinterpret_cast<uint8_t*>(vsz) + 16 * lane, reinterpret_cast<const uint8_t*>(src));
+                p0 = kpar_s + t0; p1 = kpar_z + t0; pbytes = 2 * P.tile;
             }
         } else {
             const int m = n - k_items;
             const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
-            base = vbase; cap = a.v_capacity;
-            const int nseg = a.cbv == 128 ? 4 : 2;
-            bound = 2 * nseg + nseg * (16 * a.bits_v + 16 * lbv + 256 * a.bits_v);
-            if (vi == 0) {
+            if (vi == 0 || (!P.vpair && vi == 0)) {
                 const int t0 = (gw + tl * n_warps) << P.tile_shift;
-                const int chunks = P.tile >> 3;              // 16-byte chunks per parameter array
-                if (lane < 2 * chunks) {
-                    const T* src = reinterpret_cast<const T*>(lane < chunks ? a.v_scale : a.v_zero) + (int64_t)b * a.param_tokens + t0 +
-                                   8 * (lane < chunks ? lane : lane - chunks);
-                    cp_async16(reinterpret_cast<uint8_t*>(vsz) + (tl & 1) * 4 * P.tile + 16 * lane, reinterpret_cast<const uint8_t*>(src));
-                }
+                p0 = vpar_s + t0; p1 = vpar_z + t0; pbytes = 2 * P.tile;
             }
         }
-        const unsigned off = inf.x, size = inf.y;
-        uint8_t* dst = wbase + (kSlots == 2 ? (n & 1) : 0) * P.slot;
-        if ((int64_t)off + size > cap || (int)size > bound || size < 4 || ((off | size) & 1u)) {   // blocks start and end on even bytes
-            if (lane == 0) atomicOr(a.flags, kFlagBadStream);
-            phase_out = 0; size_out = 0;
-        } else {
-            const uint8_t* src = base + off;
-            const int phase = (int)(reinterpret_cast<uintptr_t>(src) & 15);
-            const int total = (phase + (int)size + 15) & ~15;
-            for (int j = lane * 16; j < total; j += 512) cp_async16(dst + j, src - phase + j);
-            phase_out = phase; size_out = (int)size;
+        pk0 = check_block(inf.x, inf.y, base, cap, bound);
+        pk1 = (!is_k && P.vpair) ? check_block(inf.z, inf.w, base, cap, bound) : 0u;
+        if ((pk0 == 0 || (!is_k && P.vpair && pk1 == 0)) && lane == 0) atomicOr(a.flags, kFlagBadStream);
+        if (lane == 0) {
+            const unsigned slot = n & ns_mask;
+            const unsigned dst = wbase_a + slot * P.slot, bar = bar_a + 8 * slot;
+            const unsigned ph0 = pk0 & 15, tot0 = pk0 ? (ph0 + (pk0 >> 4) + 15) & ~15u : 0u;
+            const unsigned ph1 = pk1 & 15, tot1 = pk1 ? (ph1 + (pk1 >> 4) + 15) & ~15u : 0u;
+            mbar_expect_tx(bar, tot0 + tot1 + 2 * pbytes);
+            if (tot0) bulk_g2s(dst, base + inf.x - ph0, tot0, bar);
+            if (tot1) bulk_g2s(dst + half_slot, base + inf.z - ph1, tot1, bar);
+            if (pbytes) {
+                bulk_g2s(raw_a, p0, pbytes, bar);
+                bulk_g2s(raw_a + (KMODE == kKChannel && is_k ? 2 * kD : 2 * P.tile), p1, pbytes, bar);
+            }
         }
-        cp_async_commit();
+    };
+    // with one slot the next item cannot be copied while this one is in use: it is pulled into L2 instead
+    auto prefetch_l2 = [&](int n, uint4 inf2) {
+        if (lane == 0) {
+            const uint8_t* base = n < k_items ? kbase : vbase;
+            const int64_t cap = n < k_items ? a.k_capacity : a.v_capacity;
+            const unsigned bytes = inf2.y + inf2.w;       // a pair's blocks follow each other in the stream
+            if ((int64_t)inf2.x + bytes <= cap && bytes <= 16384u && bytes >= 16u)
+                bulk_prefetch_l2(reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(base + inf2.x) & ~(uintptr_t)15), bytes & ~15u);
+        }
+    };
+    // all lanes wait for item n's copy; a wait that runs out marks the warp dead (it keeps reaching every barrier)
+    auto wait_item = [&](int n) {
+        if (dead) return;
+        const unsigned bar = bar_a + 8 * (n & ns_mask), parity = (unsigned)(n >> (P.nslots - 1)) & 1u;
+        if (!mbar_try_wait(bar, parity)) {
+            unsigned spins = 0;
+            while (!mbar_try_wait(bar, parity)) {
+                if (++spins > kWaitSpins) { dead = true; break; }
+            }
+            dead = __any_sync(0xffffffffu, dead);
+            if (dead && lane == 0) atomicOr(a.flags, kFlagTimeout);
+        }
+    };
+    // natural-order per-token parameters (raw) -> pair order (perm); zero-points take the conversion bias
+    auto permute_params = [&]() {
+        const int quads = P.tile >> 2;                   // (group of eight, e) units per array
+        if (lane < quads) {
+            const int q8 = lane >> 1, e = lane & 1;
+            const unsigned src = raw_a + 16 * q8 + 4 * e, dst = perm_a + 16 * q8 + 8 * (1 - e);
+            unsigned w0, w1;
+            pair_words(lds32(src), lds32(src + 8), w0, w1);
+            sts64(dst, w0, w1);
+            pair_words(lds32(src + 2 * P.tile), lds32(src + 2 * P.tile + 8), w0, w1);
+            if (!HP) {
+                // (bias + code) + (zero - bias) is exact while -bias <= zero and code + zero stays below 2 * bias
+                const T2 z0 = as_t2<T2>(w0), z1 = as_t2<T2>(w1);
+                if (!(__hbge2(z0, nbias2) && __hbge2(z1, nbias2) && __hble2(z0, zmax2) && __hble2(z1, zmax2))) bad_zero = true;
+                w0 = as_u(__hsub2(z0, bias2)); w1 = as_u(__hsub2(z1, bias2));
+            }
+            sts64(dst + 2 * P.tile, w0, w1);
+        }
+        __syncwarp();
     };
 
-    // with one slot the next block cannot be copied while this one is in use: it is pulled into L2 instead
-    auto prefetch_l2 = [&](int n, uint2 inf2) {
-        const uint8_t* src = (n < k_items ? kbase : vbase) + inf2.x;
-        const int64_t cap = n < k_items ? a.k_capacity : a.v_capacity;
-        if ((int64_t)inf2.x + inf2.y <= cap && inf2.y <= 8192u)
-            for (unsigned j = lane * 128u; j < inf2.y; j += 4096u) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + j));
-    };
-    int cur_phase = 0, cur_size = 0, nxt_phase = 0, nxt_size = 0;
-    uint2 inf = make_uint2(0, 0);
-    if (total_items > 0) issue(0, load_info(0), nxt_phase, nxt_size);
+    unsigned cur_pk0 = 0, cur_pk1 = 0, nxt_pk0 = 0, nxt_pk1 = 0;
+    uint4 inf = make_uint4(0, 0, 0, 0);
+    if (total_items > 0) issue(0, load_info(0), nxt_pk0, nxt_pk1);
     if (total_items > 1) inf = load_info(1);
 
-    // unpack table: two 16-byte entries per pack length 0..4 (see unpack_pack)
-    __shared__ uint4 ulut[10];
-    if (threadIdx.x < 5) {
-        const unsigned L = threadIdx.x;
-        ulut[2 * L] = make_uint4(L == 4 ? 0xFFFFu : (1u << (4 * L)) - 1u, ((1u << (2 * L)) - 1u) * 0x00010001u, ((1u << L) - 1u) * 0x01010101u, 4 * L);
-        ulut[2 * L + 1] = make_uint4(16 - 2 * L, 8 - L, 8 * L, 0);
-    }
-    const unsigned ulut_a = smem_addr(ulut);
-    bool bad_len = false;
-    __syncthreads();
-
-    // q fragments: column g of the n-tile is q head g
-    unsigned qf[8][2];
+    // q fragments for the compressed tiles.  The mma step (j, ap) contracts the 16 channels
+    // 64 ap + 32 hf + 8 c' + 4 e + j  (k = 8 hf + 2 c' + e): plane j of the exchange tile, lanes 16 ap .. 16 ap + 15.
+    // From the 8 consecutive elements x0..x7 of channels 32 m + 8 c.. (m = 2 ap + hf) the operand registers are
+    // (x[j], x[j+4]).
+    unsigned qf[4][2][2];
     {
         const uint4* qp = reinterpret_cast<const uint4*>(
             reinterpret_cast<const T*>(a.q) + ((int64_t)(b * q_heads + h * G + min(g, G - 1))) * kD + 8 * c);
 #pragma unroll
         for (int m = 0; m < 4; m++) {
             const uint4 v = g < G ? __ldg(qp + 4 * m) : make_uint4(0, 0, 0, 0);
-            pair_shuffle(v, qf[2 * m], qf[2 * m + 1]);
+            unsigned f0[2], f1[2];
+            pair_shuffle(v, f0, f1);
+            qf[0][m >> 1][m & 1] = f0[0]; qf[1][m >> 1][m & 1] = f0[1];
+            qf[2][m >> 1][m & 1] = f1[0]; qf[3][m >> 1][m & 1] = f1[1];
         }
     }
+    // exchange tile rows: lane l owns row l (32 bytes = 16 token slots) of the plane in flight; the two 16-byte
+    // halves are swapped for rows 4..7 of every eight, which makes both the stores and the matrix loads conflict free
+    const unsigned kst = xch_a + lane * 32, ksw = ((lane >> 2) & 1) << 4;
+    unsigned kldm[2];
+#pragma unroll
+    for (int ap = 0; ap < 2; ap++) {
+        const int row = 16 * ap + 8 * (lane >> 4) + (lane & 7), hf = (lane >> 3) & 1;
+        kldm[ap] = xch_a + row * 32 + ((hf ^ ((row >> 2) & 1)) << 4);
+    }
+    // token (inside a round of 16) whose score this lane's fragment rows g and g+8 carry: slot g holds the low half
+    // of the lower-row registers (6,2) (4,0) (14,10) (12,8), slot g + 8 the token after it
+    const int tau = ((g >> 2) << 3) + ((g & 1) ? ((g & 2) ? 0 : 2) : ((g & 2) ? 4 : 6));
 
-    float mloc0 = -INFINITY, mloc1 = -INFINITY;       // running max of this lane's scores, heads 2c and 2c+1
+    T2 mpk0 = as_t2<T2>(Tr<T>::pack2(-INFINITY, -INFINITY)), mpk1 = mpk0;   // running max of this lane's scores, heads 2c and 2c+1
 
     // ============================================================================ phase 1: K tiles
-    for (int n = 0; n < k_items; n++) {
-        cur_phase = nxt_phase; cur_size = nxt_size;
-        cp_async_wait<0>();
-        __syncwarp();
-        // channel mode: per-(block, channel) scale and zero of this lane's channels, in mma order
-        T2 ksc[8][2], kzb[8][2];
-        if (KMODE == kKChannel) {
-#pragma unroll
-            for (int m = 0; m < 4; m++) {
-                const uint4 sv = lds128(vsz_a + 64 * m + 16 * c), zv = lds128(vsz_a + 256 + 64 * m + 16 * c);
-                unsigned s0[2], s1[2], z0[2], z1[2];
-                pair_shuffle(sv, s0, s1);
-                pair_shuffle(zv, z0, z1);
-                ksc[2 * m][0] = as_t2<T2>(s0[0]); ksc[2 * m][1] = as_t2<T2>(s0[1]);
-                ksc[2 * m + 1][0] = as_t2<T2>(s1[0]); ksc[2 * m + 1][1] = as_t2<T2>(s1[1]);
-                kzb[2 * m][0] = as_t2<T2>(z0[0]); kzb[2 * m][1] = as_t2<T2>(z0[1]);
-                kzb[2 * m + 1][0] = as_t2<T2>(z1[0]); kzb[2 * m + 1][1] = as_t2<T2>(z1[1]);
+    // one block: header, warp scan of the pack lengths, four packs per lane and round
+    auto k_block = [&](auto bits_tag, unsigned blk, int i, unsigned st, const T2 (&ksd)[4], const T2 (&kzb)[4]) {
+        constexpr int BK = decltype(bits_tag)::value, LBK = len_field_bits(BK);
+        int pos = 2 * k_rounds;
+        for (int r = 0; r < k_rounds; r++) {
+            const unsigned hdr = blk + pos;
+            unsigned lens4 = spread_const<LBK>(lane_word<4 * LBK>(hdr + 16 * BK, lane));   // byte j = length of pack j
+            const unsigned mins4 = spread_const<BK>(lane_word<4 * BK>(hdr, lane));
+            if ((lens4 + 0x03030303u) & 0x08080808u) { lens4 = 0; bad_len = true; }   // no encoder writes a length above 4
+            const unsigned inc = warp_inclusive_sum(lens4);
+            const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+            const unsigned exc2 = (inc - lens4) << 1;                 // byte j = byte offset of this lane's pack j in its group
+            const unsigned packs = hdr + 16 * BK + 16 * LBK;
+            unsigned pbase = packs;
+            const int tk0 = (i << P.cbk_shift) + r * 16;              // first token of the round inside the tile
+            uint4 sw[2], zw[2];                                       // token mode: parameter words of the round
+            if (KMODE == kKToken) {
+                sw[0] = lds128(perm_a + 2 * tk0); sw[1] = lds128(perm_a + 2 * tk0 + 16);
+                zw[0] = lds128(perm_a + 2 * P.tile + 2 * tk0); zw[1] = lds128(perm_a + 2 * P.tile + 2 * tk0 + 16);
             }
-            if (!HP) {
+            float accs[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // two chains hide the mma latency
 #pragma unroll
-                for (int j = 0; j < 8; j++) { kzb[j][0] = __hsub2(kzb[j][0], bias2); kzb[j][1] = __hsub2(kzb[j][1], bias2); }
+            for (int j = 0; j < 4; j++) {
+                unsigned lo, hi;
+                ldp_u64_align2(pbase + byte_of(exc2, j), lo, hi);
+                pbase += 2 * byte_of(tot, j);
+                const unsigned len = byte_of(lens4, j);
+                const unsigned m16 = ldp32(lutm_a + 4 * len);
+                const unsigned s1 = 16u - 4u * len;
+                unsigned ra[4], rb[4];
+                unpack8<MAGIC>(__byte_perm(lo, hi, 0x3210u + 0x1111u * len), s1, len, m16, ra);   // tokens 0..7
+                unpack8<MAGIC>(lo, s1, len, m16, rb);                                             // tokens 8..15
+                // bias + pack minimum as an element pair, then the pack minimum alone
+                const T2 mbf = __hadd2(as_t2<T2>(__byte_perm(mins4, Tr<T>::kMagicB, 0x4040 + 0x0101 * j)), nbias2);
+                unsigned x[8];
+                if (KMODE == kKChannel) {
+                    const T2 add = HP ? __hadd2(mbf, nbias2) : __hadd2(kzb[j], mbf);
+                    // in the order of the two stores below, so that each store's registers can be allocated in a row
+                    x[1] = deq<T, HP>(ra[1], add, ksd[j], kzb[j]); x[3] = deq<T, HP>(ra[3], add, ksd[j], kzb[j]);
+                    x[5] = deq<T, HP>(rb[1], add, ksd[j], kzb[j]); x[7] = deq<T, HP>(rb[3], add, ksd[j], kzb[j]);
+                    x[0] = deq<T, HP>(ra[0], add, ksd[j], kzb[j]); x[2] = deq<T, HP>(ra[2], add, ksd[j], kzb[j]);
+                    x[4] = deq<T, HP>(rb[0], add, ksd[j], kzb[j]); x[6] = deq<T, HP>(rb[2], add, ksd[j], kzb[j]);
+                } else {
+                    const unsigned s8[8] = {sw[0].x, sw[0].y, sw[0].z, sw[0].w, sw[1].x, sw[1].y, sw[1].z, sw[1].w};
+                    const unsigned z8[8] = {zw[0].x, zw[0].y, zw[0].z, zw[0].w, zw[1].x, zw[1].y, zw[1].z, zw[1].w};
+                    const T2 cadd = __hadd2(mbf, nbias2);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        x[k] = deq<T, HP>(ra[k], HP ? cadd : __hadd2(as_t2<T2>(z8[k]), mbf), as_t2<T2>(s8[k]), as_t2<T2>(z8[k]));
+                        x[4 + k] = deq<T, HP>(rb[k], HP ? cadd : __hadd2(as_t2<T2>(z8[4 + k]), mbf), as_t2<T2>(s8[4 + k]), as_t2<T2>(z8[4 + k]));
+                    }
+                }
+                // slots 0..7: tokens 6 2 4 0 14 10 12 8; slots 8..15: the tokens after them
+                const unsigned trow = kst + (j & 1) * 1024;
+                sts128(trow + ksw, make_uint4(x[1], x[3], x[5], x[7]));
+                sts128(trow + (ksw ^ 16), make_uint4(x[0], x[2], x[4], x[6]));
+                __syncwarp();
+#pragma unroll
+                for (int ap = 0; ap < 2; ap++) {
+                    unsigned af[4];
+                    ldmatrix_x4_trans(kldm[ap] + (j & 1) * 1024, af);
+                    Tr<T>::mma(accs[PKV_ONE_CHAIN ? 0 : ap], af, qf[j][ap][0], qf[j][ap][1]);
+                }
+            }
+            // scores rounded like the reference: matmul output, then * scaling; fragment rows g and g + 8 are the
+            // tokens tau and tau + 1, which share a store (lanes whose head columns are not kept compute too:
+            // only the stores are predicated, no branch)
+            {
+                const unsigned row0 = st + (2 * c) * P.prow + 2 * (tk0 + tau);
+                const unsigned p0 = Tr<T>::pack2(Tr<T>::round(accs[0][0] + accs[1][0]) * a.scaling, Tr<T>::round(accs[0][2] + accs[1][2]) * a.scaling);
+                const unsigned p1 = Tr<T>::pack2(Tr<T>::round(accs[0][1] + accs[1][1]) * a.scaling, Tr<T>::round(accs[0][3] + accs[1][3]) * a.scaling);
+                if (col_live) sts32(row0, p0);
+                if (col_live) sts32(row0 + P.prow, p1);
+                mpk0 = __hmax2(mpk0, as_t2<T2>(p0));
+                mpk1 = __hmax2(mpk1, as_t2<T2>(p1));
+            }
+            pos += 16 * BK + 16 * LBK + (int)(pbase - packs);
+        }
+    };
+
+    for (int n = 0; n < k_items; n++) {
+        cur_pk0 = nxt_pk0;
+        wait_item(n);
+        if (dead) cur_pk0 = 0;
+        __syncwarp();
+        // channel mode: scale and zero-point of this lane's four channels
+        T2 ksd[4], kzb[4];
+        if (KMODE == kKChannel) {
+            const uint2 sv = lds64(raw_a + 8 * lane), zv = lds64(raw_a + 2 * kD + 8 * lane);
+            ksd[0] = as_t2<T2>(__byte_perm(sv.x, 0, 0x1010)); ksd[1] = as_t2<T2>(__byte_perm(sv.x, 0, 0x3232));
+            ksd[2] = as_t2<T2>(__byte_perm(sv.y, 0, 0x1010)); ksd[3] = as_t2<T2>(__byte_perm(sv.y, 0, 0x3232));
+            if (!HP) {
+                // (bias + code) + (zero - bias) is exact while -bias <= zero and code + zero stays below 2 * bias
+                const T2 z01 = as_t2<T2>(zv.x), z23 = as_t2<T2>(zv.y);
+                if (!(__hbge2(z01, nbias2) && __hbge2(z23, nbias2) && __hble2(z01, zmax2) && __hble2(z23, zmax2))) bad_zero = true;
+                const unsigned y01 = as_u(__hsub2(z01, bias2)), y23 = as_u(__hsub2(z23, bias2));
+                kzb[0] = as_t2<T2>(__byte_perm(y01, 0, 0x1010)); kzb[1] = as_t2<T2>(__byte_perm(y01, 0, 0x3232));
+                kzb[2] = as_t2<T2>(__byte_perm(y23, 0, 0x1010)); kzb[3] = as_t2<T2>(__byte_perm(y23, 0, 0x3232));
+            } else {
+                kzb[0] = as_t2<T2>(__byte_perm(zv.x, 0, 0x1010)); kzb[1] = as_t2<T2>(__byte_perm(zv.x, 0, 0x3232));
+                kzb[2] = as_t2<T2>(__byte_perm(zv.y, 0, 0x1010)); kzb[3] = as_t2<T2>(__byte_perm(zv.y, 0, 0x3232));
             }
             __syncwarp();                              // every lane has its parameters before the next copy lands
         }
-        if (n + 1 < total_items) {
-            if (kSlots == 2) {
-                issue(n + 1, inf, nxt_phase, nxt_size);
+        const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
+        if (KMODE == kKToken && i == 0 && !dead) permute_params();
+        if (n + 1 < total_items && !dead) {
+            if (P.nslots == 2) {
+                issue(n + 1, inf, nxt_pk0, nxt_pk1);
                 if (n + 2 < total_items) inf = load_info(n + 2);
             } else {
                 prefetch_l2(n + 1, inf);
             }
         }
-        const unsigned blk = wbase_a + (kSlots == 2 ? (n & 1) : 0) * P.slot + cur_phase;
-        const int tl = n >> P.nkb_shift, i = n & (nkb - 1);
-        const int t0 = (gw + tl * n_warps) << P.tile_shift;
+        unsigned blk = wbase_a + (n & ns_mask) * P.slot + (cur_pk0 & 15);
+        asm volatile("" : "+r"(blk) :: "memory");          // the reads of the block stay behind the wait for its copy
         const unsigned st = stile_a + tl * P.rows * P.prow;
-
-        if (KMODE == kKToken && i == 0) {
-            const T* ks = reinterpret_cast<const T*>(a.k_scale) + (int64_t)b * a.param_tokens + t0;
-            const T* kz = reinterpret_cast<const T*>(a.k_zero) + (int64_t)b * a.param_tokens + t0;
-            for (int t = lane; t < P.tile; t += 32) {
-                ksz[t] = ks[t];
-                ksz[P.tile + t] = HP ? kz[t] : Tr<T>::from_float(Tr<T>::to_float(kz[t]) - Tr<T>::kBias);
-            }
-            __syncwarp();
-        }
-        if (cur_size > 0) {
-            const int bits_k = a.bits_k;
-            int pos = 2 * k_rounds;
-            for (int r = 0; r < k_rounds; r++) {
-                const unsigned hdr = blk + pos;
-                const unsigned minword = lds_lane_field(hdr, lane, 4 * bits_k);
-                const unsigned lenword = lds_lane_field(hdr + 16 * bits_k, lane, 4 * lbk);
-                unsigned lens4 = spread_fields(lenword, P.klen);          // byte j = length of pack j
-                const unsigned mins4 = spread_fields(minword, P.kmin);
-                if ((lens4 + 0x03030303u) & 0x08080808u) { lens4 = 0; bad_len = true; }   // no encoder writes a length above 4
-                const unsigned inc = warp_inclusive_sum(lens4);
-                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
-                const unsigned exc = inc - lens4;
-                const unsigned packs = hdr + 16 * bits_k + 16 * lbk;
-                const unsigned lidx = lens4 << 5;                          // byte j = offset of the table entry
-                unsigned before = 0;
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    unsigned lo, hi;
-                    lds_u64_align2(packs + 2 * (before + byte_of(exc, j)), lo, hi);
-                    before += byte_of(tot, j);
-                    const unsigned le = ulut_a + byte_of(lidx, j);
-                    const uint4 la = lds128(le), lb = lds128(le + 16);
-                    sts128(kst + 512 * j, unpack_pack(lo, hi, la, lb, __byte_perm(mins4, 0, 0x1111 * j)));
-                }
-                __syncwarp();
-                unsigned fr[4][4];
-#pragma unroll
-                for (int m = 0; m < 4; m++) ldmatrix_x4_trans(kldm + 128 * m, fr[m]);
-                __syncwarp();
-                // Lane (g, c) holds, per plane, channels (row 2c | row 2c+1) x tokens (2(g^1)+1 | 2(g^1)):
-                // fragment row g is token T0 = 2(g^1), row g+8 is token T0 + 1.
-                const int tk = i * a.cbk + r * 16 + 2 * (g ^ 1);
-                T2 sg, zg, sg8, zg8;                         // token mode: per-row scale / zero
-                if (KMODE == kKToken) {
-                    const unsigned sv = lds32(smem_addr(ksz) + 2 * tk), zv = lds32(smem_addr(ksz) + 2 * (P.tile + tk));
-                    sg = as_t2<T2>(__byte_perm(sv, sv, 0x1010)); sg8 = as_t2<T2>(__byte_perm(sv, sv, 0x3232));
-                    zg = as_t2<T2>(__byte_perm(zv, zv, 0x1010)); zg8 = as_t2<T2>(__byte_perm(zv, zv, 0x3232));
-                }
-                float accs[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // two chains hide the mma latency
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const unsigned u0 = fr[j >> 1][2 * (j & 1)], u1 = fr[j >> 1][2 * (j & 1) + 1];
-                    const unsigned a0 = __byte_perm(u0, Tr<T>::kMagic, 0x4341), a1 = __byte_perm(u0, Tr<T>::kMagic, 0x4240);
-                    const unsigned a2 = __byte_perm(u1, Tr<T>::kMagic, 0x4341), a3 = __byte_perm(u1, Tr<T>::kMagic, 0x4240);
-                    unsigned af[4];
-                    if (KMODE == kKChannel) {
-                        af[0] = deq2<T, HP>(a0, kzb[j][0], ksc[j][0]);
-                        af[1] = deq2<T, HP>(a1, kzb[j][0], ksc[j][0]);
-                        af[2] = deq2<T, HP>(a2, kzb[j][1], ksc[j][1]);
-                        af[3] = deq2<T, HP>(a3, kzb[j][1], ksc[j][1]);
-                    } else {
-                        af[0] = deq2<T, HP>(a0, zg, sg);
-                        af[1] = deq2<T, HP>(a1, zg8, sg8);
-                        af[2] = deq2<T, HP>(a2, zg, sg);
-                        af[3] = deq2<T, HP>(a3, zg8, sg8);
-                    }
-                    Tr<T>::mma(accs[j & 1], af, qf[j][0], qf[j][1]);
-                }
-                // scores rounded like the reference: matmul output, then * scaling; tokens T0, T0+1 share a store
-                // (lanes whose head columns are not kept compute too: only the stores are predicated, no branch)
-                {
-                    const unsigned row0 = st + (2 * c) * P.prow + 2 * tk;
-                    const unsigned p0 = Tr<T>::pack2(Tr<T>::round(accs[0][0] + accs[1][0]) * a.scaling, Tr<T>::round(accs[0][2] + accs[1][2]) * a.scaling);
-                    const unsigned p1 = Tr<T>::pack2(Tr<T>::round(accs[0][1] + accs[1][1]) * a.scaling, Tr<T>::round(accs[0][3] + accs[1][3]) * a.scaling);
-                    if (col_live) sts32(row0, p0);
-                    if (col_live) sts32(row0 + P.prow, p1);
-                    const float2 f0 = Tr<T>::unpack2(p0), f1 = Tr<T>::unpack2(p1);
-                    mloc0 = fmaxf(mloc0, fmaxf(f0.x, f0.y));
-                    mloc1 = fmaxf(mloc1, fmaxf(f1.x, f1.y));
-                }
-                pos += 16 * bits_k + 16 * lbk + 2 * (int)before;
+        if (cur_pk0 != 0 && !(PKV_ABL & 2)) {
+            switch (a.bits_k) {
+                case 4: k_block(std::integral_constant<int, 4>{}, blk, i, st, ksd, kzb); break;
+                case 3: k_block(std::integral_constant<int, 3>{}, blk, i, st, ksd, kzb); break;
+                default: k_block(std::integral_constant<int, 2>{}, blk, i, st, ksd, kzb); break;
             }
         }
         __syncwarp();
-        if (kSlots == 1 && n + 1 < total_items) {
-            issue(n + 1, inf, nxt_phase, nxt_size);
+        if (P.nslots == 1 && n + 1 < total_items && !dead) {
+            issue(n + 1, inf, nxt_pk0, nxt_pk1);
             if (n + 2 < total_items) inf = load_info(n + 2);
         }
+    }
+    float mloc0, mloc1;
+    {
+        const float2 m0 = Tr<T>::unpack2(as_u(mpk0)), m1 = Tr<T>::unpack2(as_u(mpk1));
+        mloc0 = fmaxf(m0.x, m0.y); mloc1 = fmaxf(m1.x, m1.y);
     }
 
     // ---- residual tiles, phase 1: scores -------------------------------------------------------
     // A fragments come straight from the uncompressed rows: lane (g, c) reads channels
-    // 32m + 8c .. +7 (m = 0..3) of tokens g and g+8 and pairs them in the order of the q fragments.
+    // 32m + 8c .. +7 (m = 0..3) of tokens g and g+8 and pairs them in the order of pair_shuffle.
     const T* kres = reinterpret_cast<const T*>(a.k_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
     const T* vres = reinterpret_cast<const T*>(a.v_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
-    for (int k = 0; k < my_rt; k++) {
-        const int tok0 = (rslot + k * n_warps) << 4;
-        const int ta = tok0 + g, tb = tok0 + g + 8;
-        const uint4* pa = reinterpret_cast<const uint4*>(kres + (int64_t)min(ta, a.n_res - 1) * kD + 8 * c);
-        const uint4* pb = reinterpret_cast<const uint4*>(kres + (int64_t)min(tb, a.n_res - 1) * kD + 8 * c);
-        uint4 ra[4], rb[4];
-#pragma unroll
-        for (int m = 0; m < 4; m++) { ra[m] = __ldg(pa + 4 * m); rb[m] = __ldg(pb + 4 * m); }
-        float accs[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    if (my_rt > 0) {
+        unsigned qr[8][2];
+        const uint4* qp = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const T*>(a.q) + ((int64_t)(b * q_heads + h * G + min(g, G - 1))) * kD + 8 * c);
 #pragma unroll
         for (int m = 0; m < 4; m++) {
-            unsigned a0[2], a1[2], b0[2], b1[2];
-            pair_shuffle(ra[m], a0, a1);
-            pair_shuffle(rb[m], b0, b1);
-            const unsigned f0[4] = {a0[0], b0[0], a0[1], b0[1]};
-            const unsigned f1[4] = {a1[0], b1[0], a1[1], b1[1]};
-            Tr<T>::mma(accs[0], f0, qf[2 * m][0], qf[2 * m][1]);
-            Tr<T>::mma(accs[1], f1, qf[2 * m + 1][0], qf[2 * m + 1][1]);
+            const uint4 v = g < G ? __ldg(qp + 4 * m) : make_uint4(0, 0, 0, 0);
+            pair_shuffle(v, qr[2 * m], qr[2 * m + 1]);
         }
-        if (col_live) {
-            const float ninf = -INFINITY;
-            const float sa0 = ta < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][0] + accs[1][0]) * a.scaling) : ninf;
-            const float sa1 = ta < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][1] + accs[1][1]) * a.scaling) : ninf;
-            const float sb0 = tb < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][2] + accs[1][2]) * a.scaling) : ninf;
-            const float sb1 = tb < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][3] + accs[1][3]) * a.scaling) : ninf;
-            const unsigned row0 = rst_a + (k * P.rows + 2 * c) * 32 + 2 * g, row1 = row0 + 32;
-            const T h00 = Tr<T>::from_float(sa0), h01 = Tr<T>::from_float(sa1), h10 = Tr<T>::from_float(sb0), h11 = Tr<T>::from_float(sb1);
-            sts16(row0, *reinterpret_cast<const unsigned short*>(&h00)); sts16(row1, *reinterpret_cast<const unsigned short*>(&h01));
-            sts16(row0 + 16, *reinterpret_cast<const unsigned short*>(&h10)); sts16(row1 + 16, *reinterpret_cast<const unsigned short*>(&h11));
-            mloc0 = fmaxf(mloc0, fmaxf(sa0, sb0));
-            mloc1 = fmaxf(mloc1, fmaxf(sa1, sb1));
+        for (int k = 0; k < my_rt; k++) {
+            const int tok0 = (rslot + k * n_warps) << 4;
+            const int ta = tok0 + g, tb = tok0 + g + 8;
+            const uint4* pa = reinterpret_cast<const uint4*>(kres + (int64_t)min(ta, a.n_res - 1) * kD + 8 * c);
+            const uint4* pb = reinterpret_cast<const uint4*>(kres + (int64_t)min(tb, a.n_res - 1) * kD + 8 * c);
+            uint4 ra[4], rb[4];
+#pragma unroll
+            for (int m = 0; m < 4; m++) { ra[m] = __ldg(pa + 4 * m); rb[m] = __ldg(pb + 4 * m); }
+            float accs[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                unsigned a0[2], a1[2], b0[2], b1[2];
+                pair_shuffle(ra[m], a0, a1);
+                pair_shuffle(rb[m], b0, b1);
+                const unsigned f0[4] = {a0[0], b0[0], a0[1], b0[1]};
+                const unsigned f1[4] = {a1[0], b1[0], a1[1], b1[1]};
+                Tr<T>::mma(accs[0], f0, qr[2 * m][0], qr[2 * m][1]);
+                Tr<T>::mma(accs[1], f1, qr[2 * m + 1][0], qr[2 * m + 1][1]);
+            }
+            if (col_live) {
+                const float ninf = -INFINITY;
+                const float sa0 = ta < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][0] + accs[1][0]) * a.scaling) : ninf;
+                const float sa1 = ta < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][1] + accs[1][1]) * a.scaling) : ninf;
+                const float sb0 = tb < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][2] + accs[1][2]) * a.scaling) : ninf;
+                const float sb1 = tb < a.n_res ? Tr<T>::round(Tr<T>::round(accs[0][3] + accs[1][3]) * a.scaling) : ninf;
+                const unsigned row0 = rst_a + (k * P.rows + 2 * c) * 32 + 2 * g, row1 = row0 + 32;
+                const T h00 = Tr<T>::from_float(sa0), h01 = Tr<T>::from_float(sa1), h10 = Tr<T>::from_float(sb0), h11 = Tr<T>::from_float(sb1);
+                sts16(row0, *reinterpret_cast<const unsigned short*>(&h00)); sts16(row1, *reinterpret_cast<const unsigned short*>(&h01));
+                sts16(row0 + 16, *reinterpret_cast<const unsigned short*>(&h10)); sts16(row1 + 16, *reinterpret_cast<const unsigned short*>(&h11));
+                mloc0 = fmaxf(mloc0, fmaxf(sa0, sb0));
+                mloc1 = fmaxf(mloc1, fmaxf(sa1, sb1));
+            }
         }
     }
 
@@ -608,128 +783,159 @@ __global__ void __launch_bounds__(kAW * 32, kCtasPerSm) attn_decode_kernel(const
 #pragma unroll
         for (int j = 0; j < 4; j++) o[i][j] = 0.f;
 
+    // One V block (cbv tokens x 64 channels).  A segment is 64 tokens x 32 channels; lane l of the warp owns
+    // channel l's four packs in the stream (lengths, minima, offsets), while the mma wants lane (g, c) to hold
+    // channels g, g+8, g+16, g+24 for the 16 tokens of quarter c: the owners publish their pack descriptors
+    // and every lane fetches the four packs its fragment rows need.
+    auto v_block = [&](auto bits_tag, unsigned blk, int hh, int tok_blk, unsigned st_a) {
+        constexpr int BV = decltype(bits_tag)::value, LBV = len_field_bits(BV);
+        const int rpw_shift = a.cbv == 128 ? 1 : 0;
+        const int nseg = 2 << rpw_shift;
+        int pos = 2 * nseg;
+        for (int sgi = 0; sgi < nseg; sgi++) {
+            const int w = sgi >> rpw_shift, rr = sgi & ((1 << rpw_shift) - 1);
+            const int tok_seg = tok_blk + rr * 64;     // first token (in the tile) of the segment
+            const unsigned hdr = blk + pos;
+            unsigned lens4 = spread_const<LBV>(lane_word<4 * LBV>(hdr + 16 * BV, lane));   // byte q = length of pack q (tokens 16q..16q+15)
+            const unsigned mins4 = spread_const<BV>(lane_word<4 * BV>(hdr, lane));
+            if ((lens4 + 0x03030303u) & 0x08080808u) { lens4 = 0; bad_len = true; }
+            const unsigned inc = warp_inclusive_sum(lens4);
+            const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+            const unsigned packs = hdr + 16 * BV + 16 * LBV;
+            sts32(desc_a + 4 * lane, (inc - lens4) << 1);
+            sts32(desc_a + 128 + 4 * lane, lens4);
+            sts32(desc_a + 256 + 4 * lane, mins4);
+            // start of quarter c's packs: the quarters before it hold tot[0..c-1] halfwords
+            const unsigned t01 = (tot & 0xFFu) + ((tot >> 8) & 0xFFu), t012 = t01 + ((tot >> 16) & 0xFFu);
+            const unsigned before = c == 0 ? 0u : c == 1 ? (tot & 0xFFu) : c == 2 ? t01 : t012;
+            const unsigned qbase = packs + 2 * before;
+            __syncwarp();
+            // per-token scale / zero pairs and probabilities for tokens tok_seg + 16c .. +15, in pair order
+            const unsigned tok2 = 2 * (tok_seg + 16 * c);
+            const uint4 s0 = lds128(perm_a + tok2), s1 = lds128(perm_a + tok2 + 16);
+            const uint4 z0 = lds128(perm_a + 2 * P.tile + tok2), z1 = lds128(perm_a + 2 * P.tile + tok2 + 16);
+            const unsigned vS[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            const unsigned vZ[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+            // head columns beyond the kept rows read a kept row: their output columns are never used
+            const unsigned prow_a = st_a + min(g, P.rows - 1) * P.prow + tok2;
+            const uint4 p0 = lds128(prow_a), p1 = lds128(prow_a + 16);
+            const unsigned pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+            const int sel = 2 * hh + w;
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                unsigned x[2][8];                      // rows g (channel g + 16 mt) and g + 8 (channel g + 8 + 16 mt)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const unsigned da = desc_a + 4 * (g + 8 * (2 * mt + e)) + c;    // byte c of the owner's words
+                    const unsigned len = lds8(da + 128);
+                    unsigned lo, hi;
+                    ldp_u64_align2(qbase + lds8(da), lo, hi);
+                    const unsigned m16 = ldp32(lutm_a + 4 * len);
+                    const unsigned sh1 = 16u - 4u * len;
+                    unsigned ra[4], rb[4];
+                    unpack8<MAGIC>(__byte_perm(lo, hi, 0x3210u + 0x1111u * len), sh1, len, m16, ra);
+                    unpack8<MAGIC>(lo, sh1, len, m16, rb);
+                    const T2 mbf = __hadd2(as_t2<T2>(__byte_perm(lds8(da + 256), Tr<T>::kMagicB, 0x4040)), nbias2);
+                    const T2 cadd = __hadd2(mbf, nbias2);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        x[e][k] = deq<T, HP>(ra[k], HP ? cadd : __hadd2(as_t2<T2>(vZ[k]), mbf), as_t2<T2>(vS[k]), as_t2<T2>(vZ[k]));
+                        x[e][4 + k] = deq<T, HP>(rb[k], HP ? cadd : __hadd2(as_t2<T2>(vZ[4 + k]), mbf), as_t2<T2>(vS[4 + k]), as_t2<T2>(vZ[4 + k]));
+                    }
+                }
+                // four steps of 16 token slots: step s takes the words 2s and 2s+1 of every quarter
+#pragma unroll
+                for (int idx = 0; idx < 4; idx++) {
+                    if (idx == sel) {
+#pragma unroll
+                        for (int s = 0; s < 4; s++) {
+                            const unsigned af[4] = {x[0][2 * s], x[1][2 * s], x[0][2 * s + 1], x[1][2 * s + 1]};
+                            Tr<T>::mma(o[2 * idx + mt], af, pw[2 * s], pw[2 * s + 1]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();                              // descriptors are rewritten by the next segment
+            pos += 16 * BV + 16 * LBV + 2 * (int)(t012 + (tot >> 24));
+        }
+    };
+
     for (int n = k_items; n < total_items; n++) {
-        cur_phase = nxt_phase; cur_size = nxt_size;
-        cp_async_wait<0>();
+        cur_pk0 = nxt_pk0; cur_pk1 = nxt_pk1;
+        wait_item(n);
+        if (dead) { cur_pk0 = 0; cur_pk1 = 0; }
         __syncwarp();
-        if (n + 1 < total_items) {
-            if (kSlots == 2) {
-                issue(n + 1, inf, nxt_phase, nxt_size);
+        const int m = n - k_items;
+        const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
+        const unsigned st_a = stile_a + tl * P.rows * P.prow;
+
+        if (vi == 0 && !dead) {
+            // the tile's V scales and zero-points, pair order
+            permute_params();
+            // scores -> probabilities rounded to the element type, in place, pair order: unit u = (row, group of
+            // eight tokens, e); loads of up to four units per lane, a warp barrier, then the stores
+            const int pr_shift = P.tile_shift - 2, units = P.rows << pr_shift;
+            for (int u0 = 0; u0 < units; u0 += 128) {
+                unsigned w0[4], w1[4];
+#pragma unroll
+                for (int it = 0; it < 4; it++) {
+                    const int u = u0 + 32 * it + lane;
+                    if (u < units) {
+                        const int r = u >> pr_shift, rem = u & ((1 << pr_shift) - 1), q8 = rem >> 1, e = rem & 1;
+                        const unsigned ad = st_a + r * P.prow + 16 * q8 + 4 * e;
+                        const float M = cs->gM[r], I = cs->gInvL[r];
+                        const float2 xa = Tr<T>::unpack2(lds32(ad)), xb = Tr<T>::unpack2(lds32(ad + 8));
+                        const unsigned pa = Tr<T>::pack2(fast_exp(xa.x - M) * I, fast_exp(xa.y - M) * I);
+                        const unsigned pb = Tr<T>::pack2(fast_exp(xb.x - M) * I, fast_exp(xb.y - M) * I);
+                        pair_words(pa, pb, w0[it], w1[it]);
+                    }
+                }
+                __syncwarp();
+#pragma unroll
+                for (int it = 0; it < 4; it++) {
+                    const int u = u0 + 32 * it + lane;
+                    if (u < units) {
+                        const int r = u >> pr_shift, rem = u & ((1 << pr_shift) - 1), q8 = rem >> 1, e = rem & 1;
+                        sts64(st_a + r * P.prow + 16 * q8 + 8 * (1 - e), w0[it], w1[it]);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        if (n + 1 < total_items && !dead) {
+            if (P.nslots == 2) {
+                issue(n + 1, inf, nxt_pk0, nxt_pk1);
                 if (n + 2 < total_items) inf = load_info(n + 2);
             } else {
                 prefetch_l2(n + 1, inf);
             }
         }
-        const unsigned blk = wbase_a + (kSlots == 2 ? (n & 1) : 0) * P.slot + cur_phase;
-        const int m = n - k_items;
-        const int tl = m >> P.nvi_shift, vi = m & (nvi - 1);
-        const unsigned st_a = stile_a + tl * P.rows * P.prow;
-
-        if (vi == 0) {
-            // scores -> probabilities rounded to the element type, in place; V scale / zero of the tile
-#pragma unroll
-            for (int r = 0; r < 8; r++) {
-                if (r < P.rows) {
-                    const float M = cs->gM[r], I = cs->gInvL[r];
-                    for (int ch = 0; ch < (P.tile >> 6); ch++) {
-                        const unsigned ad = st_a + r * P.prow + 128 * ch + 4 * lane;
-                        const float2 x = Tr<T>::unpack2(lds32(ad));
-                        sts32(ad, Tr<T>::pack2(fast_exp(x.x - M) * I, fast_exp(x.y - M) * I));
-                    }
+        unsigned sbase = wbase_a + (n & ns_mask) * P.slot;
+        asm volatile("" : "+r"(sbase) :: "memory");        // the reads of the blocks stay behind the wait for their copy
+        if (!(PKV_ABL & 1)) {
+#pragma unroll 1
+            for (int sub = 0; sub < (P.vpair ? 2 : 1); sub++) {
+                const unsigned pk = sub ? cur_pk1 : cur_pk0;
+                if (pk == 0) continue;
+                const unsigned blk = sbase + sub * half_slot + (pk & 15);
+                const int hh = P.vpair ? sub : vi;                       // which 64-channel half of the head
+                const int tok_blk = P.vpair ? (vi << 6) : 0;             // token offset of the block in the tile
+                switch (a.bits_v) {
+                    case 4: v_block(std::integral_constant<int, 4>{}, blk, hh, tok_blk, st_a); break;
+                    case 3: v_block(std::integral_constant<int, 3>{}, blk, hh, tok_blk, st_a); break;
+                    default: v_block(std::integral_constant<int, 2>{}, blk, hh, tok_blk, st_a); break;
                 }
-            }
-            if (!HP) {
-                // the tile's zero-points take the conversion bias once here instead of in every segment
-                const unsigned zb = vsz_a + (tl & 1) * 4 * P.tile + 2 * P.tile;
-                for (int t = lane; t < (P.tile >> 1); t += 32) sts32(zb + 4 * t, as_u(__hsub2(as_t2<T2>(lds32(zb + 4 * t)), bias2)));
-            }
-            __syncwarp();
-        }
-        if (cur_size > 0) {
-            const int hh = vi & 1;                         // which 64-channel half of the head
-            const int tok_blk = (vi >> 1) << P.cbv_shift;  // token offset of the block in the tile
-            const int rpw_shift = a.cbv == 128 ? 1 : 0;
-            const int nseg = 2 << rpw_shift;
-            const int bits_v = a.bits_v;
-            int pos = 2 * nseg;
-            for (int sgi = 0; sgi < nseg; sgi++) {
-                const int w = sgi >> rpw_shift, rr = sgi & ((1 << rpw_shift) - 1);
-                const int tok_seg = tok_blk + rr * 64;     // first token (in the tile) of the segment
-                const unsigned hdr = blk + pos;
-                const unsigned minword = lds_lane_field(hdr, lane, 4 * bits_v);
-                const unsigned lenword = lds_lane_field(hdr + 16 * bits_v, lane, 4 * lbv);
-                unsigned lens4 = spread_fields(lenword, P.vlen);          // byte q = length of pack q (tokens 16q..16q+15)
-                const unsigned mins4 = spread_fields(minword, P.vmin);
-                if ((lens4 + 0x03030303u) & 0x08080808u) { lens4 = 0; bad_len = true; }
-                const unsigned inc = warp_inclusive_sum(lens4);
-                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
-                const unsigned exc = inc - lens4;
-                const unsigned packs = hdr + 16 * bits_v + 16 * lbv;
-                const unsigned lidx = lens4 << 5;
-                unsigned before = 0;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; q4++) {
-                    unsigned lo, hi;
-                    lds_u64_align2(packs + 2 * (before + byte_of(exc, q4)), lo, hi);
-                    before += byte_of(tot, q4);
-                    const unsigned le = ulut_a + byte_of(lidx, q4);
-                    const uint4 la = lds128(le), lb = lds128(le + 16);
-                    // row = lane (channel), logical 16-byte chunk q4, swizzled; byte p of the chunk is token 16*q4 + (p ^ 3)
-                    sts128(vst + ((q4 << 4) ^ vsw), unpack_pack(lo, hi, la, lb, __byte_perm(mins4, 0, 0x1111 * q4)));
-                }
-                __syncwarp();
-                // per-token scale / zero pairs and probabilities for tokens tok_seg + 16c .. +15
-                const unsigned tok2 = 2 * (tok_seg + 16 * c);      // byte offset of this lane's 16 tokens in a row of halves
-                const unsigned vpar = vsz_a + (tl & 1) * 4 * P.tile + tok2;   // this tile's parameter buffer
-                const uint4 s0 = lds128(vpar), s1 = lds128(vpar + 16);
-                const uint4 z0 = lds128(vpar + 2 * P.tile), z1 = lds128(vpar + 2 * P.tile + 16);
-                // head columns beyond the kept rows read a kept row: their output columns are never used
-                const unsigned prow_a = st_a + min(g, P.rows - 1) * P.prow + tok2;
-                const uint4 p0 = lds128(prow_a), p1 = lds128(prow_a + 16);
-                const unsigned vS[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-                const unsigned vZ[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
-                const unsigned pf[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-                // A fragments for both 16-channel row tiles, then the contraction into the
-                // accumulator group of this (64-channel half, warp half): static register
-                // indices, so the select is unrolled
-                unsigned afr[2][4][4];
-#pragma unroll
-                for (int mt = 0; mt < 2; mt++) {
-                    const uint4 xa = lds128(vld + (16 * mt) * 64), xb = lds128(vld + (16 * mt + 8) * 64);
-                    const unsigned ua[4] = {xa.x, xa.y, xa.z, xa.w};
-                    const unsigned ub[4] = {xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        // bytes of a word are tokens 4j+3, 4j+2, 4j+1, 4j
-                        afr[mt][j][0] = deq2<T, HP>(__byte_perm(ua[j], Tr<T>::kMagic, 0x4243), as_t2<T2>(vZ[2 * j]), as_t2<T2>(vS[2 * j]));
-                        afr[mt][j][1] = deq2<T, HP>(__byte_perm(ub[j], Tr<T>::kMagic, 0x4243), as_t2<T2>(vZ[2 * j]), as_t2<T2>(vS[2 * j]));
-                        afr[mt][j][2] = deq2<T, HP>(__byte_perm(ua[j], Tr<T>::kMagic, 0x4041), as_t2<T2>(vZ[2 * j + 1]), as_t2<T2>(vS[2 * j + 1]));
-                        afr[mt][j][3] = deq2<T, HP>(__byte_perm(ub[j], Tr<T>::kMagic, 0x4041), as_t2<T2>(vZ[2 * j + 1]), as_t2<T2>(vS[2 * j + 1]));
-                    }
-                }
-                const int sel = 2 * hh + w;
-#pragma unroll
-                for (int idx = 0; idx < 4; idx++) {
-                    if (idx == sel) {
-#pragma unroll
-                        for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-                            for (int j = 0; j < 4; j++) Tr<T>::mma(o[2 * idx + mt], afr[mt][j], pf[2 * j], pf[2 * j + 1]);
-                    }
-                }
-                __syncwarp();
-                pos += 16 * bits_v + 16 * lbv + 2 * (int)before;
             }
         }
         __syncwarp();
-        if (kSlots == 1 && n + 1 < total_items) {
-            issue(n + 1, inf, nxt_phase, nxt_size);
+        if (P.nslots == 1 && n + 1 < total_items && !dead) {
+            issue(n + 1, inf, nxt_pk0, nxt_pk1);
             if (n + 2 < total_items) inf = load_info(n + 2);
         }
     }
-    cp_async_wait<0>();
     __syncwarp();
     if (__any_sync(0xffffffffu, bad_len) && lane == 0) atomicOr(a.flags, kFlagBadStream);
+    if (__any_sync(0xffffffffu, bad_zero) && lane == 0) atomicOr(a.flags, kFlagZeroRange);
 
     // ---- residual tiles, phase 2: probabilities x V ---------------------------------------------
     // The tile's 16 V rows are staged (padded to 272 bytes so that ldmatrix is conflict free) in the
@@ -835,6 +1041,44 @@ static int launch_typed(const AttnDev& P, dim3 grid, int smem, cudaStream_t st) 
     return a.high_precision_zero ? launch_one<T, kKToken, true>(P, grid, smem, st) : launch_one<T, kKToken, false>(P, grid, smem, st);
 }
 
+// tuning overrides read once from the environment (0 = choose automatically)
+static int env_int(const char* name) {
+    const char* v = std::getenv(name);
+    return v ? std::atoi(v) : 0;
+}
+
+// shared memory of one CTA for a cluster of `cl` CTAs with `nslots` staging slots per warp; fills the layout fields
+static int plan_smem(AttnDev& P, int cl, int nslots, int slot) {
+    const AttnArgs& a = P.a;
+    const int n_warps = kAW * cl;
+    P.cluster = cl;
+    P.nslots = nslots;
+    P.slot = slot;
+    P.tpw = (P.tiles_total + n_warps - 1) / n_warps;
+    P.rtw = ((a.n_res + 15) / 16 + n_warps - 1) / n_warps;
+    int off = nslots * slot;
+    if (off < 16 * 272) off = 16 * 272;                       // the residual V tile borrows the staging slots
+    if (off < 8 * kD * 4) off = 8 * kD * 4;                   // and so do the parked accumulators
+    P.out_off = off;                                          // the CTA's reduced rows sit behind them
+    P.off_xch = off; off += 2048;                             // (>= 2 * kD * 4 bytes: two heads' rows per warp)
+    // The parameter staging, the pair-order parameters and the V descriptors are idle while the K exchange tile
+    // is in use when K has per-channel parameters and the next item is only copied after the current one is
+    // done (one slot): the parameters of a block are in registers before its first round.  They share the tile then.
+    const int raw_bytes = 4 * P.tile > 4 * kD ? 4 * P.tile : 4 * kD;
+    if (a.k_mode == kKChannel && nslots == 1 && raw_bytes + 4 * P.tile + 384 <= 2048) {
+        P.off_raw = P.off_xch; P.off_perm = P.off_raw + raw_bytes; P.off_desc = P.off_perm + 4 * P.tile;
+    } else {
+        P.off_raw = off; off += raw_bytes;
+        P.off_perm = off; off += 4 * P.tile;
+        P.off_desc = off; off += 384;
+    }
+    P.off_stile = off; off += P.tpw * P.rows * P.prow;
+    P.off_rst = off; off += P.rtw * P.rows * 32;
+    P.warp_smem = (off + 15) & ~15;
+    P.cta_off = kAW * P.warp_smem;
+    return P.cta_off + (int)sizeof(CtaShared);
+}
+
 int launch_attention(const AttnArgs& a, cudaStream_t st) {
     if (a.batch <= 0 || a.kv_heads <= 0 || a.group < 1 || a.group > 8) return a.group > 8 ? kUnsupported : kBadArgument;
     if (a.n_comp < 0 || a.n_res < 0 || a.n_comp + a.n_res == 0) return kBadArgument;
@@ -870,43 +1114,57 @@ int launch_attention(const AttnArgs& a, cudaStream_t st) {
     P.cbk_shift = a.n_comp > 0 ? lg2(a.cbk) : 6;
     P.cbv_shift = a.n_comp > 0 ? lg2(a.cbv) : 6;
     P.nkb_shift = P.tile_shift - P.cbk_shift;
-    P.nvi_shift = P.tile_shift - P.cbv_shift + 1;
+    P.vpair = a.n_comp > 0 && a.cbv == 64;
+    P.nvi_shift = P.vpair ? P.tile_shift - 6 : 1;   // V items per tile: token blocks of 64 (as pairs) or the two halves of a 128-token block
     if (a.n_comp > 0) {
         P.klen = make_field_spread(len_field_bits(a.bits_k)); P.kmin = make_field_spread(a.bits_k);
         P.vlen = make_field_spread(len_field_bits(a.bits_v)); P.vmin = make_field_spread(a.bits_v);
     }
-    // cluster size: enough CTAs for ~2 waves of the 148 SMs (3 CTAs each), but at least one
-    // tile per warp; a long sequence must also fit its scores in shared memory
-    const long pairs = (long)a.batch * a.kv_heads;
-    const int units = P.tiles_total + (a.n_res + 15) / 16;
-    int cl = 1;
-    while (cl < 8 && pairs * cl < 2L * 148 * 3 && units > kAW * cl) cl *= 2;
     P.rows = (a.group + 1) & ~1;
     P.prow = 2 * P.tile + 16;
     int slot = 0;
     if (a.n_comp > 0) {
         const int kb = k_bound(a.cbk, a.bits_k), vb = v_bound(a.cbv, a.bits_v);
-        slot = ((kb > vb ? kb : vb) + 48 + 15) & ~15;
+        P.kbound = kb; P.vbound = vb;
+        const int ks = (kb + 48 + 15) & ~15;                   // 15 bytes of phase, 16 of round-up, window reads past the end
+        const int vs = P.vpair ? 2 * ((vb + 48 + 15) & ~15) : (vb + 48 + 15) & ~15;
+        slot = ((ks > vs ? ks : vs) + 31) & ~31;                // the halves of a slot are 16-byte aligned
     }
-    if (a.n_res > 0 && kSlots * slot < 16 * 272) slot = 16 * 272 / kSlots;   // the residual V tile borrows the staging slots
-    P.slot = slot;
-    int smem = 0;
-    for (;;) {
-        P.cluster = cl;
-        const int n_warps = kAW * cl;
-        P.tpw = (P.tiles_total + n_warps - 1) / n_warps;
-        P.rtw = ((a.n_res + 15) / 16 + n_warps - 1) / n_warps;
-        int warp_smem = kSlots * slot + 2048 + 8 * P.tile + P.tpw * P.rows * P.prow + P.rtw * P.rows * 32;
-        P.out_off = kSlots * slot > 8 * kD * 4 ? kSlots * slot : 8 * kD * 4;   // behind the parked accumulators
-        const int red_need = P.out_off + 2 * kD * 4;
-        if (warp_smem < red_need) warp_smem = red_need;
-        P.warp_smem = (warp_smem + 15) & ~15;
-        P.cta_off = kAW * P.warp_smem;
-        smem = P.cta_off + (int)sizeof(CtaShared);
-        if (smem <= 200 * 1024 || cl >= 16) break;
-        cl *= 2;                                          // long sequence: spread the scores over more CTAs
+    // Cluster size and staging depth: the (sequence, KV head) pairs times the cluster size should fill the
+    // 148 SMs' CTA slots in whole waves, every warp should have work, and a long sequence must fit its scores
+    // in shared memory.  Cost model: waves x work units per warp x (resident warps beyond 16 per SM share
+    // the issue slots).
+    static const int env_cl = env_int("PKV_ATTN_CLUSTER"), env_slots = env_int("PKV_ATTN_SLOTS");
+    const long pairs = (long)a.batch * a.kv_heads;
+    const int units = P.tiles_total * (P.tile / 64) * 4 + (a.n_res + 15) / 16;   // a residual tile is about a quarter of 64 compressed tokens
+    const int unit_tile = (P.tile / 64) * 4;
+    int best_cl = 0, best_ns = 1, best_smem = 0;
+    double best_cost = 1e300;
+    for (int cl = 1; cl <= 16; cl++) {
+        if (env_cl && cl != env_cl) continue;
+        for (int ns = 2; ns >= 1; ns--) {
+            if (env_slots && ns != env_slots) continue;
+            AttnDev Q = P;
+            const int smem = plan_smem(Q, cl, ns, slot);
+            if (smem > 227 * 1024) continue;
+            int per_sm = (228 * 1024) / (smem + 1024);
+            if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
+            if (per_sm < 1) continue;
+            const long ctas = pairs * cl, slots = (long)kSmCount * per_sm;
+            const long waves = (ctas + slots - 1) / slots;
+            const double resident = (double)(ctas < slots ? ctas : slots) / kSmCount * kAW;   // warps per SM
+            const int n_warps = kAW * cl;
+            const int upw = ((P.tiles_total + n_warps - 1) / n_warps) * unit_tile + (((a.n_res + 15) / 16 + n_warps - 1) / n_warps);
+            double cost = (double)waves * (upw + 3.0 /* fixed part per CTA: exchange, reductions */) * (resident > 16.0 ? resident / 16.0 : 1.0);
+            if (ns == 1) cost *= 1.06;                          // the copy of the next block is not overlapped
+            if (cl > 8) cost *= 1.10;                           // non-portable cluster sizes schedule worse
+            if (cost < best_cost - 1e-9) { best_cost = cost; best_cl = cl; best_ns = ns; best_smem = smem; }
+        }
     }
-    if (smem > 227 * 1024) return kUnsupported;
+    (void)units;
+    if (best_cl == 0) return kUnsupported;
+    const int smem = plan_smem(P, best_cl, best_ns, slot);
+    (void)best_smem;
     dim3 grid(P.cluster, a.kv_heads, a.batch);
     return a.is_bf16 ? launch_typed<__nv_bfloat16>(P, grid, smem, st) : launch_typed<__half>(P, grid, smem, st);
 }

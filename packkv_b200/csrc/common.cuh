@@ -29,6 +29,7 @@ enum DevFlag : unsigned {
     kFlagCodeRange = 2u,        // a quantised code did not fit the requested bit width
     kFlagBadStream = 4u,        // a block_info entry or header points outside the stream
     kFlagTimeout = 8u,          // a bounded wait gave up
+    kFlagZeroRange = 16u,       // a zero-point outside the range in which the in-kernel dequantisation is exact
 };
 
 __host__ __device__ constexpr int len_field_bits(int raw_bits) {

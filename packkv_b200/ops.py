@@ -193,6 +193,10 @@ class CompressedLayer:
         return n
 
 
+# changes whenever the attention kernel changes in a way that can change its DRAM traffic (keys recorded profiler figures)
+ATTN_KERNEL_REVISION = 2
+
+
 def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: Optional[torch.Tensor],
                      v_res: Optional[torch.Tensor], n_res: int, *, scaling: Optional[float] = None,
                      out: Optional[torch.Tensor] = None,

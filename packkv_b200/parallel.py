@@ -46,6 +46,54 @@ def gather_heads(local_out: torch.Tensor, group: Optional[dist.ProcessGroup] = N
     return buffer.permute(1, 0, 2, 3).reshape(B, world * Hl, D)
 
 
+class HeadExchange:
+    """Per-layer exchange of the KV-head-sharded attention outputs: every rank ends up with (B, Hq, 128).
+
+    mode "nccl": one all-gather per layer into a preallocated (world, B, Hq/world, 128) buffer (the checked
+    baseline).  The gathered tensor is a view of that buffer, heads rank-major.
+    """
+
+    def __init__(self, batch: int, q_heads_local: int, world: int, dtype, device, mode: str = "nccl",
+                 group: Optional[dist.ProcessGroup] = None):
+        if mode not in ("nccl",):
+            raise ValueError(f"unknown exchange mode {mode!r}")
+        self.mode, self.world, self.group = mode, world, group
+        self.buffer = torch.empty(world, batch, q_heads_local, 128, dtype=dtype, device=device)
+        self._parts = list(self.buffer.unbind(0))
+
+    def gather(self, local_out: torch.Tensor) -> torch.Tensor:
+        dist.all_gather(self._parts, local_out, group=self.group)
+        return self.buffer
+
+    def full(self) -> torch.Tensor:
+        """(B, Hq, 128) copy of the last gathered result."""
+        w, B, Hl, D = self.buffer.shape
+        return self.buffer.permute(1, 0, 2, 3).reshape(B, w * Hl, D)
+
+
+def check_against_full(w: dict, rank: int, world: int, device, dtype, shard_layer0, q_full0: torch.Tensor, n_comp: int, n_res: int,
+                       xchg: "HeadExchange", flags: torch.Tensor) -> dict:
+    """Runs layer 0 of a head-sharded benchmark workload once more: every rank computes its heads and takes part
+    in the exchange; rank 0 also computes all heads on its own GPU from the same seeded K/V and compares."""
+    from . import encode, ops, synth
+    from .config import QuantMode
+    layer, k_res, v_res = shard_layer0
+    Hq_l = q_full0.shape[1] // world
+    out = ops.decode_attention(q_full0[:, rank * Hq_l:(rank + 1) * Hq_l].contiguous(), layer, k_res, v_res, n_res, flags=flags)
+    xchg.gather(out)
+    torch.cuda.synchronize()
+    got = xchg.full()
+    if rank != 0:
+        return {}
+    k, v = synth.synth_kv(w["batch"], w["kv_heads"], w["ctx"], 128, seed=1000, dtype=dtype, device=device, apply_rope=True)
+    full = encode.compress_kv(k[:, :, :n_comp], v[:, :, :n_comp], block=w["block"], bits_k=w["bits_k"], bits_v=w["bits_v"],
+                              k_rel=synth.rel_for_bits(w["bits_k"]), v_rel=synth.rel_for_bits(w["bits_v"]),
+                              k_mode=QuantMode.TokenQuant if w.get("k_mode") == "token" else QuantMode.ChannelQuant, cbk=w["cbk"], cbv=w["cbv"])
+    ref = ops.decode_attention(q_full0, full, k[:, :, n_comp:].contiguous(), v[:, :, n_comp:].contiguous(), n_res, flags=flags)
+    torch.cuda.synchronize()
+    return {"bit_identical_to_one_gpu": bool(torch.equal(got, ref)), "max_abs_diff": float((got.float() - ref.float()).abs().max())}
+
+
 def compress_kv_head_shard(k: torch.Tensor, v: torch.Tensor, rank: int, world: int, *, block: int, bits_k: int, bits_v: int,
                            k_rel: float, v_rel: float, k_mode, cbk: Optional[int] = None, cbv: Optional[int] = None):
     """Builds the rank's compressed layer from the FULL K, V (B, Hkv, S, 128): quantise with

@@ -53,7 +53,7 @@ def test_prefill_then_decode_matches_reference_cache(cuda_device, method, repack
                 ref = Q.eager_attention(q, Ko, Vo).float()
                 out = cache.attend(q.to(dev), 0).float().cpu()
                 assert ((out - ref).abs().max() / ref.abs().max()).item() <= 2e-3, t
-        cache._check_flags()
+        cache.check_flags()
         assert cache.compressed_bytes() > 0
     finally:
         C.PackKVCacheConfigStatic.config = None
@@ -86,7 +86,7 @@ def test_high_precision_zero_and_three_bit_cache(cuda_device, method, dtype):
         ref = Q.eager_attention(q, Ko, Vo).float()
         out = cache.attend(q.to(dev), 0).float().cpu()
         assert ((out - ref).abs().max() / ref.abs().max()).item() <= 2e-3
-        cache._check_flags()
+        cache.check_flags()
     finally:
         C.PackKVCacheConfigStatic.config = None
 

@@ -40,7 +40,7 @@ def test_other_model_families(family):
             outs.append(model(ids[:, :280], past_key_values=cache, use_cache=True).logits[:, -1:])
             for t in range(280, 300):
                 outs.append(model(ids[:, t:t + 1], past_key_values=cache, use_cache=True).logits)
-        cache._check_flags()
+        cache.check_flags()
         return torch.cat(outs, 1).float()
 
     ref, got = run(True), run(False)
@@ -73,7 +73,7 @@ def test_llama_decode_through_registered_attention(dtype):
             for t in range(prefill, prefill + steps):
                 outs.append(model(ids[:, t:t + 1], past_key_values=cache, use_cache=True).logits)
         assert cache.get_seq_length() == prefill + steps
-        cache._check_flags()
+        cache.check_flags()
         return torch.cat(outs, 1).float(), cache
 
     ref, _ = run(True)

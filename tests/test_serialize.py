@@ -74,6 +74,6 @@ def test_restored_layer_and_cache_decode_identically(cuda_device):
             for c in (cache, twin):
                 c.update(kd[:, :, t:t + 1], vd[:, :, t:t + 1], 0, {"cos": cos[:, t:t + 1], "sin": sin[:, t:t + 1]})
             assert torch.equal(cache.attend(q.unsqueeze(2), 0), twin.attend(q.unsqueeze(2), 0))
-        cache._check_flags(); twin._check_flags()
+        cache.check_flags(); twin.check_flags()
     finally:
         PackKVCacheConfigStatic.config = None
