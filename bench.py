@@ -191,11 +191,12 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
     out_dev = [torch.empty_like(q) for q in q_dev]
     flags = ops.new_flags(device)
     alg_bytes = sum(layer_bytes(L, kr, vr, n_res, B, Hq) for L, kr, vr in layers)
-    xchg = parallel.HeadExchange(B, Hq, world, dtype, device, mode=exchange) if by_heads else None
+    xchg = parallel.HeadExchange(B, Hq, world, dtype, device, mode=exchange, rank=rank, kv_heads_local=w["kv_heads"] // world,
+                                 flags=flags) if by_heads else None
 
     def step_resident():
         for (L, kr, vr), q, o in zip(layers, q_dev, out_dev):
-            ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags)
+            ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags, exchange=xchg.begin() if by_heads else None)
             if by_heads:
                 xchg.gather(o)
 
@@ -213,9 +214,12 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
     res.update(ms_per_step=ms / steps, batches=nb, launches=len(layers) * steps * nb)
 
     if by_heads:
-        # the exchange alone (same buffers, no kernels), and the sharded result against one full-head layer
-        ms_x, _, _ = timed_batches(lambda: [xchg.gather(o) for o in out_dev], steps, world, device, min_seconds=0.2)
-        res["exchange_ms_per_step"] = ms_x / steps
+        # the kernels alone (every rank its own heads, nothing exchanged): the difference is what the exchange costs
+        def step_local():
+            for (L, kr, vr), q, o in zip(layers, q_dev, out_dev):
+                ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags)
+        ms_l, _, _ = timed_batches(step_local, steps, world, device, min_seconds=0.3)
+        res["exchange_ms_per_step"] = max(0.0, ms / steps - ms_l / steps)
         res["check"] = parallel.check_against_full(w, rank, world, device, dtype, layers[0], q_full[0], n_comp, n_res, xchg, flags)
 
     if with_e2e:
@@ -246,7 +250,7 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
                 if i + 1 < len(layers):
                     upload(i + 1)
                 main.wait_event(ev_in[i % 2])
-                ops.decode_attention(q_stage[i % 2], L, kr, vr, n_res, out=o, flags=flags)
+                ops.decode_attention(q_stage[i % 2], L, kr, vr, n_res, out=o, flags=flags, exchange=xchg.begin() if by_heads else None)
                 ev_free[i % 2].record(main)
                 if by_heads:
                     xchg.gather(o)
@@ -484,7 +488,7 @@ def main():
     ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
                     help="multi-GPU split: independent sequences per rank (weak scaling, no collective) or KV heads per "
                          "rank with an exchange of the outputs (strong scaling)")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl"], help="output exchange of --shard heads")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="output exchange of --shard heads")
     args = ap.parse_args()
     w = WORKLOADS.get(args.workload)
     overridden = w is not None and (args.decode_bits_k or args.decode_bits_v or args.decode_k_mode != "channel" or args.decode_cbv

@@ -289,6 +289,49 @@ typedef struct pkv_attn_args {
 /* `args` is a HOST pointer to the argument block (copied at call time). */
 int32_t pkv_decode_attention(const pkv_attn_args* args_host, void* cuda_stream);
 
+/*
+ * KV-head-sharded decode over several GPUs of one node (one process per GPU, rank r owns kv_heads local KV
+ * heads and their q heads): the same launch, whose last stage also delivers this rank's output rows to every
+ * rank.  No counterpart in the reference (it has no multi-GPU path for one sequence).
+ *
+ * Every rank owns a gathered buffer (n_ranks, batch, kv_heads*group, 128) and an array of n_ranks arrival
+ * counters (uint32, zero before the first step), both mapped into the other ranks' address spaces (CUDA IPC
+ * or another peer mapping).  gathered[p] / arrivals[p] are rank p's buffers as THIS process addresses them
+ * (entry `rank` = this rank's own).  The block that finishes a (sequence, KV head) pair stores its rows into
+ * slice `rank` of every gathered[p] with ordinary stores, fences, and adds 1 to arrivals[p][rank]: after a step
+ * each counter has grown by batch*kv_heads.  Plain peer stores only: no multicast, no loads from peer memory.
+ * args.out still receives the local rows.
+ *
+ * pkv_exchange_wait makes the stream wait until every arrivals[r] (this rank's own counters) has reached
+ * `expected` (compared modulo 2^32): one warp polls with acquire loads for at most `max_polls` rounds of about
+ * a microsecond each and then gives up, setting PKV_FLAG_TIMEOUT in dev_flags (the kernel always returns, so a
+ * rank that never arrives costs the others a bounded wait, not a hang).  Kernels after it on the stream see the
+ * gathered rows.  A rank must not start step s+2 into the same gathered buffer before it has waited for step
+ * s+1: alternate two buffers per layer or wait every step.
+ */
+typedef struct pkv_attn_exchange {
+    int32_t n_ranks;            /* 1..8 */
+    int32_t rank;
+    void* gathered[8];
+    uint32_t* arrivals[8];
+} pkv_attn_exchange;
+int32_t pkv_decode_attention_exchange(const pkv_attn_args* args_host, const pkv_attn_exchange* exchange_host,
+                                      void* cuda_stream);
+int32_t pkv_exchange_wait(const uint32_t* arrivals, int32_t n_ranks, uint32_t expected, uint32_t max_polls,
+                          uint32_t* dev_flags, void* cuda_stream);
+/*
+ * Set-up helpers of the exchange; the only entry points that allocate or touch address-space mappings (they
+ * synchronise, call them once, outside the decode loop).  pkv_exchange_alloc returns `bytes` of zeroed device
+ * memory on the current device (its own cudaMalloc, so that it can be exported) and the 64-byte
+ * cudaIpcMemHandle that another process of the node passes to pkv_ipc_open, which maps the buffer into the
+ * CURRENT device's address space with peer access to the owning GPU, so that this device's kernels can store
+ * into it.  pkv_ipc_close unmaps, pkv_exchange_free releases.
+ */
+int32_t pkv_exchange_alloc(int64_t bytes, void** ptr_host, uint8_t* handle64_host);
+int32_t pkv_exchange_free(void* ptr);
+int32_t pkv_ipc_open(const uint8_t* handle64_host, void** mapped_host);
+int32_t pkv_ipc_close(void* mapped);
+
 #ifdef __cplusplus
 }
 #endif

@@ -38,6 +38,11 @@ class AttnArgs(ctypes.Structure):
     ]
 
 
+class AttnExchange(ctypes.Structure):
+    """Mirror of pkv_attn_exchange (include/packkv_sm100.h)."""
+    _fields_ = [("n_ranks", _i32), ("rank", _i32), ("gathered", _p * 8), ("arrivals", _p * 8)]
+
+
 class EncodeArgs(ctypes.Structure):
     """Mirror of pkv_encode_args (include/packkv_sm100.h)."""
     _fields_ = [
@@ -67,6 +72,12 @@ SIGNATURES = {
     "pkv_dequantize": (_i32, [_p, _i64, _p, _p, _i32, _i32, _i32, _p, _i64, _i64, _i64] + [_i32] * 7 + [_p]),
     "pkv_quantize": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _p] + [_i32] * 8 + [_f32] + [_i32] * 4 + [_p, _p]),
     "pkv_decode_attention": (_i32, [ctypes.POINTER(AttnArgs), _p]),
+    "pkv_decode_attention_exchange": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnExchange), _p]),
+    "pkv_exchange_wait": (_i32, [_p, _i32, ctypes.c_uint32, ctypes.c_uint32, _p, _p]),
+    "pkv_exchange_alloc": (_i32, [_i64, ctypes.POINTER(ctypes.c_void_p), _p]),
+    "pkv_exchange_free": (_i32, [_p]),
+    "pkv_ipc_open": (_i32, [_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "pkv_ipc_close": (_i32, [_p]),
     "pkv_abi_version": (_i32, []),
     "pkv_k_encode": (_i32, _CODEC_ENC),
     "pkv_v_encode": (_i32, _CODEC_ENC),

@@ -255,6 +255,7 @@ struct AttnDev {
     int tile_shift, cbk_shift, cbv_shift;   // log2 of tile, cbk, cbv
     int nkb_shift, nvi_shift;               // log2 of K blocks per tile and of V blocks (2 halves x token blocks) per tile
     FieldSpread klen, kmin, vlen, vmin;     // header field widths -> bytes
+    AttnExchange x;      // head-sharded multi-GPU output exchange (n_ranks = 0: none)
 };
 
 // CTA-shared block (cluster-visible)
@@ -1004,7 +1005,17 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
         for (int hd = 0; hd < G; hd++) {
             float v = 0.f;
             for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
-            reinterpret_cast<T*>(a.out)[((int64_t)(b * q_heads + h * G + hd)) * kD + d] = Tr<T>::from_float(v);
+            const T r = Tr<T>::from_float(v);
+            const int64_t idx = ((int64_t)(b * q_heads + h * G + hd)) * kD + d;
+            reinterpret_cast<T*>(a.out)[idx] = r;
+            // head-sharded decode: the same row goes into this rank's slice of every rank's gathered buffer
+            for (int p = 0; p < P.x.n_ranks; p++)
+                reinterpret_cast<T*>(P.x.gathered[p])[(int64_t)P.x.rank * a.batch * q_heads * kD + idx] = r;
+        }
+        if (P.x.n_ranks > 0) {
+            __threadfence_system();                    // the rows are visible to the other GPUs before the arrival is
+            __syncthreads();
+            if (d < P.x.n_ranks) atomicAdd_system(P.x.arrivals[d] + P.x.rank, 1u);
         }
     }
     cluster.sync();   // keep every CTA's shared memory alive until rank 0 has read it
@@ -1079,7 +1090,30 @@ static int plan_smem(AttnDev& P, int cl, int nslots, int slot) {
     return P.cta_off + (int)sizeof(CtaShared);
 }
 
-int launch_attention(const AttnArgs& a, cudaStream_t st) {
+// One warp polls this rank's arrival counters; see pkv_exchange_wait.
+__global__ void exchange_wait_kernel(const uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags) {
+    const int lane = threadIdx.x;
+    bool ok = lane >= n_ranks;
+    for (unsigned it = 0; it <= max_polls; it++) {
+        if (!ok) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(arrivals + lane) : "memory");
+            ok = (int)(v - expected) >= 0;
+        }
+        if (__all_sync(0xffffffffu, ok)) break;
+        __nanosleep(1000);
+    }
+    if (!__all_sync(0xffffffffu, ok) && lane == 0) atomicOr(flags, kFlagTimeout);
+    __threadfence_system();
+}
+
+int launch_exchange_wait(const uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, cudaStream_t st) {
+    if (!arrivals || !flags || n_ranks < 1 || n_ranks > 8) return kBadArgument;
+    exchange_wait_kernel<<<1, 32, 0, st>>>(arrivals, n_ranks, expected, max_polls, flags);
+    return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
+}
+
+int launch_attention(const AttnArgs& a, const AttnExchange* xch, cudaStream_t st) {
     if (a.batch <= 0 || a.kv_heads <= 0 || a.group < 1 || a.group > 8) return a.group > 8 ? kUnsupported : kBadArgument;
     if (a.n_comp < 0 || a.n_res < 0 || a.n_comp + a.n_res == 0) return kBadArgument;
     if (!a.q || !a.out || !a.flags) return kBadArgument;
@@ -1107,6 +1141,12 @@ int launch_attention(const AttnArgs& a, cudaStream_t st) {
 
     AttnDev P{};
     P.a = a;
+    if (xch) {
+        if (xch->n_ranks < 1 || xch->n_ranks > 8 || xch->rank < 0 || xch->rank >= xch->n_ranks) return kBadArgument;
+        for (int p = 0; p < xch->n_ranks; p++)
+            if (!xch->gathered[p] || !xch->arrivals[p]) return kBadArgument;
+        P.x = *xch;
+    }
     P.tile = (a.n_comp > 0 && (a.cbk == 128 || a.cbv == 128)) ? 128 : 64;
     P.tiles_total = a.n_comp / P.tile;
     auto lg2 = [](int v) { int s = 0; while ((1 << s) < v) s++; return s; };

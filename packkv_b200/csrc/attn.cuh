@@ -10,6 +10,10 @@ namespace pkv {
 enum KMode : int { kKChannel = PKV_K_CHANNEL, kKToken = PKV_K_TOKEN };
 using AttnArgs = pkv_attn_args;
 
-int launch_attention(const AttnArgs& a, cudaStream_t st);
+using AttnExchange = pkv_attn_exchange;
+
+// xch may be null (single GPU)
+int launch_attention(const AttnArgs& a, const AttnExchange* xch, cudaStream_t st);
+int launch_exchange_wait(const uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, cudaStream_t st);
 
 }  // namespace pkv

@@ -1,5 +1,6 @@
 // extern "C" surface of libpackkv_sm100.so; declarations and contracts live in
 // include/packkv_sm100.h.
+#include <cstring>
 #include "../../include/packkv_sm100.h"
 #include "common.cuh"
 #include "launch.h"
@@ -148,7 +149,60 @@ int32_t pkv_dequantize(const uint8_t* codes, int64_t codes_seq_stride, const voi
 
 int32_t pkv_decode_attention(const pkv_attn_args* args_host, void* cuda_stream) {
     if (!args_host) return kBadArgument;
-    return launch_attention(*args_host, static_cast<cudaStream_t>(cuda_stream));
+    return launch_attention(*args_host, nullptr, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_decode_attention_exchange(const pkv_attn_args* args_host, const pkv_attn_exchange* exchange_host, void* cuda_stream) {
+    if (!args_host || !exchange_host) return kBadArgument;
+    return launch_attention(*args_host, exchange_host, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_exchange_wait(const uint32_t* arrivals, int32_t n_ranks, uint32_t expected, uint32_t max_polls, uint32_t* dev_flags,
+                          void* cuda_stream) {
+    return launch_exchange_wait(arrivals, n_ranks, expected, max_polls, dev_flags, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_exchange_alloc(int64_t bytes, void** ptr_host, uint8_t* handle64_host) {
+    if (bytes <= 0 || !ptr_host || !handle64_host) return kBadArgument;
+    void* p = nullptr;
+    if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) { cudaGetLastError(); return kCudaError; }
+    cudaIpcMemHandle_t h;
+    if (cudaMemset(p, 0, (size_t)bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+        cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(p);
+        return kCudaError;
+    }
+    memcpy(handle64_host, &h, sizeof(h));
+    *ptr_host = p;
+    return kOk;
+}
+
+int32_t pkv_exchange_free(void* ptr) {
+    if (!ptr) return kBadArgument;
+    return cudaFree(ptr) == cudaSuccess ? kOk : kCudaError;
+}
+
+int32_t pkv_ipc_open(const uint8_t* handle64_host, void** mapped_base_host) {
+    if (!handle64_host || !mapped_base_host) return kBadArgument;
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    memcpy(&h, handle64_host, sizeof(h));
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); return kCudaError; }
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+        cudaGetLastError();
+        cudaIpcCloseMemHandle(p);
+        return kCudaError;
+    }
+    *mapped_base_host = p;
+    return kOk;
+}
+
+int32_t pkv_ipc_close(void* mapped_base) {
+    if (!mapped_base) return kBadArgument;
+    return cudaIpcCloseMemHandle(mapped_base) == cudaSuccess ? kOk : kCudaError;
 }
 
 }  // extern "C"

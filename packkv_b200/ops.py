@@ -200,12 +200,14 @@ ATTN_KERNEL_REVISION = 2
 def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: Optional[torch.Tensor],
                      v_res: Optional[torch.Tensor], n_res: int, *, scaling: Optional[float] = None,
                      out: Optional[torch.Tensor] = None,
-                     flags: Optional[torch.Tensor] = None, kv_heads: Optional[int] = None) -> torch.Tensor:
+                     flags: Optional[torch.Tensor] = None, kv_heads: Optional[int] = None,
+                     exchange: Optional["_lib.AttnExchange"] = None) -> torch.Tensor:
     """softmax(q K^T * scaling) V for one query token per sequence.
 
     q: (B, Hq, 128) fp16/bf16 (post-RoPE).  `layer` holds the compressed tokens, k_res/v_res
     (B, Hkv, R_cap, 128) the uncompressed residual whose first n_res tokens are valid.
-    Returns out (B, Hq, 128) in q's dtype; asynchronous on the current stream.
+    Returns out (B, Hq, 128) in q's dtype; asynchronous on the current stream.  `exchange` (KV-head-sharded
+    decode on several GPUs, see parallel.HeadExchange) makes the launch also deliver the rows to every rank.
     """
     _require_cuda(q, k_res, v_res, out, flags)
     if q.dim() != 3 or q.shape[2] != 128 or not q.is_contiguous():
@@ -254,9 +256,20 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
     a.is_bf16 = int(q.dtype == torch.bfloat16)
     a.scaling = float(D ** -0.5 if scaling is None else scaling)
     a.flags = flags.data_ptr()
-    st = _lib.lib().pkv_decode_attention(ctypes.byref(a), _stream_ptr())
+    if exchange is None:
+        st = _lib.lib().pkv_decode_attention(ctypes.byref(a), _stream_ptr())
+    else:
+        st = _lib.lib().pkv_decode_attention_exchange(ctypes.byref(a), ctypes.byref(exchange), _stream_ptr())
     _lib.check(st, "decode_attention")
     return out
+
+
+def exchange_wait(arrivals: torch.Tensor, n_ranks: int, expected: int, flags: torch.Tensor, max_polls: int = 2_000_000) -> None:
+    """Makes the current stream wait until this rank's n_ranks arrival counters have reached `expected`
+    (modulo 2^32); after max_polls polls of about a microsecond the wait gives up and sets FLAG_TIMEOUT."""
+    _require_cuda(arrivals, flags)
+    st = _lib.lib().pkv_exchange_wait(arrivals.data_ptr(), n_ranks, expected & 0xFFFFFFFF, max_polls, flags.data_ptr(), _stream_ptr())
+    _lib.check(st, "exchange_wait")
 
 
 def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -15,6 +15,8 @@ from __future__ import annotations
 
 from typing import List, Optional, Tuple
 
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -46,23 +48,102 @@ def gather_heads(local_out: torch.Tensor, group: Optional[dist.ProcessGroup] = N
     return buffer.permute(1, 0, 2, 3).reshape(B, world * Hl, D)
 
 
-class HeadExchange:
-    """Per-layer exchange of the KV-head-sharded attention outputs: every rank ends up with (B, Hq, 128).
+class _RawCuda:
+    """Lets torch view device memory that this package allocated itself (uint8, 1-D)."""
 
-    mode "nccl": one all-gather per layer into a preallocated (world, B, Hq/world, 128) buffer (the checked
-    baseline).  The gathered tensor is a view of that buffer, heads rank-major.
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
+
+
+class HeadExchange:
+    """Per-layer exchange of the KV-head-sharded attention outputs: every rank ends up with the rows of all
+    ranks in a (world, B, Hq/world, 128) buffer, heads rank-major.
+
+    mode "nccl": one all-gather per layer after the attention launch (the checked baseline).
+    mode "peer": the attention launch itself stores its rows into every rank's buffer (buffers and arrival
+    counters are shared between the processes of the node through CUDA IPC handles) and a one-warp kernel makes
+    the stream wait for the other ranks' rows; two buffers alternate, so a rank may run one step ahead of the
+    slowest one.  Use: ``o = ops.decode_attention(..., exchange=x.begin()); x.gather(o)``.
     """
 
     def __init__(self, batch: int, q_heads_local: int, world: int, dtype, device, mode: str = "nccl",
-                 group: Optional[dist.ProcessGroup] = None):
-        if mode not in ("nccl",):
+                 group: Optional[dist.ProcessGroup] = None, rank: Optional[int] = None, kv_heads_local: Optional[int] = None,
+                 flags: Optional[torch.Tensor] = None, max_polls: int = 2_000_000):
+        if mode not in ("nccl", "peer"):
             raise ValueError(f"unknown exchange mode {mode!r}")
         self.mode, self.world, self.group = mode, world, group
-        self.buffer = torch.empty(world, batch, q_heads_local, 128, dtype=dtype, device=device)
-        self._parts = list(self.buffer.unbind(0))
+        self.rank = dist.get_rank(group) if rank is None else rank
+        self.step, self.max_polls = 0, max_polls
+        if mode == "nccl":
+            self.buffer = torch.empty(world, batch, q_heads_local, 128, dtype=dtype, device=device)
+            self._parts = list(self.buffer.unbind(0))
+            return
+        from . import _lib, ops
+        if kv_heads_local is None:
+            raise ValueError("peer mode needs kv_heads_local (arrivals per step = batch * kv_heads_local)")
+        self.per_step = batch * kv_heads_local
+        self.flags = ops.new_flags(device) if flags is None else flags
+        slice_bytes = batch * q_heads_local * 128 * torch.empty((), dtype=dtype).element_size()
+        buf_bytes = (world * slice_bytes + 255) // 256 * 256
+        # one exportable allocation per rank: two gathered buffers, then two sets of arrival counters
+        total = 2 * buf_bytes + 256
+        ptr, hbuf = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        with torch.cuda.device(device):
+            _lib.check(_lib.lib().pkv_exchange_alloc(total, ctypes.byref(ptr), hbuf), "exchange_alloc")
+        self._own = ptr.value
+        self._store = torch.as_tensor(_RawCuda(ptr.value, total), device=device)
+        handles = [None] * world
+        dist.all_gather_object(handles, (self.rank, hbuf.raw), group=group)
+        self._mapped, base = [], [0] * world
+        for r, h in handles:
+            if r == self.rank:
+                base[r] = self._own
+            else:
+                # mapped into THIS device's address space (the exporter's GPU becomes a peer of this one)
+                mp_ = ctypes.c_void_p()
+                with torch.cuda.device(device):
+                    _lib.check(_lib.lib().pkv_ipc_open(ctypes.c_char_p(h), ctypes.byref(mp_)), "ipc_open")
+                self._mapped.append(mp_.value)
+                base[r] = mp_.value
+        self.buffers = [self._store[i * buf_bytes:i * buf_bytes + world * slice_bytes].view(dtype).view(world, batch, q_heads_local, 128)
+                        for i in range(2)]
+        self._arrivals = [self._store[2 * buf_bytes + 128 * i:2 * buf_bytes + 128 * i + 4 * world].view(torch.int32) for i in range(2)]
+        self._x = []
+        for i in range(2):
+            x = _lib.AttnExchange()
+            x.n_ranks, x.rank = world, self.rank
+            for r in range(world):
+                x.gathered[r] = base[r] + i * buf_bytes
+                x.arrivals[r] = base[r] + 2 * buf_bytes + 128 * i
+            self._x.append(x)
+        self.buffer = self.buffers[0]
+        dist.barrier(group=group)
+
+    def close(self):
+        """Unmaps the other ranks' buffers (after all ranks have stopped using the exchange)."""
+        from . import _lib
+        for p in getattr(self, "_mapped", []):
+            _lib.lib().pkv_ipc_close(p)
+        self._mapped = []
+        if getattr(self, "_own", None):
+            torch.cuda.synchronize()
+            self.buffers = self._arrivals = self._store = self.buffer = None
+            _lib.lib().pkv_exchange_free(self._own)
+            self._own = None
+
+    def begin(self):
+        """The exchange block for the next attention launch (peer mode; None in nccl mode)."""
+        return None if self.mode == "nccl" else self._x[self.step & 1]
 
     def gather(self, local_out: torch.Tensor) -> torch.Tensor:
-        dist.all_gather(self._parts, local_out, group=self.group)
+        if self.mode == "nccl":
+            dist.all_gather(self._parts, local_out, group=self.group)
+            return self.buffer
+        from . import ops
+        i = self.step & 1
+        self.step += 1
+        ops.exchange_wait(self._arrivals[i], self.world, ((self.step + 1) // 2) * self.per_step, self.flags, self.max_polls)
+        self.buffer = self.buffers[i]
         return self.buffer
 
     def full(self) -> torch.Tensor:
@@ -79,7 +160,8 @@ def check_against_full(w: dict, rank: int, world: int, device, dtype, shard_laye
     from .config import QuantMode
     layer, k_res, v_res = shard_layer0
     Hq_l = q_full0.shape[1] // world
-    out = ops.decode_attention(q_full0[:, rank * Hq_l:(rank + 1) * Hq_l].contiguous(), layer, k_res, v_res, n_res, flags=flags)
+    out = ops.decode_attention(q_full0[:, rank * Hq_l:(rank + 1) * Hq_l].contiguous(), layer, k_res, v_res, n_res, flags=flags,
+                               exchange=xchg.begin())
     xchg.gather(out)
     torch.cuda.synchronize()
     got = xchg.full()

@@ -1,6 +1,10 @@
-"""GPU, 2 ranks over NCCL (skipped on a single-GPU box): KV-head-sharded decode attention with an
-all-gather of the outputs equals the single-GPU result bit for bit, and every rank's streams are the
-per-head slices of the single-GPU encoding."""
+"""KV-head-sharded decode attention.
+
+On one GPU: the exchange path of the attention launch (rows stored into every rank's gathered buffer, arrival
+counters, the bounded wait) with the ranks run one after the other on the same device, and a wait whose
+counters never arrive, which must give up with the timeout flag and leave the context usable.
+On 2 GPUs (skipped on a single-GPU box): two processes over NCCL, both exchange modes, equal to the single-GPU
+result bit for bit."""
 import os
 import socket
 
@@ -42,6 +46,18 @@ def _worker(rank, world, port, results):
             torch.cuda.synchronize()
             ok = torch.equal(got, want)
             results[(rank, k_mode.value)] = bool(ok)
+            # the same through the launch's own peer stores, three steps in a row (the two buffers alternate)
+            flags = ops.new_flags(dev)
+            x = parallel.HeadExchange(B, (qhi - qlo), world, dtype, dev, mode="peer", rank=rank, kv_heads_local=hi - lo, flags=flags)
+            ok = True
+            for _ in range(3):
+                local = ops.decode_attention(q[:, qlo:qhi].contiguous(), layer, k[:, lo:hi, S:].contiguous(), v[:, lo:hi, S:].contiguous(), R,
+                                             flags=flags, exchange=x.begin())
+                x.gather(local)
+                torch.cuda.synchronize()
+                ok = ok and torch.equal(x.full(), want)
+                dist.barrier()
+            results[(rank, k_mode.value, "peer")] = bool(ok) and int(flags.item()) == 0
     finally:
         dist.destroy_process_group()
 
@@ -52,4 +68,56 @@ def test_head_sharded_attention_equals_single_gpu():
     with mp.Manager() as mgr:
         results = mgr.dict()
         mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
-        assert len(results) == 4 and all(results.values()), dict(results)
+        assert len(results) == 8 and all(results.values()), dict(results)
+
+
+def test_exchange_rows_and_counters_on_one_gpu(cuda_device):
+    """Two ranks' launches run one after the other on one device, each with the exchange block that names both
+    ranks' (local) gathered buffers: the buffers end up equal to the unsharded result and every counter has
+    grown by batch * local KV heads; the wait then passes without a poll running out."""
+    from packkv_b200 import _lib, encode, ops, parallel, synth
+    from packkv_b200.config import QuantMode
+    dev, dtype = cuda_device, torch.float16
+    B, H, G, S, R, world = 2, 4, 2, 256, 20, 2
+    k, v = synth.synth_kv(B, H, S + R, 128, seed=5, dtype=dtype, device=dev, apply_rope=True)
+    q = synth.synth_q(B, H * G, 128, seed=5, dtype=dtype, device=dev)[:, :, 0].contiguous()
+    args = dict(block=64, bits_k=4, bits_v=4, k_rel=1 / 14, v_rel=1 / 14, k_mode=QuantMode.ChannelQuant)
+    full = encode.compress_kv(k[:, :, :S], v[:, :, :S], **args)
+    want = ops.decode_attention(q, full, k[:, :, S:].contiguous(), v[:, :, S:].contiguous(), R)
+    Hl, Hql = H // world, H * G // world
+    gathered = [torch.zeros(world, B, Hql, 128, dtype=dtype, device=dev) for _ in range(world)]
+    arrivals = [torch.zeros(world, dtype=torch.int32, device=dev) for _ in range(world)]
+    flags = ops.new_flags(dev)
+    for rank in range(world):
+        layer, (lo, hi) = parallel.compress_kv_head_shard(k[:, :, :S], v[:, :, :S], rank, world, **args)
+        x = _lib.AttnExchange()
+        x.n_ranks, x.rank = world, rank
+        for r in range(world):
+            x.gathered[r], x.arrivals[r] = gathered[r].data_ptr(), arrivals[r].data_ptr()
+        ops.decode_attention(q[:, lo * G:hi * G].contiguous(), layer, k[:, lo:hi, S:].contiguous(), v[:, lo:hi, S:].contiguous(), R,
+                             flags=flags, exchange=x)
+    for r in range(world):
+        ops.exchange_wait(arrivals[r], world, B * Hl, flags, max_polls=10)
+    torch.cuda.synchronize()
+    assert int(flags.item()) == 0
+    for r in range(world):
+        assert arrivals[r].tolist() == [B * Hl] * world
+        assert torch.equal(gathered[r].permute(1, 0, 2, 3).reshape(B, H * G, 128), want)
+
+
+def test_exchange_wait_gives_up(cuda_device):
+    """A rank that never arrives: the wait returns after its poll limit with PKV_FLAG_TIMEOUT set, and the device
+    keeps working afterwards."""
+    from packkv_b200 import _lib, ops
+    dev = cuda_device
+    arrivals = torch.zeros(4, dtype=torch.int32, device=dev)
+    arrivals[0] = 7
+    flags = ops.new_flags(dev)
+    ops.exchange_wait(arrivals, 4, 7, flags, max_polls=50)
+    torch.cuda.synchronize()
+    assert int(flags.item()) == _lib.FLAG_TIMEOUT
+    arrivals[:] = 7
+    flags.zero_()
+    ops.exchange_wait(arrivals, 4, 7, flags, max_polls=50)
+    torch.cuda.synchronize()
+    assert int(flags.item()) == 0
