@@ -20,7 +20,8 @@ own CPU path (C++ bit-unpack + torch dequantise + eager attention) on a bounded 
 default workload's line also carries the other parts of the metric as extra keys:
 `v_block_64` (the same decode with 64-token V blocks), `encode` (Mistral-7B-shaped KV encode, 64
 sequences x 16384 tokens split over the ranks, with and without the median reorder, and the
-single-token append) and, on more than one GPU, `head_sharded` (the long-context workload split
+single-token append), `phi3_e2e` (Phi-3-mini-shaped model generating 256 tokens after a 4096-token
+prompt, 8 sequences per GPU) and, on more than one GPU, `head_sharded` (the long-context workload split
 by KV heads with the output exchange).
 """
 from __future__ import annotations
@@ -464,6 +465,74 @@ def encode_leg(steps, warmup, rank, world, device, *, total_seqs=64, bits=4, blo
     return out if rank == 0 else None
 
 
+def phi3_e2e_leg(rank, world, device, *, seqs_per_gpu=8, prompt=4096, new_tokens=256, layers=32):
+    """Phi-3-mini-shaped end-to-end decode (32 layers, 32 heads without grouping, head_dim 96, hidden 3072, bf16,
+    random-initialised weights, random prompt ids): prefill of `prompt` tokens, then `new_tokens` greedy steps of
+    the unmodified transformers model whose decode attention runs on the compressed cache through the
+    registered attention function.  Every GPU serves `seqs_per_gpu` sequences (batch sharding, no collective);
+    value = generated tokens of all ranks / max over ranks of the decode-loop device time."""
+    from transformers import Phi3Config, Phi3ForCausalLM
+    from packkv_b200 import hf
+    from packkv_b200.cache import PackKVCacheConfigStatic
+    from packkv_b200.config import PackKVCacheConfig, QuantMethod, RepackMethod
+    torch.manual_seed(1234)
+    cfg = Phi3Config(hidden_size=3072, num_attention_heads=32, num_key_value_heads=32, num_hidden_layers=layers, intermediate_size=8192,
+                     vocab_size=32064, max_position_embeddings=prompt + new_tokens + 64, pad_token_id=0, bos_token_id=1, eos_token_id=2)
+    with torch.device(device):
+        model = Phi3ForCausalLM(cfg).to(torch.bfloat16).eval()
+    hf.register()
+    model.set_attn_implementation(hf.ATTN_NAME)
+    PackKVCacheConfigStatic.config = PackKVCacheConfig("phi-3-mini-shaped", QuantMethod.KIVI, RepackMethod.NONE, False, 64, 192, 16, 1 / 14, 1 / 14)
+    try:
+        g = torch.Generator(device=device).manual_seed(99 + rank)
+        ids = torch.randint(3, 32000, (seqs_per_gpu, prompt), generator=g, device=device)
+        cache = hf.make_cache(cfg, seqs_per_gpu)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        with torch.no_grad():
+            ev[0].record()
+            nxt = model(ids, past_key_values=cache, use_cache=True, logits_to_keep=1).logits[:, -1].argmax(-1, keepdim=True)
+            if world > 1:
+                torch.distributed.barrier()
+            torch.cuda.synchronize()
+            ev[1].record()
+            for _ in range(new_tokens):
+                nxt = model(nxt, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
+            ev[2].record()
+            torch.cuda.synchronize()
+        cache.check_flags()
+        ms_prefill, ms_decode = ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
+        # the attention launches alone, on the final cache (one token more or less does not matter)
+        q = torch.randn(seqs_per_gpu, 32, 1, 96, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        for _ in range(2):
+            for li in range(layers):
+                cache.attend(q, li)
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(8):
+            for li in range(layers):
+                cache.attend(q, li)
+        a1.record()
+        torch.cuda.synchronize()
+        ms_attn_step = a0.elapsed_time(a1) / 8
+        if world > 1:
+            t = torch.tensor([ms_decode, ms_prefill], device=device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms_decode, ms_prefill = float(t[0]), float(t[1])
+        kv_tokens = cache.get_seq_length(0)
+        comp = cache.compressed_bytes()
+        return {"workload": f"phi-3-mini-shaped model, {layers} layers, 32 heads x 96, bf16, random weights: {seqs_per_gpu} sequences per GPU x "
+                            f"{world} GPU(s), prompt {prompt}, {new_tokens} generated tokens, 4-bit K (per channel) / V (per token), block 64",
+                "value": world * seqs_per_gpu * new_tokens / (ms_decode * 1e-3), "unit": "tok/s", "ms_per_token_step": ms_decode / new_tokens,
+                "prefill_ms": ms_prefill, "attention_ms_per_token_step": ms_attn_step, "attention_share": ms_attn_step / (ms_decode / new_tokens),
+                "kv_tokens_at_end": kv_tokens, "compressed_stream_bytes_per_gpu": comp,
+                "fp_kv_bytes_per_gpu": 2 * layers * seqs_per_gpu * 32 * kv_tokens * 96 * 2,
+                "layout_note": "head_dim 96 is stored in 128-channel blocks (the tail repeats 32 channels): no reference bitstream exists for it"}
+    finally:
+        PackKVCacheConfigStatic.config = None
+        del model
+        torch.cuda.empty_cache()
+
+
 ENCODE_REVISION = 1   # changes when the encoder kernels change (keys NCU_TRAFFIC_BYTES)
 
 
@@ -473,7 +542,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS) + ["mistral7b-encode"])
+    ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS) + ["mistral7b-encode", "phi3-e2e"])
     ap.add_argument("--encode-batch", type=int, default=64, help="sequences in all (split over the ranks)")
     ap.add_argument("--encode-bits", type=int, default=4)
     ap.add_argument("--encode-block", type=int, default=64)
@@ -527,6 +596,14 @@ def main():
                         "source_fp16_gbs": p["source_fp16_gbs"], "compressed_over_fp16": p["compressed_over_fp16"], "gpu_launches": 7 * args.steps}
                 print(json.dumps(line), flush=True)
             return
+        if args.workload == "phi3-e2e":
+            leg = phi3_e2e_leg(rank, world, device)
+            if rank == 0:
+                print(json.dumps({"metric": "end-to-end decode throughput with the compressed KV cache", "value": leg["value"], "unit": "tok/s",
+                                  "n_gpus": world, "steps": 256, "warmup": 0, "ms_per_step": leg["ms_per_token_step"], "higher_is_better": True,
+                                  "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {"workload": leg["workload"]},
+                                  "detail": leg}), flush=True)
+            return
         line = decode_line(args, w, rank, world, device)
         extras = args.workload == "llama8b" and not overridden and not args.no_extras and args.shard == "batch"
         if extras:
@@ -544,6 +621,10 @@ def main():
             leg = encode_leg(args.steps, args.warmup, rank, world, device)
             if rank == 0:
                 line["encode"] = leg
+            torch.cuda.empty_cache()
+            leg = phi3_e2e_leg(rank, world, device)
+            if rank == 0:
+                line["phi3_e2e"] = leg
             torch.cuda.empty_cache()
             if world > 1:
                 wq = dict(WORKLOADS["qwen8b-long"], layers=6)

@@ -194,10 +194,19 @@ class PackKVCache(_HFCache):
             assert not cfg.enable_quant, "Disable quant to enable cache collect."
         L = self._layers[layer_idx]
         B, H, T, D = key_states.shape
-        if D != 128:
-            raise RuntimeError("not supported")   # streams are built from 128-channel blocks
+        if D != 128 and (D > 128 or D < 64 or D % 8):
+            raise RuntimeError("not supported")   # streams are built from 128-channel blocks; 64..120 are padded, see _widen
+        if cfg.enable_quant and cfg.block_size not in (64, 128):
+            # the codec packs 32-token blocks too, but the attention kernel reads 64- and 128-token blocks only:
+            # refuse here, not at the first attend()
+            raise RuntimeError("not supported: PackKVCache needs block_size 64 or 128")
         # the reference's models pass K before RoPE together with sin/cos; the installed transformers rotates K itself
         cos, sin = (cache_kwargs["cos"], cache_kwargs["sin"]) if cache_kwargs is not None and "cos" in cache_kwargs and "sin" in cache_kwargs else (None, None)
+        if D != 128 and cfg.enable_quant:
+            if cos is not None:
+                key_states, cos, sin = ops.rope(key_states, cos, sin), None, None
+            key_states, value_states = self._widen(key_states), self._widen(value_states)
+            D = 128
         if cfg.enable_quant and L.k_res is not None:
             total = L.n_res + T
             if compress_block_count(total, cfg.block_size, cfg.buffer_size) == 0:
@@ -240,6 +249,15 @@ class PackKVCache(_HFCache):
             L.v_res[:, :, : L.n_res] = v_all[:, :, n_c:]
         return self._step_result(layer_idx, T)
 
+    @staticmethod
+    def _widen(x: torch.Tensor) -> torch.Tensor:
+        """(B, H, T, D) with 64 <= D < 128 -> (B, H, T, 128): the tail repeats the first 128 - D channels.  The
+        streams are built from 128-channel blocks; with copies in the tail the per-channel K parameters of the real
+        channels and the per-token minima / maxima of V (and token-mode K) are unchanged, so codes and parameters
+        of the real channels are exactly the reference's for head_dim D.  attend() pads q with zeros, so the copies
+        add nothing to the scores, and drops the tail of the output."""
+        return torch.cat([x, x[..., : 128 - x.shape[-1]]], dim=-1)
+
     def _step_result(self, layer_idx: int, T: int):
         if T > 1 or self.materialize:
             return self.dense(layer_idx)
@@ -250,7 +268,8 @@ class PackKVCache(_HFCache):
     def dense(self, layer_idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """Dequantised history + residual, (B, H, S, 128): what the reference's update returns."""
         L = self._layers[layer_idx]
-        k_res, v_res = L.k_res[:, :, : L.n_res], L.v_res[:, :, : L.n_res]
+        D = self.head_dim if self.head_dim < 128 else 128
+        k_res, v_res = L.k_res[:, :, : L.n_res, :D], L.v_res[:, :, : L.n_res, :D]
         if L.n_comp == 0:
             return k_res.clone(), v_res.clone()
         C, cfg = L.comp, self._config()
@@ -266,7 +285,7 @@ class PackKVCache(_HFCache):
             inv.scatter_(1, pos, torch.arange(L.n_comp, device=kd.device).expand_as(pos))
             idx = inv.view(kd.shape[0], 1, L.n_comp, 1).expand_as(kd)
             kd, vd = torch.gather(kd, 2, idx), torch.gather(vd, 2, idx)
-        return torch.cat([kd, k_res], dim=2), torch.cat([vd, v_res], dim=2)
+        return torch.cat([kd[..., :D], k_res], dim=2), torch.cat([vd[..., :D], v_res], dim=2)
 
     def attend(self, query_states: torch.Tensor, layer_idx: int, scaling: Optional[float] = None) -> torch.Tensor:
         """Decode attention for one new token: query_states (B, Hq, 1, 128) after RoPE ->
@@ -277,11 +296,16 @@ class PackKVCache(_HFCache):
             raise ValueError("attend handles one query token per sequence; use dense() for prefill")
         if self.flags is None:
             self.flags = ops.new_flags(query_states.device)
-        q = query_states.reshape(B, Hq, D).contiguous()
+        q = query_states.reshape(B, Hq, D)
+        if D != 128:
+            if scaling is None:
+                scaling = D ** -0.5
+            q = torch.nn.functional.pad(q, (0, 128 - D))       # zeros: the copied channels of K add nothing
+        q = q.contiguous()
         kv_heads = L.comp.kv_heads if L.comp is not None else L.k_res.shape[1]
         out = ops.decode_attention(q, L.comp if L.n_comp else None, L.k_res, L.v_res, L.n_res, scaling=scaling,
                                    flags=self.flags, kv_heads=kv_heads)
-        return out.view(B, 1, Hq, D)
+        return out.view(B, 1, Hq, 128)[..., :D]
 
     def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:
         self._config()

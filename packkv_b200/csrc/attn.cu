@@ -1042,6 +1042,12 @@ static int launch_one(const AttnDev& P, dim3 grid, int smem, cudaStream_t st) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (P.cluster > 8) {
+        // a non-portable cluster size with this much shared memory may not be schedulable at all: say so
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return kCudaError; }
+        if (clusters < 1) return kUnsupported;
+    }
     return cudaLaunchKernelEx(&cfg, kern, P) == cudaSuccess ? kOk : kCudaError;
 }
 

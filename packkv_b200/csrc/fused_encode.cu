@@ -594,7 +594,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) compact_kernel(const uint8_
     const unsigned sh = (unsigned)(head & 3) * 8;                      // 0 or 16: byte offset inside that word
     for (int c = lane; c < nfull; c += 32) {
         const unsigned* p = s32 + sw + 4 * c;                          // aligned 32-bit loads, realigned by funnel shifts
-        const unsigned w0 = p[0], w1 = p[1], w2 = p[2], w3 = p[3], w4 = p[4];
+        const unsigned w0 = p[0], w1 = p[1], w2 = p[2], w3 = p[3], w4 = sh ? p[4] : 0u;   // the fifth word is past the slot when sh == 0
         *reinterpret_cast<uint4*>(dst + head + 16 * c) = make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh),
                                                                     __funnelshift_r(w2, w3, sh), __funnelshift_r(w3, w4, sh));
     }

@@ -49,7 +49,8 @@ def register(name: str = ATTN_NAME) -> str:
 
 
 def make_cache(config, batch_size: int, materialize: bool = False) -> PackKVCache:
-    """Cache for a transformers model config (llama / mistral / qwen3 style: head_dim 128)."""
+    """Cache for a transformers model config: llama / mistral / qwen3 style (head_dim 128) or phi-3 style (head_dim 96,
+    hidden_size // num_attention_heads)."""
     head_dim = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
     return PackKVCache(batch_size, config.num_attention_heads, head_dim, config.num_hidden_layers,
                        materialize=materialize, decode_handles=not materialize)

@@ -193,6 +193,34 @@ class CompressedLayer:
         return n
 
 
+def _check_layer_shapes(L: "CompressedLayer", batch: int) -> None:
+    """Host-side bounds of everything the attention kernel indexes from n_comp, kv_heads and the block sizes:
+    a layer whose metadata disagrees with its arrays (a caller mistake, a truncated or corrupt blob) must raise
+    here instead of reading outside the arrays on the device."""
+    if L.cbk not in (64, 128) or L.cbv not in (64, 128) or L.n_comp <= 0 or L.kv_heads <= 0:
+        raise RuntimeError("not supported") if L.cbk == 32 or L.cbv == 32 else ValueError("bad layer metadata")
+    nkb, nvb = (L.n_comp // L.cbk) * L.kv_heads, (L.n_comp // L.cbv) * 2 * L.kv_heads
+    for name in ("k_stream", "v_stream", "k_info", "v_info", "k_scale", "k_zero", "v_scale", "v_zero"):
+        t = getattr(L, name)
+        if t.shape[0] != batch:
+            raise ValueError(f"{name} holds {t.shape[0]} sequences, q holds {batch}")
+    if L.k_info.dim() != 3 or L.k_info.shape[2] != 2 or L.k_info.shape[1] < nkb or not L.k_info.is_contiguous():
+        raise ValueError(f"k_info must be a contiguous (B, >= {nkb}, 2) table")
+    if L.v_info.dim() != 3 or L.v_info.shape[2] != 2 or L.v_info.shape[1] < nvb or not L.v_info.is_contiguous():
+        raise ValueError(f"v_info must be a contiguous (B, >= {nvb}, 2) table")
+    if L.v_scale.dim() != 2 or L.v_scale.shape[1] < L.n_comp or L.v_zero.shape != L.v_scale.shape:
+        raise ValueError("v_scale / v_zero must be (B, >= n_comp)")
+    if L.k_mode == K_CHANNEL:
+        want = (batch, L.kv_heads)
+        if L.k_scale.dim() != 4 or tuple(L.k_scale.shape[:2]) != want or L.k_scale.shape[2] < L.n_comp // L.cbk or L.k_scale.shape[3] != 128 \
+                or L.k_zero.shape != L.k_scale.shape:
+            raise ValueError("channel-mode k_scale / k_zero must be (B, kv_heads, >= n_comp / cbk, 128)")
+    elif L.k_scale.dim() != 2 or L.k_scale.shape[1] < L.n_comp or L.k_zero.shape != L.k_scale.shape:
+        raise ValueError("token-mode k_scale / k_zero must be (B, >= n_comp)")
+    if L.k_stream.dim() != 2 or L.v_stream.dim() != 2 or L.k_stream.stride(1) != 1 or L.v_stream.stride(1) != 1:
+        raise ValueError("streams must be (B, capacity) with contiguous bytes")
+
+
 # changes whenever the attention kernel changes in a way that can change its DRAM traffic (keys recorded profiler figures)
 ATTN_KERNEL_REVISION = 2
 
@@ -233,6 +261,7 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
         for t in (L.k_scale, L.k_zero, L.v_scale, L.v_zero):
             if t.dtype != q.dtype or not t.is_contiguous():
                 raise ValueError("scale / zero tensors must be contiguous and of q's dtype")
+        _check_layer_shapes(L, B)
         a.k_stream, a.k_seq_stride, a.k_capacity = L.k_stream.data_ptr(), L.k_stream.stride(0), L.k_stream.shape[1] & ~15
         a.k_info, a.k_info_seq_stride = L.k_info.data_ptr(), L.k_info.shape[1]
         a.k_scale, a.k_zero = L.k_scale.data_ptr(), L.k_zero.data_ptr()

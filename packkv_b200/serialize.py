@@ -89,10 +89,15 @@ def _layer_from(meta: dict, arrays: Dict[str, torch.Tensor], prefix: str = "") -
     k_stream, v_stream = g("k_stream"), g("v_stream")
     # a decode step reads 16-byte chunks and may touch up to 16 bytes past a block: keep a tail
     pad = lambda s: torch.cat([s, torch.zeros(s.shape[0], 32, dtype=torch.uint8, device=s.device)], dim=1).contiguous()
-    return ops.CompressedLayer(
+    layer = ops.CompressedLayer(
         k_stream=pad(k_stream), k_info=g("k_info").contiguous(), k_bytes=g("k_bytes"), k_scale=g("k_scale").contiguous(), k_zero=g("k_zero").contiguous(),
         v_stream=pad(v_stream), v_info=g("v_info").contiguous(), v_bytes=g("v_bytes"), v_scale=g("v_scale").contiguous(), v_zero=g("v_zero").contiguous(),
         order=arrays.get(prefix + "order"), high_precision_zero=bool(meta["high_precision_zero"]), **{k: int(meta[k]) for k in _LAYER_INTS})
+    # the kernels index the arrays from the metadata: a blob whose metadata and arrays disagree is rejected here
+    if layer.bits_k not in (2, 3, 4) or layer.bits_v not in (2, 3, 4) or layer.k_mode not in (ops.K_CHANNEL, ops.K_TOKEN):
+        raise ValueError("bad layer metadata")
+    ops._check_layer_shapes(layer, int(layer.k_stream.shape[0]))
+    return layer
 
 
 def dumps_layer(layer: ops.CompressedLayer) -> bytes:

@@ -91,6 +91,41 @@ def test_high_precision_zero_and_three_bit_cache(cuda_device, method, dtype):
         C.PackKVCacheConfigStatic.config = None
 
 
+@pytest.mark.parametrize("method", [QuantMethod.KIVI, QuantMethod.PackKV])
+@pytest.mark.parametrize("head_dim", [96, 64])
+def test_head_dim_below_128_matches_reference_cache(cuda_device, method, head_dim):
+    """Phi-3-style heads (head_dim 96, MHA): the cache stores them in 128-channel blocks whose tail repeats the
+    first channels, which leaves every real channel's codes and parameters those of the reference's cache run on
+    head_dim-wide tensors (models/phi.py:744-747 creates the cache with hidden_size // num_attention_heads).
+    Dense views bit-identical, fused attention within 2e-3, prefill + decode across a block boundary."""
+    dev, dtype = cuda_device, torch.bfloat16
+    B, H, G, S0, steps, D = 2, 4, 1, 270, 70, head_dim
+    cfg = _cfg(method)
+    C.PackKVCacheConfigStatic.config = cfg
+    try:
+        cache = C.PackKVCache(B, H * G, D, 1, materialize=True)
+        km, vm = _modes(method)
+        oracle = Q.CacheLayerOracle(64, 192, cfg.k_quant_scale_rel, cfg.v_quant_scale_rel, km, vm)
+        k, v = synth.synth_kv(B, H, S0 + steps, D, seed=41, dtype=dtype)
+        cos, sin = synth.rope_tables(S0 + steps, D, dtype=dtype)
+        Ko, Vo = oracle.update(k[:, :, :S0], v[:, :, :S0], cos[:, :S0], sin[:, :S0])
+        Kg, Vg = cache.update(k[:, :, :S0].to(dev), v[:, :, :S0].to(dev), 0, {"cos": cos[:, :S0].to(dev), "sin": sin[:, :S0].to(dev)})
+        assert Kg.shape[-1] == D and torch.equal(Kg.cpu(), Ko) and torch.equal(Vg.cpu(), Vo)
+        for t in range(S0, S0 + steps):
+            Ko, Vo = oracle.update(k[:, :, t:t + 1], v[:, :, t:t + 1], cos[:, t:t + 1], sin[:, t:t + 1])
+            Kg, Vg = cache.update(k[:, :, t:t + 1].to(dev), v[:, :, t:t + 1].to(dev), 0,
+                                  {"cos": cos[:, t:t + 1].to(dev), "sin": sin[:, t:t + 1].to(dev)})
+        assert torch.equal(Kg.cpu(), Ko) and torch.equal(Vg.cpu(), Vo)
+        q = synth.synth_q(B, H * G, D, seed=5, dtype=dtype)
+        ref = Q.eager_attention(q, Ko, Vo).float()                  # scaling head_dim ** -0.5
+        out = cache.attend(q.to(dev), 0).float().cpu()
+        assert out.shape == ref.shape
+        assert ((out - ref).abs().max() / ref.abs().max()).item() <= 2e-3
+        cache.check_flags()
+    finally:
+        C.PackKVCacheConfigStatic.config = None
+
+
 def test_append_streams_equal_one_shot_encode(cuda_device):
     """Blocks appended one at a time give the same bytes as encoding the history in one call."""
     from packkv_b200 import encode, ops

@@ -11,9 +11,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("family", ["mistral", "qwen3"])
+@pytest.mark.parametrize("family", ["mistral", "qwen3", "phi3"])
 def test_other_model_families(family):
-    """The same drop-in on the other head_dim-128 families the reference patches (models/mistral.py, qwen3.py)."""
+    """The same drop-in on the other families the reference patches (models/mistral.py, qwen3.py, phi.py); Phi-3
+    has head_dim 96 and no grouped queries, its cache is created with hidden_size // num_attention_heads
+    (models/phi.py:744-747)."""
     transformers = pytest.importorskip("transformers")
     from packkv_b200 import hf
     from packkv_b200.cache import PackKVCacheConfigStatic
@@ -23,6 +25,10 @@ def test_other_model_families(family):
     if family == "mistral":
         from transformers import MistralConfig as Cfg, MistralForCausalLM as Model
         kw["sliding_window"] = None
+    elif family == "phi3":
+        from transformers import Phi3Config as Cfg, Phi3ForCausalLM as Model
+        kw = dict(hidden_size=384, num_attention_heads=4, num_key_value_heads=4, num_hidden_layers=2, intermediate_size=768,
+                  vocab_size=1000, max_position_embeddings=1024, pad_token_id=0, bos_token_id=1, eos_token_id=2)
     else:
         from transformers import Qwen3Config as Cfg, Qwen3ForCausalLM as Model
     torch.manual_seed(2)

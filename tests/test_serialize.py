@@ -44,6 +44,28 @@ def test_rejects_garbage():
         serialize.loads_cache(blob, device="cpu")
 
 
+def test_rejects_metadata_that_disagrees_with_the_arrays():
+    """The attention kernel indexes the block tables and parameter arrays from n_comp, kv_heads and the block
+    sizes: a layer (restored from a blob or built by a caller) that claims more tokens or heads than its arrays
+    hold, or another batch than q, must raise on the host and never reach the device."""
+    for field, value in (("cbk", 32), ("bits_v", 7), ("k_mode", 5)):
+        L = _fake_layer()
+        setattr(L, field, value)
+        with pytest.raises((ValueError, RuntimeError)):
+            serialize.loads_layer(serialize.dumps_layer(L), device="cpu")
+    for field, value in (("n_comp", 4096), ("kv_heads", 16)):
+        L = _fake_layer()
+        setattr(L, field, value)
+        with pytest.raises(ValueError):
+            ops._check_layer_shapes(L, 2)
+    with pytest.raises(ValueError):
+        ops._check_layer_shapes(_fake_layer(), 3)          # q with another batch size
+    L = _fake_layer()
+    L.v_info = L.v_info[:, :3]
+    with pytest.raises(ValueError):
+        ops._check_layer_shapes(L, 2)
+
+
 @pytest.mark.gpu
 def test_restored_layer_and_cache_decode_identically(cuda_device):
     from packkv_b200 import encode, synth

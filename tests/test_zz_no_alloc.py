@@ -56,6 +56,37 @@ def test_static_scratch_matches_caller_scratch_twice(cuda_device):
         _same(want, got)
 
 
+def test_static_scratch_two_stage_paths_appends_and_the_exact_limit(cuda_device):
+    """The paths that keep a whole code matrix in the built-in array (high-precision zero-points; per-token K),
+    an append into a stream that already holds blocks (first_token > 0), and a call that needs exactly the
+    array's 16 MiB: all bit-identical to the ordinary entry point."""
+    dev = cuda_device
+    cases = [  # (which, mode, dtype, B, H, S, block, bits, hp, first_tokens)
+        ("k", ops.K_CHANNEL, torch.float16, 2, 4, 256, 64, 4, True, 0),
+        ("v", ops.K_TOKEN, torch.bfloat16, 2, 4, 256, 64, 4, True, 0),
+        ("k", ops.K_TOKEN, torch.bfloat16, 3, 2, 128, 64, 3, False, 0),
+        ("k", ops.K_CHANNEL, torch.bfloat16, 2, 8, 128, 64, 4, False, 128),    # second call appends 128 tokens after 128
+        ("k", ops.K_CHANNEL, torch.float16, 4, 8, 4096, 64, 4, False, 0),       # 4*4096*8*128 = 16 MiB exactly
+    ]
+    for which, mode, dtype, B, H, S, block, bits, hp, first in cases:
+        total = S + first
+        k, v = synth.synth_kv(B, H, total, 128, seed=11, dtype=dtype, device=dev)
+        x = k if which == "k" else v
+        rel = synth.rel_for_bits(bits)
+        want = _buffers(B, H, total, block, bits, which, mode, dtype, dev)
+        got = _buffers(B, H, total, block, bits, which, mode, dtype, dev)
+        if S * B * H * 128 == _lib.STATIC_SCRATCH_BYTES:
+            assert B * S * H * 128 == _lib.STATIC_SCRATCH_BYTES
+        for fn, bufs in ((ops.encode_tensor, want), (ops.encode_tensor_static, got)):
+            if first:
+                fn(which, x[:, :, :first], block, rel, mode, bits, block, high_precision_zero=hp, **bufs)
+            fn(which, x[:, :, first:], block, rel, mode, bits, block, high_precision_zero=hp, first_token=first, **bufs)
+        torch.cuda.synchronize()
+        assert int(want["flags"].item()) == 0
+        assert int(want["stream_bytes"].min().item()) > 0
+        _same(want, got)
+
+
 def test_static_scratch_refuses_oversized_calls(cuda_device):
     dev = cuda_device
     B, H, S = 8, 8, 4096                      # 8*4096*8*128 = 32 MiB of codes > 16 MiB
