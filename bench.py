@@ -420,25 +420,48 @@ def encode_leg(steps, warmup, rank, world, device, *, total_seqs=64, bits=4, blo
                                   "traffic": NCU_TRAFFIC_BYTES.get(("encode", ENCODE_REVISION, B, bits, block)) if method == RepackMethod.NONE else None}}
         del layer
     if with_append:
-        # append: 512 single-token steps on a cache prefilled with 1024 tokens
+        # append: 512 single-token decode steps on a cache prefilled with 1024 tokens.  (a) update() + attend(): the
+        # attention launch writes the new token itself, every 64th step a block is compressed; (b) attend() alone on
+        # the same cache; the difference is what appending costs per token step.  (c) update() alone: the
+        # separate append launch that a caller without the fused attention pays.
         C.PackKVCacheConfigStatic.config = PackKVCacheConfig("synthetic", QuantMethod.KIVI, RepackMethod.NONE, False, block, 128 + block, 16, rel, rel)
-        cache = C.PackKVCache(B, H, 128, 1)
-        cos, sin = synth.rope_tables(1024 + 512 + 4, 128, device=device, dtype=dtype)
-        cache.update(k[:, :, :1024], v[:, :, :1024], 0, {"cos": cos[:, :1024], "sin": sin[:, :1024]})
-        pos = [1024]
+        cos, sin = synth.rope_tables(1024 + 1100, 128, device=device, dtype=dtype)
+        q = synth.synth_q(B, 4 * H, 128, seed=9, dtype=dtype, device=device)
 
-        def append_step():
+        def fresh():
+            c = C.PackKVCache(B, 4 * H, 128, 1)
+            c.update(k[:, :, :1024], v[:, :, :1024], 0, {"cos": cos[:, :1024], "sin": sin[:, :1024]})
+            return c, [1024]
+        cache, pos = fresh()
+
+        def step_update():
             t = pos[0]
             cache.update(k[:, :, t:t + 1], v[:, :, t:t + 1], 0, {"cos": cos[:, t:t + 1], "sin": sin[:, t:t + 1]})
             pos[0] += 1
+
+        def step_both():
+            step_update()
+            cache.attend(q, 0)
         for _ in range(3):
-            append_step()
-        ms_append, _, _ = timed_batches(append_step, 512, world, device, min_seconds=0.0, max_batches=1)
-        ms_append /= 512
+            step_both()
+        ms_both, _, _ = timed_batches(step_both, 512, world, device, min_seconds=0.0, max_batches=1)
+        cache.check_flags()
+        # attention alone at the middle length of those steps
+        cache = C.PackKVCache(B, 4 * H, 128, 1)
+        cache.update(k[:, :, :1024 + 256], v[:, :, :1024 + 256], 0, {"cos": cos[:, :1280], "sin": sin[:, :1280]})
+        for _ in range(3):
+            cache.attend(q, 0)
+        ms_attend, _, _ = timed_batches(lambda: cache.attend(q, 0), 512, world, device, min_seconds=0.0, max_batches=1)
+        cache.check_flags()
+        cache, pos = fresh()
+        for _ in range(3):
+            step_update()
+        ms_update, _, _ = timed_batches(step_update, 512, world, device, min_seconds=0.0, max_batches=1)
         cache.check_flags()
         C.PackKVCacheConfigStatic.config = None
-        out["append"] = {"us_per_token_step": ms_append * 1e3, "sequences_per_gpu": B, "steps": 512,
-                         "token_appends_per_s": world * B / (ms_append * 1e-3)}
+        out["append"] = {"us_per_token_step": max(0.0, ms_both - ms_attend) / 512 * 1e3, "update_plus_attend_us": ms_both / 512 * 1e3,
+                         "attend_only_us": ms_attend / 512 * 1e3, "separate_append_launch_us": ms_update / 512 * 1e3,
+                         "sequences_per_gpu": B, "steps": 512, "token_appends_per_s": world * B / (max(1e-6, ms_both - ms_attend) / 512 * 1e-3)}
     if with_e2e:
         # end to end: K and V start in pinned host memory, the streams and their byte counts go back to it
         layer = encode.compress_kv(k, v, **kw)
@@ -553,6 +576,7 @@ def main():
     ap.add_argument("--decode-cbv", type=int, default=None, choices=[64, 128], help="override the V token block (sweeps)")
     ap.add_argument("--decode-batch", type=int, default=None, help="override the batch (sweeps)")
     ap.add_argument("--decode-ctx", type=int, default=None, help="override the context length (sweeps)")
+    ap.add_argument("--decode-layers", type=int, default=None, help="override the number of layers (sweeps, profiling)")
     ap.add_argument("--decode-k-mode", default="channel", choices=["channel", "token"], help="K quantisation parameters (sweeps)")
     ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
                     help="multi-GPU split: independent sequences per rank (weak scaling, no collective) or KV heads per "
@@ -561,10 +585,10 @@ def main():
     args = ap.parse_args()
     w = WORKLOADS.get(args.workload)
     overridden = w is not None and (args.decode_bits_k or args.decode_bits_v or args.decode_k_mode != "channel" or args.decode_cbv
-                                    or args.decode_batch or args.decode_ctx)
+                                    or args.decode_batch or args.decode_ctx or args.decode_layers)
     if overridden:
         w = dict(w, bits_k=args.decode_bits_k or w["bits_k"], bits_v=args.decode_bits_v or w["bits_v"], k_mode=args.decode_k_mode,
-                 cbv=args.decode_cbv or w["cbv"], batch=args.decode_batch or w["batch"], ctx=args.decode_ctx or w["ctx"])
+                 cbv=args.decode_cbv or w["cbv"], batch=args.decode_batch or w["batch"], ctx=args.decode_ctx or w["ctx"], layers=args.decode_layers or w["layers"])
         w["name"] += f" [override: batch {w['batch']}, ctx {w['ctx']}, K {w['bits_k']}-bit {w['k_mode']}, V {w['bits_v']}-bit, V block {w['cbv']}]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -200,6 +200,22 @@ int32_t pkv_encode_tensor(const pkv_encode_args* args_host, uint8_t* codes_scrat
                           void* cuda_stream);
 
 /*
+ * The same single pass with the reference's median reorder inside (median_repacking, utils/compute.py:262-270:
+ * the tokens of every block are sorted by the descending lower median of their V codes, one order for K and V).
+ * pkv_value_median_order computes the order straight from fp16/bf16 V (args: x, strides, batch, heads <= 8,
+ * tokens, rel, is_bf16 of the V tensor; block = 64): order (batch, tokens/block, block) uint8, entry r = source
+ * row of stored row r, stable on ties, per sequence.  pkv_encode_tensor_ordered then encodes K or V reading
+ * its rows through that order (per-token parameters land at the stored positions); streams and parameters
+ * equal pkv_quantize -> pkv_gather_rows / pkv_gather_params -> pkv_{k,v}_encode.  Restrictions: the modes the
+ * single pass serves (K per channel with cb = qblock = order_block, or per token; V per token; no
+ * high-precision zero), order_block a multiple of 16 that divides cb; PKV_ERR_UNSUPPORTED otherwise.
+ * scratch: 16-byte aligned, at least batch*tokens*heads*128 bytes is always enough.
+ */
+int32_t pkv_value_median_order(const pkv_encode_args* v_args_host, uint8_t* order, int32_t block, void* cuda_stream);
+int32_t pkv_encode_tensor_ordered(const pkv_encode_args* args_host, const uint8_t* order, int32_t order_block,
+                                  uint8_t* scratch, int64_t scratch_bytes, void* cuda_stream);
+
+/*
  * pkv_encode_tensor without a scratch argument, for callers that must not touch the device
  * allocator.  (No counterpart in the reference, which allocates freely through torch.)
  *
@@ -319,6 +335,26 @@ int32_t pkv_decode_attention_exchange(const pkv_attn_args* args_host, const pkv_
                                       void* cuda_stream);
 int32_t pkv_exchange_wait(const uint32_t* arrivals, int32_t n_ranks, uint32_t expected, uint32_t max_polls,
                           uint32_t* dev_flags, void* cuda_stream);
+/*
+ * Decode step with the append folded in: the launch first writes the step's new token (K after RoPE with the
+ * arithmetic of pkv_rope, V as is) into row n_res-1 of the residual buffers and then attends over all n_res
+ * residual tokens, i.e. args.n_res COUNTS the new token.  Replaces the pair
+ * past_key_value.update(...) + attention of a decode step (models/llama.py:259-282,
+ * models/cache/packkv_quant.py:57-60) when no block leaves the residual in this step; saves the separate
+ * pkv_append_residual launch.  new_k / new_v: (batch, kv_heads, 1, 128), strides in elements; cos / sin:
+ * (batch or 1, 1, 128) with cs_stride_b = 0 for a shared row, or both NULL if new_k is already rotated.
+ * res_capacity = rows of the residual buffers (n_res <= res_capacity is checked).  `exchange_host` may be NULL.
+ */
+typedef struct pkv_attn_append {
+    const void* new_k; const void* new_v;
+    int64_t k_stride_b, k_stride_h, v_stride_b, v_stride_h;
+    const void* cos; const void* sin;
+    int64_t cs_stride_b;
+    int32_t res_capacity;
+} pkv_attn_append;
+int32_t pkv_decode_attention_append(const pkv_attn_args* args_host, const pkv_attn_append* append_host,
+                                    const pkv_attn_exchange* exchange_host, void* cuda_stream);
+
 /*
  * Set-up helpers of the exchange; the only entry points that allocate or touch address-space mappings (they
  * synchronise, call them once, outside the decode loop).  pkv_exchange_alloc returns `bytes` of zeroed device

@@ -43,6 +43,12 @@ class AttnExchange(ctypes.Structure):
     _fields_ = [("n_ranks", _i32), ("rank", _i32), ("gathered", _p * 8), ("arrivals", _p * 8)]
 
 
+class AttnAppend(ctypes.Structure):
+    """Mirror of pkv_attn_append (include/packkv_sm100.h)."""
+    _fields_ = [("new_k", _p), ("new_v", _p), ("k_stride_b", _i64), ("k_stride_h", _i64), ("v_stride_b", _i64), ("v_stride_h", _i64),
+                ("cos", _p), ("sin", _p), ("cs_stride_b", _i64), ("res_capacity", _i32)]
+
+
 class EncodeArgs(ctypes.Structure):
     """Mirror of pkv_encode_args (include/packkv_sm100.h)."""
     _fields_ = [
@@ -58,6 +64,8 @@ class EncodeArgs(ctypes.Structure):
 SIGNATURES = {
     "pkv_encode_tensor": (_i32, [ctypes.POINTER(EncodeArgs), _p, _i64, _p]),
     "pkv_encode_tensor_static": (_i32, [ctypes.POINTER(EncodeArgs), _p]),
+    "pkv_encode_tensor_ordered": (_i32, [ctypes.POINTER(EncodeArgs), _p, _i32, _p, _i64, _p]),
+    "pkv_value_median_order": (_i32, [ctypes.POINTER(EncodeArgs), _p, _i32, _p]),
     "pkv_kq_mat_vec_mul": (_i32, [_p, _i64, _p, _p, _p] + [_i32] * 6 + [_p, _p]),
     "pkv_wv_mat_vec_mul": (_i32, [_p, _i64, _p, _p, _p] + [_i32] * 6 + [_p, _p]),
     "pkv_fused_kq": (_i32, [_p] * 5 + [_i32] * 4 + [_p]),
@@ -73,6 +81,7 @@ SIGNATURES = {
     "pkv_quantize": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _p] + [_i32] * 8 + [_f32] + [_i32] * 4 + [_p, _p]),
     "pkv_decode_attention": (_i32, [ctypes.POINTER(AttnArgs), _p]),
     "pkv_decode_attention_exchange": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnExchange), _p]),
+    "pkv_decode_attention_append": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnAppend), ctypes.POINTER(AttnExchange), _p]),
     "pkv_exchange_wait": (_i32, [_p, _i32, ctypes.c_uint32, ctypes.c_uint32, _p, _p]),
     "pkv_exchange_alloc": (_i32, [_i64, ctypes.POINTER(ctypes.c_void_p), _p]),
     "pkv_exchange_free": (_i32, [_p]),

@@ -69,6 +69,7 @@ class _Layer:
         self.v_res: Optional[torch.Tensor] = None
         self.n_res = 0
         self.n_comp = 0
+        self.pending = None        # (k_new, v_new, cos, sin) of a decode step whose token the next attend() writes into row n_res - 1
 
 
 class PackKVCache(_HFCache):
@@ -193,6 +194,7 @@ class PackKVCache(_HFCache):
         if PackKVCacheConfigStatic.extract_cache is not None:
             assert not cfg.enable_quant, "Disable quant to enable cache collect."
         L = self._layers[layer_idx]
+        self._flush(L)
         B, H, T, D = key_states.shape
         if D != 128 and (D > 128 or D < 64 or D % 8):
             raise RuntimeError("not supported")   # streams are built from 128-channel blocks; 64..120 are padded, see _widen
@@ -210,8 +212,14 @@ class PackKVCache(_HFCache):
         if cfg.enable_quant and L.k_res is not None:
             total = L.n_res + T
             if compress_block_count(total, cfg.block_size, cfg.buffer_size) == 0:
-                # the common decode step: rotate K and copy V straight into the residual, one launch
-                ops.append_residual(key_states, value_states, L.k_res, L.v_res, L.n_res, cos, sin)
+                # the common decode step: rotate K and copy V straight into the residual.  With one new token and
+                # the fused attention to follow, the attention launch does it itself (attend() below); otherwise one launch
+                if T == 1 and not self.materialize and key_states.dtype in (torch.float16, torch.bfloat16):
+                    if cos is not None:
+                        cos, sin = cos.to(key_states.dtype).contiguous(), sin.to(key_states.dtype).contiguous()
+                    L.pending = (key_states, value_states, cos, sin)
+                else:
+                    ops.append_residual(key_states, value_states, L.k_res, L.v_res, L.n_res, cos, sin)
                 L.n_res = total
                 return self._step_result(layer_idx, T)
         k_new = ops.rope(key_states, cos, sin) if cos is not None else key_states.contiguous()
@@ -249,6 +257,18 @@ class PackKVCache(_HFCache):
             L.v_res[:, :, : L.n_res] = v_all[:, :, n_c:]
         return self._step_result(layer_idx, T)
 
+    def _flush(self, L: "_Layer") -> None:
+        """Writes a decode step's token that no attend() has consumed into the residual (one launch)."""
+        if L.pending is not None:
+            k_new, v_new, cos, sin = L.pending
+            L.pending = None
+            ops.append_residual(k_new, v_new, L.k_res, L.v_res, L.n_res - 1, cos, sin)
+
+    def flush(self) -> None:
+        """Makes the residual buffers of every layer complete (call before reading them from outside)."""
+        for L in self._layers:
+            self._flush(L)
+
     @staticmethod
     def _widen(x: torch.Tensor) -> torch.Tensor:
         """(B, H, T, D) with 64 <= D < 128 -> (B, H, T, 128): the tail repeats the first 128 - D channels.  The
@@ -268,6 +288,7 @@ class PackKVCache(_HFCache):
     def dense(self, layer_idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """Dequantised history + residual, (B, H, S, 128): what the reference's update returns."""
         L = self._layers[layer_idx]
+        self._flush(L)
         D = self.head_dim if self.head_dim < 128 else 128
         k_res, v_res = L.k_res[:, :, : L.n_res, :D], L.v_res[:, :, : L.n_res, :D]
         if L.n_comp == 0:
@@ -303,8 +324,9 @@ class PackKVCache(_HFCache):
             q = torch.nn.functional.pad(q, (0, 128 - D))       # zeros: the copied channels of K add nothing
         q = q.contiguous()
         kv_heads = L.comp.kv_heads if L.comp is not None else L.k_res.shape[1]
+        pending, L.pending = L.pending, None
         out = ops.decode_attention(q, L.comp if L.n_comp else None, L.k_res, L.v_res, L.n_res, scaling=scaling,
-                                   flags=self.flags, kv_heads=kv_heads)
+                                   flags=self.flags, kv_heads=kv_heads, append=pending)
         return out.view(B, 1, Hq, 128)[..., :D]
 
     def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:

@@ -256,6 +256,7 @@ struct AttnDev {
     int nkb_shift, nvi_shift;               // log2 of K blocks per tile and of V blocks (2 halves x token blocks) per tile
     FieldSpread klen, kmin, vlen, vmin;     // header field widths -> bytes
     AttnExchange x;      // head-sharded multi-GPU output exchange (n_ranks = 0: none)
+    AttnAppend ap;       // the step's new token, written into residual row n_res - 1 by this launch (new_k = null: none)
 };
 
 // CTA-shared block (cluster-visible)
@@ -649,6 +650,43 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
     // 32m + 8c .. +7 (m = 0..3) of tokens g and g+8 and pairs them in the order of pair_shuffle.
     const T* kres = reinterpret_cast<const T*>(a.k_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
     const T* vres = reinterpret_cast<const T*>(a.v_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
+    // The decode step's new token: the warp that owns the residual tile of row n_res - 1 rotates K (the
+    // arithmetic of rope_kernel: both products rounded to the element type, then their sum) and copies V into
+    // that row first; its own loads of the tile below then see the row (plain loads and cp.async, no read-only path).
+    if (P.ap.new_k != nullptr && my_rt > 0) {
+        const int tn = a.n_res - 1, tile_n = tn >> 4;
+        if (tile_n % n_warps == rslot) {
+            if (lane < 16) {
+                const T* x = reinterpret_cast<const T*>(P.ap.new_k) + (int64_t)b * P.ap.k_stride_b + (int64_t)h * P.ap.k_stride_h;
+                const int d0 = 8 * lane;
+                uint4 xv = *reinterpret_cast<const uint4*>(x + d0);
+                if (P.ap.cos != nullptr) {
+                    const uint4 rv = *reinterpret_cast<const uint4*>(x + (d0 < 64 ? d0 + 64 : d0 - 64));
+                    const uint4 cv = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(P.ap.cos) + (int64_t)b * P.ap.cs_stride_b + d0);
+                    const uint4 sv = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(P.ap.sin) + (int64_t)b * P.ap.cs_stride_b + d0);
+                    const unsigned xs[4] = {xv.x, xv.y, xv.z, xv.w}, rs[4] = {rv.x, rv.y, rv.z, rv.w};
+                    const unsigned cs4[4] = {cv.x, cv.y, cv.z, cv.w}, ss4[4] = {sv.x, sv.y, sv.z, sv.w};
+                    unsigned o4[4];
+                    const float sgn = d0 < 64 ? -1.f : 1.f;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float2 xf = Tr<T>::unpack2(xs[i]), rf = Tr<T>::unpack2(rs[i]), cf = Tr<T>::unpack2(cs4[i]), sf = Tr<T>::unpack2(ss4[i]);
+                        const float a0 = Tr<T>::round(xf.x * cf.x), a1 = Tr<T>::round(xf.y * cf.y);
+                        const float c0 = Tr<T>::round(sgn * rf.x * sf.x), c1 = Tr<T>::round(sgn * rf.y * sf.y);
+                        o4[i] = Tr<T>::pack2(a0 + c0, a1 + c1);
+                    }
+                    xv = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+                }
+                *reinterpret_cast<uint4*>(const_cast<T*>(kres) + (int64_t)tn * kD + d0) = xv;
+            } else {
+                const T* y = reinterpret_cast<const T*>(P.ap.new_v) + (int64_t)b * P.ap.v_stride_b + (int64_t)h * P.ap.v_stride_h;
+                const int d0 = 8 * (lane - 16);
+                *reinterpret_cast<uint4*>(const_cast<T*>(vres) + (int64_t)tn * kD + d0) = *reinterpret_cast<const uint4*>(y + d0);
+            }
+            __threadfence();
+        }
+        __syncwarp();
+    }
     if (my_rt > 0) {
         unsigned qr[8][2];
         const uint4* qp = reinterpret_cast<const uint4*>(
@@ -665,7 +703,7 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
             const uint4* pb = reinterpret_cast<const uint4*>(kres + (int64_t)min(tb, a.n_res - 1) * kD + 8 * c);
             uint4 ra[4], rb[4];
 #pragma unroll
-            for (int m = 0; m < 4; m++) { ra[m] = __ldg(pa + 4 * m); rb[m] = __ldg(pb + 4 * m); }
+            for (int m = 0; m < 4; m++) { ra[m] = pa[4 * m]; rb[m] = pb[4 * m]; }   // plain loads: a row may have been written by this launch
             float accs[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int m = 0; m < 4; m++) {
@@ -1119,7 +1157,7 @@ int launch_exchange_wait(const uint32_t* arrivals, int n_ranks, unsigned expecte
     return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
 }
 
-int launch_attention(const AttnArgs& a, const AttnExchange* xch, cudaStream_t st) {
+int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppend* ap, cudaStream_t st) {
     if (a.batch <= 0 || a.kv_heads <= 0 || a.group < 1 || a.group > 8) return a.group > 8 ? kUnsupported : kBadArgument;
     if (a.n_comp < 0 || a.n_res < 0 || a.n_comp + a.n_res == 0) return kBadArgument;
     if (!a.q || !a.out || !a.flags) return kBadArgument;
@@ -1147,6 +1185,14 @@ int launch_attention(const AttnArgs& a, const AttnExchange* xch, cudaStream_t st
 
     AttnDev P{};
     P.a = a;
+    if (ap) {
+        if (!ap->new_k || !ap->new_v || a.n_res < 1 || a.n_res > ap->res_capacity || ((ap->cos == nullptr) != (ap->sin == nullptr))) return kBadArgument;
+        if ((reinterpret_cast<uintptr_t>(ap->new_k) & 15) || (reinterpret_cast<uintptr_t>(ap->new_v) & 15) || (ap->k_stride_b & 7) || (ap->k_stride_h & 7) ||
+            (ap->v_stride_b & 7) || (ap->v_stride_h & 7) || (reinterpret_cast<uintptr_t>(ap->cos) & 15) || (reinterpret_cast<uintptr_t>(ap->sin) & 15) ||
+            (ap->cs_stride_b & 7))
+            return kBadArgument;
+        P.ap = *ap;
+    }
     if (xch) {
         if (xch->n_ranks < 1 || xch->n_ranks > 8 || xch->rank < 0 || xch->rank >= xch->n_ranks) return kBadArgument;
         for (int p = 0; p < xch->n_ranks; p++)
@@ -1178,7 +1224,7 @@ int launch_attention(const AttnArgs& a, const AttnExchange* xch, cudaStream_t st
     }
     // Cluster size and staging depth: the (sequence, KV head) pairs times the cluster size should fill the
     // 148 SMs' CTA slots in whole waves, every warp should have work, and a long sequence must fit its scores
-    // in shared memory.  Cost model: waves x work units per warp x (resident warps beyond 16 per SM share
+    // in shared memory.  Cost model: waves x work units per warp x (resident warps beyond 10 per SM share
     // the issue slots).
     static const int env_cl = env_int("PKV_ATTN_CLUSTER"), env_slots = env_int("PKV_ATTN_SLOTS");
     const long pairs = (long)a.batch * a.kv_heads;
@@ -1201,7 +1247,8 @@ int launch_attention(const AttnArgs& a, const AttnExchange* xch, cudaStream_t st
             const double resident = (double)(ctas < slots ? ctas : slots) / kSmCount * kAW;   // warps per SM
             const int n_warps = kAW * cl;
             const int upw = ((P.tiles_total + n_warps - 1) / n_warps) * unit_tile + (((a.n_res + 15) / 16 + n_warps - 1) / n_warps);
-            double cost = (double)waves * (upw + 3.0 /* fixed part per CTA: exchange, reductions */) * (resident > 16.0 ? resident / 16.0 : 1.0);
+            // measured: an SM's throughput stops growing at about 10 resident warps (the kernel is bound by instruction issue)
+            double cost = (double)waves * (upw + 3.0 /* fixed part per CTA: exchange, reductions */) * (resident > 10.0 ? resident / 10.0 : 1.0);
             if (ns == 1) cost *= 1.06;                          // the copy of the next block is not overlapped
             if (cl > 8) cost *= 1.10;                           // non-portable cluster sizes schedule worse
             if (cost < best_cost - 1e-9) { best_cost = cost; best_cl = cl; best_ns = ns; best_smem = smem; }

@@ -11,9 +11,10 @@ enum KMode : int { kKChannel = PKV_K_CHANNEL, kKToken = PKV_K_TOKEN };
 using AttnArgs = pkv_attn_args;
 
 using AttnExchange = pkv_attn_exchange;
+using AttnAppend = pkv_attn_append;
 
-// xch may be null (single GPU)
-int launch_attention(const AttnArgs& a, const AttnExchange* xch, cudaStream_t st);
+// xch may be null (single GPU); ap may be null (the residual already holds every token)
+int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppend* ap, cudaStream_t st);
 int launch_exchange_wait(const uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, cudaStream_t st);
 
 }  // namespace pkv

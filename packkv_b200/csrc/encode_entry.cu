@@ -18,7 +18,7 @@ static int32_t encode_tensor(const pkv_encode_args& e, uint8_t* codes, cudaStrea
     // K per-channel and V per-token go through the single-pass kernels; the scratch then holds
     // fixed-stride block slots (smaller than the code matrix it is sized for)
     if (fused_encode_applicable(e) && fused_encode_scratch_bytes(e) <= (int64_t)e.batch * e.tokens * e.heads * 128)
-        return launch_fused_encode(e, codes, st);
+        return launch_fused_encode(e, codes, nullptr, 0, st);
     QuantArgs q{e.x, e.stride_b, e.stride_h, e.stride_s, codes, (int64_t)e.tokens * e.heads * 128, e.scale, e.zero,
                 e.param_blocks, e.qblock > 0 ? e.first_token / e.qblock : 0, e.param_tokens, e.first_token,
                 e.batch, e.heads, e.tokens, e.qblock, e.rel, e.bits, e.mode, e.high_precision_zero, e.is_bf16, e.flags};
@@ -39,6 +39,22 @@ extern "C" int32_t pkv_encode_tensor(const pkv_encode_args* args_host, uint8_t* 
     if (need == 0) return kOk;
     if (!codes_scratch || scratch_bytes < need || (reinterpret_cast<uintptr_t>(codes_scratch) & 15)) return kBadArgument;
     return encode_tensor(e, codes_scratch, static_cast<cudaStream_t>(cuda_stream));
+}
+
+extern "C" int32_t pkv_encode_tensor_ordered(const pkv_encode_args* args_host, const uint8_t* order, int32_t order_block, uint8_t* scratch,
+                                             int64_t scratch_bytes, void* cuda_stream) {
+    if (!args_host || !order) return kBadArgument;
+    const pkv_encode_args& e = *args_host;
+    if (e.batch < 0 || e.heads <= 0 || e.tokens < 0 || (e.which != 0 && e.which != 1) || e.cb <= 0 || e.first_token % e.cb) return kBadArgument;
+    if ((int64_t)e.batch * e.tokens == 0) return kOk;
+    if (!fused_encode_applicable(e)) return kUnsupported;
+    if (!scratch || scratch_bytes < fused_encode_scratch_bytes(e) || (reinterpret_cast<uintptr_t>(scratch) & 15)) return kBadArgument;
+    return launch_fused_encode(e, scratch, order, order_block, static_cast<cudaStream_t>(cuda_stream));
+}
+
+extern "C" int32_t pkv_value_median_order(const pkv_encode_args* v_args_host, uint8_t* order, int32_t block, void* cuda_stream) {
+    if (!v_args_host) return kBadArgument;
+    return launch_value_median_order(*v_args_host, order, block, static_cast<cudaStream_t>(cuda_stream));
 }
 
 // Device address of g_static_codes on the current device.  In host code the symbol's name is only

@@ -32,6 +32,8 @@ struct FusedArgs {
     int batch, heads, tokens, cb, bits;
     float rel;
     unsigned* flags;
+    const uint8_t* order;                   // optional (batch, tokens / order_block, order_block): source row of every stored row
+    int order_block;                        // tokens per reorder block (divides cb)
 };
 
 __device__ __forceinline__ void store_slot(uint8_t* slot, const uint8_t* stage, int size, int lane) {
@@ -41,8 +43,9 @@ __device__ __forceinline__ void store_slot(uint8_t* slot, const uint8_t* stage, 
 
 // ------------------------------------------------------------------------------------------ K
 // rounds of one K block: quantise 16 tokens x 4 channels per lane, pack, append to `stage`
-template <typename T, bool HP, int BITS, bool FAST>
-__device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const Quantiser<T, HP>& q0, const Quantiser<T, HP>& q1,
+// ORDERED: stored row t of the block is source row ordp[t] (16-byte aligned table of the block's rows)
+template <typename T, bool HP, int BITS, bool FAST, bool ORDERED>
+__device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const uint8_t* ordp, const Quantiser<T, HP>& q0, const Quantiser<T, HP>& q1,
                                                const Quantiser<T, HP>& q2, const Quantiser<T, HP>& q3, const KGeom& g, uint8_t* stage,
                                                int lane, bool& bad) {
     constexpr int LB = len_field_bits(BITS);
@@ -52,9 +55,13 @@ __device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const Qua
     for (int r = 0; r < g.rounds; r++) {
         unsigned u[16];                               // four channel codes per token, one byte each
         unsigned mnj[4] = {255u, 255u, 255u, 255u}, mxj[4] = {0u, 0u, 0u, 0u};
+        uint4 ob = make_uint4(0, 0, 0, 0);
+        if (ORDERED) ob = __ldg(reinterpret_cast<const uint4*>(ordp + 16 * r));
+        const unsigned ow[4] = {ob.x, ob.y, ob.z, ob.w};
 #pragma unroll
         for (int t = 0; t < 16; t++) {
-            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)(r * 16 + t) * ss));
+            const int row = ORDERED ? (int)((ow[t >> 2] >> (8 * (t & 3))) & 0xFFu) : r * 16 + t;
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)row * ss));
             const T* e = reinterpret_cast<const T*>(&raw);
             const unsigned c0 = q0.template code_u8<FAST>(QT<T>::ld(e), z0), c1 = q1.template code_u8<FAST>(QT<T>::ld(e + 1), z1);
             const unsigned c2 = q2.template code_u8<FAST>(QT<T>::ld(e + 2), z2), c3 = q3.template code_u8<FAST>(QT<T>::ld(e + 3), z3);
@@ -111,8 +118,8 @@ __device__ __forceinline__ int k_encode_rounds(const T* x, int64_t ss, const Qua
 // The same rounds for blocks whose four quantisers are packable(): two channels per instruction
 // from the conversion to the pack minimum / maximum (16-bit lanes), then one multiply-add per code
 // into the pack words.
-template <typename T, int BITS, bool HALF>
-__device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, const Quantiser<T, false>& q0, const Quantiser<T, false>& q1,
+template <typename T, int BITS, bool HALF, bool ORDERED>
+__device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, const uint8_t* ordp, const Quantiser<T, false>& q0, const Quantiser<T, false>& q1,
                                                       const Quantiser<T, false>& q2, const Quantiser<T, false>& q3, const KGeom& g,
                                                       uint8_t* stage, int lane, bool& bad) {
     constexpr int LB = len_field_bits(BITS);
@@ -123,9 +130,13 @@ __device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, co
     for (int r = 0; r < g.rounds; r++) {
         unsigned c01[16], c23[16];
         unsigned mn01 = 0xFFFFFFFFu, mx01 = 0u, mn23 = 0xFFFFFFFFu, mx23 = 0u;
+        uint4 ob = make_uint4(0, 0, 0, 0);
+        if (ORDERED) ob = __ldg(reinterpret_cast<const uint4*>(ordp + 16 * r));
+        const unsigned ow[4] = {ob.x, ob.y, ob.z, ob.w};
 #pragma unroll
         for (int t = 0; t < 16; t++) {
-            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)(r * 16 + t) * ss));
+            const int row = ORDERED ? (int)((ow[t >> 2] >> (8 * (t & 3))) & 0xFFu) : r * 16 + t;
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)row * ss));
             c01[t] = HALF ? h01.codes(raw.x) : packed_codes<T>(raw.x, q0, q1, k01);
             c23[t] = HALF ? h23.codes(raw.y) : packed_codes<T>(raw.y, q2, q3, k23);
             mn01 = min_u16x2(mn01, c01[t]); mx01 = max_u16x2(mx01, c01[t]);
@@ -181,7 +192,7 @@ __device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, co
 // same ownership as the stream format, so per-channel statistics need no cross-lane step.
 // CONTIG: token rows are 128 elements apart (a contiguous (B, H, S, 128) tensor), so every load of a
 // round is the block pointer plus a constant
-template <typename T, bool CONTIG, int BITS>
+template <typename T, bool CONTIG, int BITS, bool ORDERED = false>
 __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(FusedArgs a) {
     constexpr bool HP = false;
     const int64_t ss = CONTIG ? 128 : a.ss;
@@ -225,9 +236,11 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
     const bool packable = __all_sync(0xffffffffu, q0.packable() && q1.packable() && q2.packable() && q3.packable());
     int pos;
     const bool half_ok = __all_sync(0xffffffffu, q0.half_domain() && q1.half_domain() && q2.half_domain() && q3.half_domain());
-    if (!HP && half_ok) pos = k_encode_rounds_packed<T, BITS, true>(x, ss, q0, q1, q2, q3, g, stage, lane, bad);
-    else if (!HP && packable) pos = k_encode_rounds_packed<T, BITS, false>(x, ss, q0, q1, q2, q3, g, stage, lane, bad);
-    else pos = k_encode_rounds<T, HP, BITS, false>(x, ss, q0, q1, q2, q3, g, stage, lane, bad);
+    // reordered blocks (order_block == cb here): the table of this block's rows
+    const uint8_t* ordp = ORDERED ? a.order + ((int64_t)b * nctx + cbi) * a.cb : nullptr;
+    if (!HP && half_ok) pos = k_encode_rounds_packed<T, BITS, true, ORDERED>(x, ss, ordp, q0, q1, q2, q3, g, stage, lane, bad);
+    else if (!HP && packable) pos = k_encode_rounds_packed<T, BITS, false, ORDERED>(x, ss, ordp, q0, q1, q2, q3, g, stage, lane, bad);
+    else pos = k_encode_rounds<T, HP, BITS, false, ORDERED>(x, ss, ordp, q0, q1, q2, q3, g, stage, lane, bad);
     __syncwarp();
     store_slot(a.slots + (int64_t)warp * a.slot_stride, stage, pos, lane);
     if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * a.heads + h) * 2 + 1] = (unsigned)pos;
@@ -253,7 +266,7 @@ __device__ __forceinline__ int v_swz(int ch) { return ((ch >> 1) ^ (ch >> 3)) & 
 // 4-token word per channel.  PACKED: two channels per instruction (all tokens packable()).
 // Returns the OR of all codes in 16-bit lanes for the range check.
 template <typename T, int CB, int MODE>     // MODE 0: scalar conversion, 1: two elements per instruction in fp32, 2: in the element type
-__device__ __forceinline__ unsigned v_quantise_tile(const T* src, int64_t ss, const float4* prm, uint8_t* tile, int lane) {
+__device__ __forceinline__ unsigned v_quantise_tile(const T* src, int64_t ss, const float4* prm, const uint8_t* ord, uint8_t* tile, int lane) {
     constexpr bool PACKED = MODE == 1;
     const uint4* prmh = reinterpret_cast<const uint4*>(prm + CB);   // per token: r, -128*scale, r/128 (element-type pairs), code bias
     const int r0 = lane >> 3, cg = lane & 7;
@@ -265,14 +278,14 @@ __device__ __forceinline__ unsigned v_quantise_tile(const T* src, int64_t ss, co
         wr[i] = tile + (8 * cg + 2 * i) * CB + 4 * r0;
         sw[i] = v_swz<CB>(8 * cg + 2 * i) << 4;           // channels 8cg + 2i and + 1 share the swizzle
     }
-    const T* lsrc = src + (int64_t)r0 * ss + 8 * cg;
+    const T* lsrc = src + 8 * cg;
 #pragma unroll 1
     for (int p = 0; p < CB / 16; p++) {
         unsigned c[4][4];                                  // [token k][channel pair i] as 16-bit lanes
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             const int tok = 16 * p + 4 * k + r0;
-            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(lsrc + (int64_t)(16 * p + 4 * k) * ss));
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(lsrc + (int64_t)ord[tok] * ss));
             const unsigned rw[4] = {raw.x, raw.y, raw.z, raw.w};
             if (MODE == 2) {
                 const uint4 ph = prmh[tok];
@@ -351,11 +364,12 @@ __device__ __forceinline__ void chunk_to_pack(const uint4& cw, int& len, uint64_
 // Per-token quantisation parameters of one token block over all heads and channels (the
 // reference's token mode reduces over dims [1, 4], utils/compute.py:405-410): half a warp per token.
 // Writes (scale, zero, 1/scale, packed code bias or 0) to prm[] and scale / zero to the caller's arrays.
-template <typename T, int CB>
-__device__ __forceinline__ bool token_params_pass(const FusedArgs& a, const T* xb, float4* prm, int b, int cbi, int lane, int wic) {
+// ord[t] = source row (inside the block) of stored row t; WRITE = false keeps the parameters in shared memory only.
+template <typename T, int CB, bool WRITE = true>
+__device__ __forceinline__ bool token_params_pass(const FusedArgs& a, const T* xb, float4* prm, const uint8_t* ord, int b, int cbi, int lane, int wic) {
     bool bad = false;
     for (int t = 2 * wic + (lane >> 4); t < CB; t += 16) {     // 8 channels per lane
-        const T* xt = xb + (int64_t)t * a.ss + 8 * (lane & 15);
+        const T* xt = xb + (int64_t)ord[t] * a.ss + 8 * (lane & 15);
         using T2 = typename QT<T>::T2;
         T2 lo2 = QT<T>::init2(INFINITY), hi2 = QT<T>::init2(-INFINITY);
 #pragma unroll 4
@@ -379,12 +393,29 @@ __device__ __forceinline__ bool token_params_pass(const FusedArgs& a, const T* x
             const HalfQuotient<T> hq(qz, qz);
             reinterpret_cast<uint4*>(prm + CB)[t] = make_uint4(*reinterpret_cast<const unsigned*>(&hq.r), *reinterpret_cast<const unsigned*>(&hq.nsp),
                                                                *reinterpret_cast<const unsigned*>(&hq.rp), qz.half_domain() ? hq.kab : 0u);
-            const int64_t pi = (int64_t)b * a.param_tokens + a.first_token + cbi * CB + t;
-            reinterpret_cast<T*>(a.scale)[pi] = QT<T>::cvt(qz.scale);
-            reinterpret_cast<T*>(a.zero)[pi] = QT<T>::cvt(qz.zero);
+            if (WRITE) {
+                const int64_t pi = (int64_t)b * a.param_tokens + a.first_token + cbi * CB + t;
+                reinterpret_cast<T*>(a.scale)[pi] = QT<T>::cvt(qz.scale);
+                reinterpret_cast<T*>(a.zero)[pi] = QT<T>::cvt(qz.zero);
+            }
         }
     }
     return bad;
+}
+
+// Source row (inside a block of CB tokens) of every stored row: the identity, or the caller's reorder of every
+// order_block tokens.  256 threads; ends with a CTA barrier.
+template <int CB>
+__device__ __forceinline__ void load_row_order(const FusedArgs& a, uint8_t* ord, int b, int cbi) {
+    for (int t = threadIdx.x; t < CB; t += 256) {
+        unsigned src = t;
+        if (a.order) {
+            const int ob = a.order_block, sub = t / ob;
+            src = sub * ob + a.order[((int64_t)b * (a.tokens / ob) + (int64_t)cbi * (CB / ob) + sub) * ob + (t - sub * ob)];
+        }
+        ord[t] = (uint8_t)src;
+    }
+    __syncthreads();
 }
 
 template <typename T, bool HP, int BITS, int CB>
@@ -402,9 +433,11 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
     uint8_t* ctile = wbase;                                  // [cb][64] codes
     uint8_t* stage = wbase + CB * 64;
     const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
+    uint8_t* ord = smem + 32 * CB + 8 * (CB * 64 + bound16);
+    load_row_order<CB>(a, ord, b, cbi);
 
     // pass 1: per-token statistics across every head and channel
-    bool bad = token_params_pass<T, CB>(a, xb, prm, b, cbi, lane, wic);
+    bool bad = token_params_pass<T, CB>(a, xb, prm, ord, b, cbi, lane, wic);
     // one decision for the whole CTA: the packed conversion needs every token's parameters in range
     __syncthreads();
     bool mine_ok = true, mine_half = true;
@@ -422,8 +455,8 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
         const int h = vb >> 1, half = vb & 1;
         const T* src = xb + (int64_t)h * a.sh + 64 * half;
         __syncwarp();
-        seen |= all_half ? v_quantise_tile<T, CB, 2>(src, a.ss, prm, ctile, lane)
-                         : all_packed ? v_quantise_tile<T, CB, 1>(src, a.ss, prm, ctile, lane) : v_quantise_tile<T, CB, 0>(src, a.ss, prm, ctile, lane);
+        seen |= all_half ? v_quantise_tile<T, CB, 2>(src, a.ss, prm, ord, ctile, lane)
+                         : all_packed ? v_quantise_tile<T, CB, 1>(src, a.ss, prm, ord, ctile, lane) : v_quantise_tile<T, CB, 0>(src, a.ss, prm, ord, ctile, lane);
         __syncwarp();
         int pos = g.head_bytes;
         unsigned seg_end = 0;
@@ -494,8 +527,10 @@ __global__ void __launch_bounds__(256, 2) kt_fused_encode_kernel(FusedArgs a) {
     uint8_t* ctile = wbase;                                  // two 64-channel halves of [64][CB] codes
     uint8_t* stage = wbase + CB * 128;
     const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
+    uint8_t* ord = smem + 32 * CB + 8 * (CB * 128 + bound16);
+    load_row_order<CB>(a, ord, b, cbi);
 
-    bool bad = token_params_pass<T, CB>(a, xb, prm, b, cbi, lane, wic);
+    bool bad = token_params_pass<T, CB>(a, xb, prm, ord, b, cbi, lane, wic);
     __syncthreads();
     bool mine_ok = true, mine_half = true;
     for (int t = threadIdx.x; t < CB; t += 256) {
@@ -511,9 +546,9 @@ __global__ void __launch_bounds__(256, 2) kt_fused_encode_kernel(FusedArgs a) {
         __syncwarp();
 #pragma unroll 1
         for (int half = 0; half < 2; half++)
-            seen |= all_half ? v_quantise_tile<T, CB, 2>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane)
-                             : all_packed ? v_quantise_tile<T, CB, 1>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane)
-                                          : v_quantise_tile<T, CB, 0>(src + 64 * half, a.ss, prm, ctile + half * 64 * CB, lane);
+            seen |= all_half ? v_quantise_tile<T, CB, 2>(src + 64 * half, a.ss, prm, ord, ctile + half * 64 * CB, lane)
+                             : all_packed ? v_quantise_tile<T, CB, 1>(src + 64 * half, a.ss, prm, ord, ctile + half * 64 * CB, lane)
+                                          : v_quantise_tile<T, CB, 0>(src + 64 * half, a.ss, prm, ord, ctile + half * 64 * CB, lane);
         __syncwarp();
         // this lane's four channel rows and their chunk swizzles
         const uint8_t* row[4];
@@ -563,6 +598,85 @@ __global__ void __launch_bounds__(256, 2) kt_fused_encode_kernel(FusedArgs a) {
     }
     bad = bad || (seen & ~(((1u << BITS) - 1u) * 0x00010001u)) != 0;
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
+}
+
+// ------------------------------------------------------------------------- order from values
+// Token order of one block of 64 tokens by descending lower median of the V codes (stable on ties), the
+// reference's median_repacking key (utils/compute.py:262-270), computed straight from fp16/bf16 V: per-token
+// parameters as in the encoder, the token's heads*128 codes in registers (half a warp per token, 8 heads at
+// most), then a binary search for the smallest m with count(code <= m) >= ceil(n / 2).  Same keys and the
+// same order as median_order_kernel on the code matrix.  grid (tokens / 64, batch), 256 threads.
+template <typename T>
+__global__ void __launch_bounds__(256) value_median_order_kernel(FusedArgs a, uint8_t* order) {
+    constexpr int CB = 64;
+    __shared__ float4 prm[2 * CB];
+    __shared__ uint8_t ident[CB];
+    __shared__ uint8_t key[CB];
+    const int lane = lane_id(), wic = threadIdx.x >> 5;
+    const int cbi = blockIdx.x, b = blockIdx.y;
+    if (threadIdx.x < CB) ident[threadIdx.x] = (uint8_t)threadIdx.x;
+    __syncthreads();
+    const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
+    token_params_pass<T, CB, false>(a, xb, prm, ident, b, cbi, lane, wic);
+    __syncthreads();
+    const int need = (a.heads * 128 + 1) / 2;
+    for (int t = 2 * wic + (lane >> 4); t < CB; t += 16) {
+        const float4 pr = prm[t];
+        Quantiser<T, false> qz;
+        qz.scale = pr.x; qz.zero = pr.y;
+        qz.prepare();
+        const int zi = (int)pr.y;
+        const T* xt = xb + (int64_t)t * a.ss + 8 * (lane & 15);
+        unsigned cw[16];
+#pragma unroll
+        for (int h = 0; h < 8; h++) {
+            cw[2 * h] = 0x7F7F7F7Fu; cw[2 * h + 1] = 0x7F7F7F7Fu;       // heads that do not exist count as large codes
+            if (h < a.heads) {
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xt + (int64_t)h * a.sh));
+                const unsigned rw[4] = {raw.x, raw.y, raw.z, raw.w};
+                unsigned c[8];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = QT<T>::to_float2(rw[i]);
+                    c[2 * i] = min(qz.fast ? qz.template code_u8<true>(f.x, zi) : qz.template code_u8<false>(f.x, zi), 127u);
+                    c[2 * i + 1] = min(qz.fast ? qz.template code_u8<true>(f.y, zi) : qz.template code_u8<false>(f.y, zi), 127u);
+                }
+                cw[2 * h] = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+                cw[2 * h + 1] = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+            }
+        }
+        // count(code <= m) over the token = n_slots - count(code > m); bit 7 of (code + 127 - m) is set iff code > m
+        auto count_le = [&](int m) {
+            unsigned over = 0;
+#pragma unroll
+            for (int i = 0; i < 16; i++) over += __popc((cw[i] + 0x01010101u * (unsigned)(127 - m)) & 0x80808080u);
+#pragma unroll
+            for (int s = 8; s > 0; s >>= 1) over += __shfl_xor_sync(0xffffffffu, over, s);
+            return 16 * 64 - (int)over;
+        };
+        int med = 16;                                  // codes above 15 are not expected (bits <= 4)
+        if (count_le(15) >= need) {
+            int lo = 0, hi = 15;                       // smallest m in [lo, hi] with count_le(m) >= need
+#pragma unroll
+            for (int step = 0; step < 4; step++) {
+                const int mid = (lo + hi) >> 1;
+                if (count_le(mid) >= need) hi = mid; else lo = mid + 1;
+            }
+            med = hi;
+        }
+        if ((lane & 15) == 0) key[t] = (uint8_t)med;
+    }
+    __syncthreads();
+    const int i = threadIdx.x;
+    if (i < CB) {
+        const int ki = key[i];
+        int rank = 0;
+        for (int j = 0; j < CB; j++) {
+            const int kj = key[j];
+            rank += (kj > ki) || (kj == ki && j < i);
+        }
+        order[((int64_t)b * (a.tokens / CB) + cbi) * CB + rank] = (uint8_t)i;
+    }
 }
 
 // ------------------------------------------------------------------------------------ compact
@@ -629,8 +743,9 @@ int64_t fused_encode_scratch_bytes(const FusedEncodeRequest& r) {
 }
 
 template <typename T, bool HP, int BITS>
-static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStream_t st) {
+static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, const uint8_t* order, int order_block, cudaStream_t st) {
     FusedArgs a{};
+    a.order = order; a.order_block = order_block;
     a.x = r.x; a.sb = r.stride_b; a.sh = r.stride_h; a.ss = r.stride_s;
     a.scale = r.scale; a.zero = r.zero;
     a.param_blocks = r.param_blocks; a.first_block = r.first_token / r.cb;
@@ -649,7 +764,7 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
         const int smem = kWarpsPerCta * bound16;
         const unsigned grid = (unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta);
         if (r.mode == 1) {                       // per-token parameters: CTA per (sequence, token block)
-            const int smem_t = 32 * r.cb + 8 * (r.cb * 128 + bound16);
+            const int smem_t = 32 * r.cb + 8 * (r.cb * 128 + bound16) + r.cb;
             auto launch_kt = [&](auto kern) {
                 if (opt_in_smem(kern, smem_t)) return (int)kCudaError;
                 kern<<<dim3(nctx, r.batch), 256, smem_t, st>>>(a);
@@ -660,6 +775,10 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
             else if (r.cb == 64) rc = launch_kt(kt_fused_encode_kernel<T, BITS, 64>);
             else rc = launch_kt(kt_fused_encode_kernel<T, BITS, 128>);
             if (rc != kOk) return rc;
+        } else if (a.order) {
+            auto kern = k_fused_encode_kernel<T, false, BITS, true>;
+            if (opt_in_smem(kern, smem)) return kCudaError;
+            kern<<<grid, kWarpsPerCta * 32, smem, st>>>(a);
         } else if (r.stride_s == 128) {
             auto kern = k_fused_encode_kernel<T, true, BITS>;
             if (opt_in_smem(kern, smem)) return kCudaError;
@@ -674,7 +793,7 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
         bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * g.ppt * 2 * BITS) + 15) & ~15;
         a.slot_stride = bound16;
         blocks_per_seq = nctx * 2 * r.heads;
-        const int smem = 32 * r.cb + 8 * (r.cb * 64 + bound16);
+        const int smem = 32 * r.cb + 8 * (r.cb * 64 + bound16) + r.cb;
         auto launch_v = [&](auto kern) {
             if (opt_in_smem(kern, smem)) return (int)kCudaError;
             kern<<<dim3(nctx, r.batch), 256, smem, st>>>(a);
@@ -701,21 +820,41 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, cudaStrea
 }
 
 template <typename T, bool HP>
-static int launch_fused_b(const FusedEncodeRequest& r, uint8_t* slots, cudaStream_t st) {
+static int launch_fused_b(const FusedEncodeRequest& r, uint8_t* slots, const uint8_t* order, int order_block, cudaStream_t st) {
     switch (r.bits) {
-        case 2: return launch_fused_t<T, HP, 2>(r, slots, st);
-        case 3: return launch_fused_t<T, HP, 3>(r, slots, st);
-        case 4: return launch_fused_t<T, HP, 4>(r, slots, st);
+        case 2: return launch_fused_t<T, HP, 2>(r, slots, order, order_block, st);
+        case 3: return launch_fused_t<T, HP, 3>(r, slots, order, order_block, st);
+        case 4: return launch_fused_t<T, HP, 4>(r, slots, order, order_block, st);
     }
     return kUnsupported;
 }
 
-int launch_fused_encode(const FusedEncodeRequest& r, uint8_t* slots, cudaStream_t st) {
+int launch_fused_encode(const FusedEncodeRequest& r, uint8_t* slots, const uint8_t* order, int order_block, cudaStream_t st) {
     if (!fused_encode_applicable(r)) return kUnsupported;
+    if (order) {
+        // a reorder block must be a whole number of 16-token packs, fit a byte index, divide the stream block
+        // and, for K with per-channel parameters, be the stream block itself
+        if (order_block < 16 || order_block > 128 || order_block % 16 || r.cb % order_block || r.first_token % order_block) return kUnsupported;
+        if (r.which == 0 && r.mode == 0 && order_block != r.cb) return kUnsupported;
+        if (reinterpret_cast<uintptr_t>(order) & 15) return kBadArgument;
+    }
     if ((int64_t)r.batch * r.tokens == 0) return kOk;
     if (!r.x || !r.scale || !r.zero || !r.stream || !r.block_info || !r.stream_bytes || !r.flags || !slots) return kBadArgument;
     if ((reinterpret_cast<uintptr_t>(slots) & 15) || (reinterpret_cast<uintptr_t>(r.stream) & 1) || (r.stream_seq_stride & 1)) return kBadArgument;
-    return r.is_bf16 ? launch_fused_b<__nv_bfloat16, false>(r, slots, st) : launch_fused_b<__half, false>(r, slots, st);
+    return r.is_bf16 ? launch_fused_b<__nv_bfloat16, false>(r, slots, order, order_block, st) : launch_fused_b<__half, false>(r, slots, order, order_block, st);
+}
+
+int launch_value_median_order(const FusedEncodeRequest& r, uint8_t* order, int block, cudaStream_t st) {
+    if (block != 64 || r.heads < 1 || r.heads > 8 || r.tokens % 64 || r.high_precision_zero) return kUnsupported;
+    if (r.batch < 0 || r.tokens < 0) return kBadArgument;
+    if ((int64_t)r.batch * r.tokens == 0) return kOk;
+    if (!r.x || !order || (reinterpret_cast<uintptr_t>(r.x) & 15) || (r.stride_b & 7) || (r.stride_h & 7) || (r.stride_s & 7)) return kBadArgument;
+    FusedArgs a{};
+    a.x = r.x; a.sb = r.stride_b; a.sh = r.stride_h; a.ss = r.stride_s;
+    a.batch = r.batch; a.heads = r.heads; a.tokens = r.tokens; a.cb = 64; a.rel = r.rel; a.flags = r.flags;
+    if (r.is_bf16) value_median_order_kernel<__nv_bfloat16><<<dim3(r.tokens / 64, r.batch), 256, 0, st>>>(a, order);
+    else value_median_order_kernel<__half><<<dim3(r.tokens / 64, r.batch), 256, 0, st>>>(a, order);
+    return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
 }
 
 }  // namespace pkv

@@ -100,7 +100,10 @@ int launch_quantize(const QuantArgs& q, cudaStream_t st);
 using FusedEncodeRequest = pkv_encode_args;
 bool fused_encode_applicable(const FusedEncodeRequest& r);
 int64_t fused_encode_scratch_bytes(const FusedEncodeRequest& r);
-int launch_fused_encode(const FusedEncodeRequest& r, uint8_t* slots, cudaStream_t st);
+// order (optional): (batch, tokens / order_block, order_block) uint8, source row of every stored row of a reorder block
+int launch_fused_encode(const FusedEncodeRequest& r, uint8_t* slots, const uint8_t* order, int order_block, cudaStream_t st);
+// token order of every `block` tokens by descending lower median of the V codes, straight from fp16/bf16 V
+int launch_value_median_order(const FusedEncodeRequest& r, uint8_t* order, int block, cudaStream_t st);
 int launch_scan_sizes(const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
 int launch_encode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);
 int launch_decode(bool is_k, const CodecShape& sh, const CodecBuffers& b, cudaStream_t st);

@@ -60,6 +60,22 @@ def compress_kv(k: torch.Tensor, v: torch.Tensor, *, block: int, bits_k: int, bi
     k_info = torch.empty(B, (cap_tok // cbk) * H, 2, dtype=torch.int32, device=dev)
     v_info = torch.empty(B, (cap_tok // cbv) * 2 * H, 2, dtype=torch.int32, device=dev)
     k_bytes, v_bytes = zeros[:B], zeros[B:2 * B]
+    fused_median = (repack_method == RepackMethod.MEDIAN and not high_precision_zero and block == 64 and H <= 8 and cbv % 64 == 0
+                    and (cbk == block if km == ops.K_CHANNEL else cbk % 64 == 0)
+                    and k.stride(3) == 1 and v.stride(3) == 1 and all(t.stride(i) % 8 == 0 for t in (k, v) for i in range(3)))
+    if fused_median:
+        # the order straight from V, then the single-pass encoder reads K and V rows through it: no code matrix in HBM
+        order = ops.value_median_order(v, block, v_rel, flags=flags)
+        scratch = torch.empty(max(16, B * S * H * D), dtype=torch.uint8, device=dev)
+        ops.encode_tensor("k", k, block, k_rel, km, bits_k, cbk, scale=k_scale, zero=k_zero, stream=k_stream, info=k_info,
+                          stream_bytes=k_bytes, flags=flags, scratch=scratch, order=order, order_block=block)
+        ops.encode_tensor("v", v, block, v_rel, ops.K_TOKEN, bits_v, cbv, scale=v_scale, zero=v_zero, stream=v_stream, info=v_info,
+                          stream_bytes=v_bytes, flags=flags, scratch=scratch, order=order, order_block=block)
+        return ops.CompressedLayer(
+            k_stream=k_stream, k_info=k_info, k_bytes=k_bytes, k_scale=k_scale, k_zero=k_zero,
+            v_stream=v_stream, v_info=v_info, v_bytes=v_bytes, v_scale=v_scale, v_zero=v_zero,
+            n_comp=S, kv_heads=H, cbk=cbk, cbv=cbv, bits_k=bits_k, bits_v=bits_v, k_mode=km,
+            high_precision_zero=high_precision_zero, order=order)
     if repack_method in (RepackMethod.MEDIAN, RepackMethod.GREEDY):
         kq = ops.quantize(k, block, k_rel, km, bits=bits_k, high_precision_zero=high_precision_zero, flags=flags,
                           scale=k_scale, zero=k_zero)

@@ -229,13 +229,16 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
                      v_res: Optional[torch.Tensor], n_res: int, *, scaling: Optional[float] = None,
                      out: Optional[torch.Tensor] = None,
                      flags: Optional[torch.Tensor] = None, kv_heads: Optional[int] = None,
-                     exchange: Optional["_lib.AttnExchange"] = None) -> torch.Tensor:
+                     exchange: Optional["_lib.AttnExchange"] = None, append: Optional[tuple] = None) -> torch.Tensor:
     """softmax(q K^T * scaling) V for one query token per sequence.
 
     q: (B, Hq, 128) fp16/bf16 (post-RoPE).  `layer` holds the compressed tokens, k_res/v_res
     (B, Hkv, R_cap, 128) the uncompressed residual whose first n_res tokens are valid.
     Returns out (B, Hq, 128) in q's dtype; asynchronous on the current stream.  `exchange` (KV-head-sharded
     decode on several GPUs, see parallel.HeadExchange) makes the launch also deliver the rows to every rank.
+    `append` = (k_new, v_new, cos, sin) with k_new / v_new (B, Hkv, 1, 128) and cos / sin (B or 1, 1, 128) or None:
+    the launch writes the step's new token (K rotated like rope()) into residual row n_res - 1 before attending;
+    n_res counts that token.
     """
     _require_cuda(q, k_res, v_res, out, flags)
     if q.dim() != 3 or q.shape[2] != 128 or not q.is_contiguous():
@@ -285,7 +288,24 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
     a.is_bf16 = int(q.dtype == torch.bfloat16)
     a.scaling = float(D ** -0.5 if scaling is None else scaling)
     a.flags = flags.data_ptr()
-    if exchange is None:
+    if append is not None:
+        k_new, v_new, cos, sin = append
+        _require_cuda(k_new, v_new, cos, sin)
+        if n_res < 1 or k_new.shape != (B, kv_heads, 1, 128) or v_new.shape != k_new.shape or k_new.stride(3) != 1 or v_new.stride(3) != 1 \
+                or k_new.dtype != q.dtype or v_new.dtype != q.dtype:
+            raise ValueError("append needs k_new / v_new of shape (B, Hkv, 1, 128) in q's dtype with contiguous channels")
+        ap = _lib.AttnAppend()
+        ap.new_k, ap.new_v = k_new.data_ptr(), v_new.data_ptr()
+        ap.k_stride_b, ap.k_stride_h, ap.v_stride_b, ap.v_stride_h = k_new.stride(0), k_new.stride(1), v_new.stride(0), v_new.stride(1)
+        if cos is not None:
+            if cos.dtype != q.dtype or sin.dtype != q.dtype or cos.shape[-2:] != (1, 128) or sin.shape != cos.shape or not cos.is_contiguous() \
+                    or not sin.is_contiguous():
+                raise ValueError("cos / sin must be contiguous (B or 1, 1, 128) tensors of q's dtype")
+            ap.cos, ap.sin, ap.cs_stride_b = cos.data_ptr(), sin.data_ptr(), (0 if cos.shape[0] == 1 else 128)
+        ap.res_capacity = k_res.shape[2]
+        st = _lib.lib().pkv_decode_attention_append(ctypes.byref(a), ctypes.byref(ap), ctypes.byref(exchange) if exchange is not None else None,
+                                                    _stream_ptr())
+    elif exchange is None:
         st = _lib.lib().pkv_decode_attention(ctypes.byref(a), _stream_ptr())
     else:
         st = _lib.lib().pkv_decode_attention_exchange(ctypes.byref(a), ctypes.byref(exchange), _stream_ptr())
@@ -382,10 +402,13 @@ def _encode_args(which: str, x, block, rel, mode, bits, hp, cb, scale, zero, str
 def encode_tensor(which: str, x: torch.Tensor, block: int, rel: float, mode: int, bits: int, cb: int, *,
                   scale: torch.Tensor, zero: torch.Tensor, stream: torch.Tensor, info: torch.Tensor,
                   stream_bytes: torch.Tensor, flags: torch.Tensor, first_token: int = 0,
-                  high_precision_zero: bool = False, scratch: Optional[torch.Tensor] = None) -> None:
+                  high_precision_zero: bool = False, scratch: Optional[torch.Tensor] = None,
+                  order: Optional[torch.Tensor] = None, order_block: int = 64) -> None:
     """Quantises x (B, H, S, 128) and packs it behind the `first_token` tokens already in the
     streams (one C call).  `scratch` (uint8, >= B*S*H*128 bytes) holds the codes in between; one is
-    allocated when not given."""
+    allocated when not given.  `order` (B, S/order_block, order_block) uint8 (value_median_order): rows are read
+    through it, i.e. the tokens of every reorder block are stored in that order (single-pass modes only:
+    RuntimeError("not supported") otherwise)."""
     _require_cuda(x, scale, zero, stream, info, stream_bytes, flags, scratch)
     if x.dim() != 4 or x.shape[3] != 128 or x.stride(3) != 1 or x.dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("x must be (B, H, S, 128) fp16/bf16 with contiguous channels")
@@ -396,8 +419,35 @@ def encode_tensor(which: str, x: torch.Tensor, block: int, rel: float, mode: int
     if scratch is None:
         scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
     a = _encode_args(which, x, block, rel, mode, bits, high_precision_zero, cb, scale, zero, stream, info, stream_bytes, flags, first_token)
-    st = _lib.lib().pkv_encode_tensor(ctypes.byref(a), scratch.data_ptr(), scratch.numel(), _stream_ptr())
+    if order is not None:
+        _require_cuda(order)
+        if order.dtype != torch.uint8 or not order.is_contiguous() or order.numel() != B * S:
+            raise ValueError("order must be a contiguous uint8 tensor with one entry per token")
+        st = _lib.lib().pkv_encode_tensor_ordered(ctypes.byref(a), order.data_ptr(), order_block, scratch.data_ptr(), scratch.numel(), _stream_ptr())
+    else:
+        st = _lib.lib().pkv_encode_tensor(ctypes.byref(a), scratch.data_ptr(), scratch.numel(), _stream_ptr())
     _lib.check(st, f"encode_tensor({which})")
+
+
+def value_median_order(v: torch.Tensor, block: int, rel: float, flags: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Token order of every block by descending lower median of the V codes (stable on ties), computed from
+    fp16/bf16 V (B, H <= 8, S, 128) without a code matrix: the same order as median_order on quantised codes.
+    Returns (B, S/block, block) uint8."""
+    _require_cuda(v, flags)
+    if v.dim() != 4 or v.shape[3] != 128 or v.stride(3) != 1 or v.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("v must be (B, H, S, 128) fp16/bf16 with contiguous channels")
+    B, H, S, _ = v.shape
+    if S % block:
+        raise ValueError("Tensor shape is not divisible by block size")
+    order = torch.empty(B, S // block, block, dtype=torch.uint8, device=v.device)
+    a = _lib.EncodeArgs()
+    a.x, a.stride_b, a.stride_h, a.stride_s = v.data_ptr(), v.stride(0), v.stride(1), v.stride(2)
+    a.batch, a.heads, a.tokens, a.which, a.mode = B, H, S, 1, K_TOKEN
+    a.is_bf16, a.rel = int(v.dtype == torch.bfloat16), float(rel)
+    a.flags = (flags if flags is not None else new_flags(v.device)).data_ptr()
+    st = _lib.lib().pkv_value_median_order(ctypes.byref(a), order.data_ptr(), block, _stream_ptr())
+    _lib.check(st, "value_median_order")
+    return order
 
 
 def encode_tensor_static(which: str, x: torch.Tensor, block: int, rel: float, mode: int, bits: int, cb: int, *,

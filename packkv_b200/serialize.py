@@ -117,6 +117,7 @@ def dumps_cache(cache) -> bytes:
     """Every layer of a PackKVCache: compressed store + uncompressed residual + lengths."""
     arrays: Dict[str, torch.Tensor] = {}
     layers: List[Optional[dict]] = []
+    cache.flush()                      # a decode step's token that no attend() has written yet
     for i, L in enumerate(cache._layers):
         entry = {"n_res": int(L.n_res), "n_comp": int(L.n_comp), "layer": None}
         if L.k_res is not None:

@@ -126,6 +126,50 @@ def test_head_dim_below_128_matches_reference_cache(cuda_device, method, head_di
         C.PackKVCacheConfigStatic.config = None
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_decode_step_append_inside_the_attention_launch(cuda_device, dtype):
+    """A decode step without materialised K/V: update() only records the new token, attend() lets the attention
+    launch rotate K, write both rows into the residual and attend over them.  The residual rows must equal the
+    ones pkv_append_residual writes (bit for bit, same RoPE arithmetic), the attention output the reference's
+    within 2e-3, and an update() that is not followed by attend() must still land in the residual."""
+    dev = cuda_device
+    B, H, G, S0, steps = 2, 2, 4, 300, 40
+    cfg = _cfg(QuantMethod.KIVI)
+    C.PackKVCacheConfigStatic.config = cfg
+    try:
+        fused, plain = C.PackKVCache(B, H * G, 128, 1), C.PackKVCache(B, H * G, 128, 1, materialize=True)
+        oracle = Q.CacheLayerOracle(64, 192, cfg.k_quant_scale_rel, cfg.v_quant_scale_rel, "channel", "token")
+        k, v = synth.synth_kv(B, H, S0 + steps, 128, seed=51, dtype=dtype)
+        cos, sin = synth.rope_tables(S0 + steps, 128, dtype=dtype)
+        kw = lambda a, b: {"cos": cos[:, a:b].to(dev), "sin": sin[:, a:b].to(dev)}
+        Ko, Vo = oracle.update(k[:, :, :S0], v[:, :, :S0], cos[:, :S0], sin[:, :S0])
+        for c in (fused, plain):
+            c.update(k[:, :, :S0].to(dev), v[:, :, :S0].to(dev), 0, kw(0, S0))
+        for t in range(S0, S0 + steps):
+            Ko, Vo = oracle.update(k[:, :, t:t + 1], v[:, :, t:t + 1], cos[:, t:t + 1], sin[:, t:t + 1])
+            n_comp_before = fused._layers[0].n_comp
+            for c in (fused, plain):
+                c.update(k[:, :, t:t + 1].to(dev), v[:, :, t:t + 1].to(dev), 0, kw(t, t + 1))
+            if t % 3 == 0:
+                continue                                             # no attend(): the next update() must flush the token
+            # a step that moved a block out of the residual went through the ordinary path; every other step defers
+            assert (fused._layers[0].pending is not None) == (fused._layers[0].n_comp == n_comp_before)
+            q = synth.synth_q(B, H * G, 128, seed=t, dtype=dtype)
+            out = fused.attend(q.to(dev), 0).float().cpu()
+            assert fused._layers[0].pending is None
+            ref = Q.eager_attention(q, Ko, Vo).float()
+            assert ((out - ref).abs().max() / ref.abs().max()).item() <= 2e-3, t
+            Lf, Lp = fused._layers[0], plain._layers[0]
+            assert Lf.n_res == Lp.n_res
+            assert torch.equal(Lf.k_res[:, :, : Lf.n_res], Lp.k_res[:, :, : Lp.n_res]), t
+            assert torch.equal(Lf.v_res[:, :, : Lf.n_res], Lp.v_res[:, :, : Lp.n_res]), t
+        Kd, Vd = fused.dense(0)
+        assert torch.equal(Kd.cpu(), Ko) and torch.equal(Vd.cpu(), Vo)
+        fused.check_flags()
+    finally:
+        C.PackKVCacheConfigStatic.config = None
+
+
 def test_append_streams_equal_one_shot_encode(cuda_device):
     """Blocks appended one at a time give the same bytes as encoding the history in one call."""
     from packkv_b200 import encode, ops

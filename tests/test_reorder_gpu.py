@@ -89,6 +89,28 @@ def test_reordered_streams_and_attention(cuda_device, k_mode):
     assert ((o1 - o2).abs().max() / o1.abs().max()).item() <= 2e-3
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("heads", [2, 8])
+def test_order_from_values_equals_order_from_codes(cuda_device, dtype, heads):
+    """The single-pass encoder takes its token order from a kernel that never writes codes to memory: it must
+    give exactly the order that median_order gives on the quantiser's code matrix (same keys, same stable ties),
+    and the per-token parameters of the reordered layer must be the plain layer's, moved with their tokens."""
+    dev = cuda_device
+    B, S = 3, 320
+    k, v = synth.synth_kv(B, heads, S, 128, seed=23, dtype=dtype, device=dev, apply_rope=True)
+    vq = ops.quantize(v, 64, 1 / 14, ops.K_TOKEN, bits=4)
+    want = ops.median_order(vq.codes, heads, 64)
+    got = ops.value_median_order(v, 64, 1 / 14)
+    assert torch.equal(got, want)
+    args = dict(block=64, bits_k=4, bits_v=4, k_rel=1 / 14, v_rel=1 / 14, k_mode=QuantMode.TokenQuant)
+    plain = encode.compress_kv(k, v, **args)
+    re = encode.compress_kv(k, v, repack_method=RepackMethod.MEDIAN, **args)
+    assert torch.equal(re.order, want)
+    idx = (want.to(torch.int64) + torch.arange(S // 64, device=dev).view(1, -1, 1) * 64).reshape(B, S)
+    for name in ("v_scale", "v_zero", "k_scale", "k_zero"):
+        assert torch.equal(getattr(re, name)[:, :S], torch.gather(getattr(plain, name)[:, :S], 1, idx)), name
+
+
 def _feature_blocks(kcodes, vcodes, block):
     """(S, hidden) K and V codes of one sequence -> (n_blocks, block, 2*hidden) like compute.py:336-338."""
     S = kcodes.shape[0]
