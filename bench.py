@@ -57,7 +57,7 @@ MIN_TIMED_S = 1.0   # the timed region is repeated until it is at least this lon
 # captures summarised under profiles/.  An entry is valid for one revision of the kernel only (the revision is
 # a constant of packkv_b200.ops that changes with the kernel): other revisions report null.
 NCU_TRAFFIC_BYTES = {
-    ("attn", 2, 16, 8192, 8, 4, 4, 64, 128): None,
+    ("attn", 2, 16, 8192, 8, 4, 4, 64, 128): 161.3e6,      # profiles/attn_decode_kernel_llama8b.md
     ("encode", 1, 16, 4, 64): 1836e6,
 }
 
