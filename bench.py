@@ -194,14 +194,21 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
     alg_bytes = sum(layer_bytes(L, kr, vr, n_res, B, Hq) for L, kr, vr in layers)
     xchg = parallel.HeadExchange(B, Hq, world, dtype, device, mode=exchange, rank=rank, kv_heads_local=w["kv_heads"] // world,
                                  flags=flags) if by_heads else None
+    # scratch of the two-launch form (several clusters per (sequence, KV head)): the library uses it when the
+    # launch has too few pairs to fill the GPU; w["plan"] forces (cluster, nsplit, launches)
+    scratch = ops.new_attention_scratch(device, 64 << 20) if w.get("split", True) else None
+    plan = w.get("plan")
+    L0, kr0, vr0 = layers[0]
+    used = ops.decode_attention(q_dev[0], L0, kr0, vr0, n_res, flags=flags, scratch=scratch, plan=plan, plan_only=True)
 
     def step_resident():
         for (L, kr, vr), q, o in zip(layers, q_dev, out_dev):
-            ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags, exchange=xchg.begin() if by_heads else None)
+            ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags, exchange=xchg.begin() if by_heads else None, scratch=scratch, plan=plan)
             if by_heads:
                 xchg.gather(o)
 
-    res = {"n_comp": n_comp, "n_res": n_res, "layers": len(layers), "batch": B, "q_heads_local": Hq, "alg_bytes": alg_bytes}
+    res = {"n_comp": n_comp, "n_res": n_res, "layers": len(layers), "batch": B, "q_heads_local": Hq, "alg_bytes": alg_bytes,
+           "plan": {"cluster": used[0], "clusters_per_pair": used[1], "launches": used[2]}}
     for _ in range(max(warmup, 3)):
         step_resident()
     sampler = None
@@ -218,10 +225,11 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
         # the kernels alone (every rank its own heads, nothing exchanged): the difference is what the exchange costs
         def step_local():
             for (L, kr, vr), q, o in zip(layers, q_dev, out_dev):
-                ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags)
+                ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags, scratch=scratch, plan=plan)
         ms_l, _, _ = timed_batches(step_local, steps, world, device, min_seconds=0.3)
         res["exchange_ms_per_step"] = max(0.0, ms / steps - ms_l / steps)
-        res["check"] = parallel.check_against_full(w, rank, world, device, dtype, layers[0], q_full[0], n_comp, n_res, xchg, flags)
+        res["check"] = parallel.check_against_full(w, rank, world, device, dtype, layers[0], q_full[0], n_comp, n_res, xchg, flags, scratch=scratch,
+                                                      plan=plan)
 
     if with_e2e:
         # End to end: every layer's q comes from pinned host memory and every layer's output goes back to
@@ -251,7 +259,7 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
                 if i + 1 < len(layers):
                     upload(i + 1)
                 main.wait_event(ev_in[i % 2])
-                ops.decode_attention(q_stage[i % 2], L, kr, vr, n_res, out=o, flags=flags, exchange=xchg.begin() if by_heads else None)
+                ops.decode_attention(q_stage[i % 2], L, kr, vr, n_res, out=o, flags=flags, exchange=xchg.begin() if by_heads else None, scratch=scratch, plan=plan)
                 ev_free[i % 2].record(main)
                 if by_heads:
                     xchg.gather(o)
@@ -642,6 +650,24 @@ def main():
                 line["v_block_64"] = {"us_per_layer": us, "tok_s_at_32_layers": w["batch"] * world / (us * 1e-6 * 32), "compressed_kv_gbs": gbs,
                                       "roofline_frac": gbs / peak, "layers_timed": m["layers"]}
             torch.cuda.empty_cache()
+            # one sequence at long contexts (the regime of the reference's own throughput scripts): few (sequence, KV
+            # head) pairs, so the library splits each pair over several clusters in two launches; beside it the
+            # single launch (one cluster of at most 16 CTAs per pair)
+            low = {}
+            for ctx in (32768, 131072):
+                wl = dict(w, batch=1, ctx=ctx, layers=4)
+                ms_ = time_decode(wl, args.steps, args.warmup, rank, world, device, with_e2e=False, sample_clocks=False)
+                mo_ = time_decode(dict(wl, split=False), args.steps, args.warmup, rank, world, device, with_e2e=False, sample_clocks=False)
+                if rank == 0:
+                    peak, _ = measured_peak_gbs()
+                    us = ms_["ms_per_step"] / ms_["layers"] * 1e3
+                    gbs = ms_["alg_bytes"] / ms_["layers"] / (us * 1e-6) / 1e9
+                    low[f"batch1_ctx{ctx}"] = {"us_per_layer": us, "tok_s_at_32_layers": world / (us * 1e-6 * 32), "compressed_kv_gbs": gbs,
+                                               "roofline_frac": gbs / peak, "plan": ms_["plan"],
+                                               "single_launch_us_per_layer": mo_["ms_per_step"] / mo_["layers"] * 1e3, "layers_timed": ms_["layers"]}
+                torch.cuda.empty_cache()
+            if rank == 0:
+                line["low_batch"] = low
             leg = encode_leg(args.steps, args.warmup, rank, world, device)
             if rank == 0:
                 line["encode"] = leg

@@ -356,6 +356,32 @@ int32_t pkv_decode_attention_append(const pkv_attn_args* args_host, const pkv_at
                                     const pkv_attn_exchange* exchange_host, void* cuda_stream);
 
 /*
+ * Decode attention with a work split the caller can see and steer, for launches with few (sequence, KV head)
+ * pairs (batch 1-2 at long contexts, the regime of scripts/rebuttal_throughout.py:28-37, or KV heads sharded
+ * over many GPUs), where one cluster of at most 16 CTAs per pair leaves most of the GPU idle.  With `scratch`
+ * the library may run the step as TWO launches with `nsplit` clusters per pair: the first computes the scores
+ * of all tokens (K phase) and leaves them, with every CTA's maximum and sum, in the scratch; the second
+ * normalises with the global maximum and sum, rounds the probabilities, contracts V, and the pair's last
+ * cluster to finish adds the clusters' rows in a fixed order.  Rounding points are those of the single launch.
+ *   plan_io   in: cluster (CTAs per cluster, 1..16), nsplit (clusters per pair), launches (1 or 2) to force,
+ *             0 = let the library choose; out: what was used.  May be NULL.  Two launches of the same tensors with
+ *             the same cluster * nsplit give bit-identical results whatever the batch and head counts.
+ *   scratch   device memory, 256-byte aligned, ZERO before its first use (the library leaves its counters at
+ *             zero after every call); launches that share it must be ordered on one stream.  NULL: single launch.
+ * pkv_attention_plan fills plan_io the same way and launches nothing (scratch_bytes alone decides what fits).
+ * append_host and exchange_host may be NULL.
+ */
+typedef struct pkv_attn_plan {
+    int32_t cluster;
+    int32_t nsplit;
+    int32_t launches;
+} pkv_attn_plan;
+int32_t pkv_decode_attention_split(const pkv_attn_args* args_host, const pkv_attn_append* append_host,
+                                   const pkv_attn_exchange* exchange_host, pkv_attn_plan* plan_io,
+                                   void* scratch, int64_t scratch_bytes, void* cuda_stream);
+int32_t pkv_attention_plan(const pkv_attn_args* args_host, pkv_attn_plan* plan_io, int64_t scratch_bytes);
+
+/*
  * Set-up helpers of the exchange; the only entry points that allocate or touch address-space mappings (they
  * synchronise, call them once, outside the decode loop).  pkv_exchange_alloc returns `bytes` of zeroed device
  * memory on the current device (its own cudaMalloc, so that it can be exported) and the 64-byte

@@ -49,6 +49,11 @@ class AttnAppend(ctypes.Structure):
                 ("cos", _p), ("sin", _p), ("cs_stride_b", _i64), ("res_capacity", _i32)]
 
 
+class AttnPlan(ctypes.Structure):
+    """Mirror of pkv_attn_plan (include/packkv_sm100.h)."""
+    _fields_ = [("cluster", _i32), ("nsplit", _i32), ("launches", _i32)]
+
+
 class EncodeArgs(ctypes.Structure):
     """Mirror of pkv_encode_args (include/packkv_sm100.h)."""
     _fields_ = [
@@ -82,6 +87,9 @@ SIGNATURES = {
     "pkv_decode_attention": (_i32, [ctypes.POINTER(AttnArgs), _p]),
     "pkv_decode_attention_exchange": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnExchange), _p]),
     "pkv_decode_attention_append": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnAppend), ctypes.POINTER(AttnExchange), _p]),
+    "pkv_decode_attention_split": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnAppend), ctypes.POINTER(AttnExchange), ctypes.POINTER(AttnPlan),
+                                          _p, _i64, _p]),
+    "pkv_attention_plan": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnPlan), _i64]),
     "pkv_exchange_wait": (_i32, [_p, _i32, ctypes.c_uint32, ctypes.c_uint32, _p, _p]),
     "pkv_exchange_alloc": (_i32, [_i64, ctypes.POINTER(ctypes.c_void_p), _p]),
     "pkv_exchange_free": (_i32, [_p]),

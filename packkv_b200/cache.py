@@ -89,6 +89,7 @@ class PackKVCache(_HFCache):
         self.decode_handles = decode_handles
         self._layers: List[_Layer] = [_Layer() for _ in range(layer_num)]
         self.flags: Optional[torch.Tensor] = None
+        self._scratch: Optional[torch.Tensor] = None   # hand-over area of the attention's two-launch form
 
     # ---------------------------------------------------------------------------------------------
     @staticmethod
@@ -325,8 +326,12 @@ class PackKVCache(_HFCache):
         q = q.contiguous()
         kv_heads = L.comp.kv_heads if L.comp is not None else L.k_res.shape[1]
         pending, L.pending = L.pending, None
+        if self._scratch is None and B * kv_heads <= 64:
+            # few (sequence, KV head) pairs: let the library split each over several clusters (all layers share the
+            # area: their launches are ordered on one stream)
+            self._scratch = ops.new_attention_scratch(q.device)
         out = ops.decode_attention(q, L.comp if L.n_comp else None, L.k_res, L.v_res, L.n_res, scaling=scaling,
-                                   flags=self.flags, kv_heads=kv_heads, append=pending)
+                                   flags=self.flags, kv_heads=kv_heads, append=pending, scratch=self._scratch)
         return out.view(B, 1, Hq, 128)[..., :D]
 
     def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:

@@ -52,13 +52,19 @@ constexpr int kAW = 4;            // warps per CTA
 constexpr int kMaxCtasPerSm = PKV_ATTN_CTAS;  // register budget: 65536 / (128 * 4) -> 128 per thread, 96 for 5
 constexpr int kD = 128;           // head dimension
 constexpr int kSmCount = 148;
-constexpr unsigned kWaitSpins = 1u << 22;
+constexpr unsigned kWaitSpins = 1u << 22;   // bounded mbarrier wait (each try suspends for a while by itself)
+#ifndef PKV_ATTN_CTAS_SCORES
+#define PKV_ATTN_CTAS_SCORES PKV_ATTN_CTAS   // the two-launch form's kernels may take other register budgets
+#endif
+#ifndef PKV_ATTN_CTAS_VALUES
+#define PKV_ATTN_CTAS_VALUES PKV_ATTN_CTAS
+#endif
 #ifndef PKV_ONE_CHAIN
 #define PKV_ONE_CHAIN 0
 #endif
 #ifndef PKV_ABL
 #define PKV_ABL 0
-#endif   // bounded mbarrier wait (each try suspends for a while by itself)
+#endif
 
 // ---- element-type traits --------------------------------------------------------------------
 template <typename T> struct Tr;
@@ -257,6 +263,13 @@ struct AttnDev {
     FieldSpread klen, kmin, vlen, vmin;     // header field widths -> bytes
     AttnExchange x;      // head-sharded multi-GPU output exchange (n_ranks = 0: none)
     AttnAppend ap;       // the step's new token, written into residual row n_res - 1 by this launch (new_k = null: none)
+    // two-launch form: `nsplit` clusters per (sequence, KV head), state handed over through caller scratch
+    int nsplit;          // clusters per (sequence, KV head); 1 in the single-launch form
+    int dump_bytes;      // bytes of a warp's score region (compressed + residual tiles), a multiple of 16
+    unsigned* sc_count;  // [pairs] arrivals of the pair's clusters in the second launch (zero between launches)
+    float* sc_ml;        // [pairs][cluster * nsplit][16] per-CTA max (8 rows) and sum (8 rows)
+    uint8_t* sc_scores;  // [pairs][cluster * nsplit * kAW][dump_bytes]
+    float* sc_part;      // [pairs][nsplit][8][kD] per-cluster unnormalised output rows
 };
 
 // CTA-shared block (cluster-visible)
@@ -266,6 +279,8 @@ struct CtaShared {
     float wm[kAW][8];    // per-warp scratch
     float gM[8], gInvL[8];
     unsigned lutm[8];    // (2^len - 1) * 0x00010001 per pack length 0..4 (see unpack8)
+    unsigned last;       // two-launch form: this cluster is the pair's last one to deliver its rows
+    unsigned pad_[3];
     unsigned long long mbar[kAW][2];
 };
 // The CTA's reduced accumulators out[head][channel] (read by rank 0 through distributed shared
@@ -287,8 +302,13 @@ __device__ __forceinline__ unsigned deq(unsigned biased, typename Tr<T>::T2 add,
 }
 
 // =================================================================================================
-template <typename T, int KMODE, bool HP>
-__global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(const AttnDev P) {
+// PASS: kFused = everything in one launch (one cluster per pair); kScores = first launch of the two-launch
+// form: K phase, per-CTA max and sum and the score tiles go to the scratch; kValues = second launch: scores
+// come back, global max and sum, V phase, per-cluster rows to the scratch, the pair's last cluster adds them up.
+enum AttnPass : int { kFused = 0, kScores = 1, kValues = 2 };
+
+template <typename T, int KMODE, bool HP, int PASS>
+__global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : PASS == 2 ? PKV_ATTN_CTAS_VALUES : kMaxCtasPerSm) attn_decode_kernel(const AttnDev P) {
     using T2 = typename Tr<T>::T2;
     constexpr unsigned MAGIC = Tr<T>::kMagic2;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -296,11 +316,14 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
     const AttnArgs& a = P.a;
     const int lane = lane_id(), wic = threadIdx.x >> 5;
     const int g = lane >> 2, c = lane & 3;
-    const int rank = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int vrank = blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // vrank: CTA index among all clusters of the pair
+    const int rank = PASS == kFused ? vrank : vrank % P.cluster, split = PASS == kFused ? 0 : vrank / P.cluster;
     const int G = a.group;
     const int q_heads = a.kv_heads * G;
-    const int n_warps = kAW * P.cluster;
-    const int gw = rank * kAW + wic;                   // warp index inside the cluster
+    const int n_vctas = P.cluster * P.nsplit;
+    const int n_warps = kAW * n_vctas;
+    const int gw = vrank * kAW + wic;                  // warp index among all warps of the pair
+    const int pair = b * a.kv_heads + h;
 
     uint8_t* wbase = smem + wic * P.warp_smem;
     CtaShared* cs = reinterpret_cast<CtaShared*>(smem + P.cta_off);
@@ -333,7 +356,7 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
     const int n_rt = (a.n_res + 15) >> 4, rslot = n_warps - 1 - gw;
     const int my_rt = rslot < n_rt ? (n_rt - rslot + n_warps - 1) / n_warps : 0;
     const int nkb = 1 << P.nkb_shift, nvi = 1 << P.nvi_shift;   // K blocks / V blocks per tile
-    const int k_items = my_tiles << P.nkb_shift, v_items = my_tiles << P.nvi_shift;
+    const int k_items = PASS == kValues ? 0 : my_tiles << P.nkb_shift, v_items = PASS == kScores ? 0 : my_tiles << P.nvi_shift;
     const int total_items = k_items + v_items;
     const int k_rounds = a.cbk >> 4;
     const int lbk = len_field_bits(a.bits_k), lbv = len_field_bits(a.bits_v);
@@ -589,6 +612,9 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
         }
     };
 
+    const T* kres = reinterpret_cast<const T*>(a.k_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
+    const T* vres = reinterpret_cast<const T*>(a.v_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
+    if constexpr (PASS != kValues) {
     for (int n = 0; n < k_items; n++) {
         cur_pk0 = nxt_pk0;
         wait_item(n);
@@ -648,8 +674,6 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
     // ---- residual tiles, phase 1: scores -------------------------------------------------------
     // A fragments come straight from the uncompressed rows: lane (g, c) reads channels
     // 32m + 8c .. +7 (m = 0..3) of tokens g and g+8 and pairs them in the order of pair_shuffle.
-    const T* kres = reinterpret_cast<const T*>(a.k_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
-    const T* vres = reinterpret_cast<const T*>(a.v_res) + (int64_t)b * a.res_seq_stride + (int64_t)h * a.res_head_stride;
     // The decode step's new token: the warp that owns the residual tile of row n_res - 1 rotates K (the
     // arithmetic of rope_kernel: both products rounded to the element type, then their sum) and copies V into
     // that row first; its own loads of the tile below then see the row (plain loads and cp.async, no read-only path).
@@ -799,21 +823,102 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
         }
         cs->cl_l[threadIdx.x] = l;
     }
-    // ---- cluster exchange: global max and sum ---------------------------------------------------
-    cluster.sync();
-    if (threadIdx.x < 8) {
-        float M = -INFINITY;
-        for (int r = 0; r < P.cluster; r++) M = fmaxf(M, cluster.map_shared_rank(cs, r)->cl_m[threadIdx.x]);
-        float L = 0.f;
-        for (int r = 0; r < P.cluster; r++) {
-            const CtaShared* o = cluster.map_shared_rank(cs, r);
-            const float mr = o->cl_m[threadIdx.x];
-            if (mr != -INFINITY) L += o->cl_l[threadIdx.x] * fast_exp(mr - M);
+    }   // PASS != kValues
+    auto report_flags = [&]() {
+        if (__any_sync(0xffffffffu, bad_len) && lane == 0) atomicOr(a.flags, kFlagBadStream);
+        if (__any_sync(0xffffffffu, bad_zero) && lane == 0) atomicOr(a.flags, kFlagZeroRange);
+    };
+    if constexpr (PASS == kFused) {
+        // ---- cluster exchange: global max and sum ---------------------------------------------------
+        cluster.sync();
+        if (threadIdx.x < 8) {
+            float M = -INFINITY;
+            for (int r = 0; r < P.cluster; r++) M = fmaxf(M, cluster.map_shared_rank(cs, r)->cl_m[threadIdx.x]);
+            float L = 0.f;
+            for (int r = 0; r < P.cluster; r++) {
+                const CtaShared* o = cluster.map_shared_rank(cs, r);
+                const float mr = o->cl_m[threadIdx.x];
+                if (mr != -INFINITY) L += o->cl_l[threadIdx.x] * fast_exp(mr - M);
+            }
+            cs->gM[threadIdx.x] = M;
+            cs->gInvL[threadIdx.x] = L > 0.f ? 1.f / L : 0.f;
         }
-        cs->gM[threadIdx.x] = M;
-        cs->gInvL[threadIdx.x] = L > 0.f ? 1.f / L : 0.f;
+        __syncthreads();
     }
-    __syncthreads();
+    if constexpr (PASS == kScores) {
+        // ---- first launch ends here: this CTA's max and sum and every warp's score region go to the scratch ----
+        __syncthreads();
+        if (threadIdx.x < 16)
+            P.sc_ml[((int64_t)pair * n_vctas + vrank) * 16 + threadIdx.x] = threadIdx.x < 8 ? cs->cl_m[threadIdx.x] : cs->cl_l[threadIdx.x - 8];
+        {
+            uint4* dst = reinterpret_cast<uint4*>(P.sc_scores + ((int64_t)pair * n_warps + gw) * P.dump_bytes);
+            const uint4* src = reinterpret_cast<const uint4*>(wbase + P.off_stile);
+            for (int i = lane; i < (P.dump_bytes >> 4); i += 32) dst[i] = src[i];
+        }
+        report_flags();
+        return;
+    } else {
+    if constexpr (PASS == kValues) {
+        // ---- second launch starts here: the warp's score region comes back; global max and sum from all CTAs' ----
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(P.sc_scores + ((int64_t)pair * n_warps + gw) * P.dump_bytes);
+            uint4* dst = reinterpret_cast<uint4*>(wbase + P.off_stile);
+            for (int i = lane; i < (P.dump_bytes >> 4); i += 32) dst[i] = __ldcg(src + i);
+        }
+        // thread t takes the CTAs t, t + 128, ...: maxima first, then the sums rescaled to the global maxima;
+        // warp shuffles, then the four warps' values in a fixed order (every CTA of the pair gets the same bits)
+        float m8[8], l8[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) { m8[r] = -INFINITY; l8[r] = 0.f; }
+        const float4* ml = reinterpret_cast<const float4*>(P.sc_ml + (int64_t)pair * n_vctas * 16);
+        for (int v = threadIdx.x; v < n_vctas; v += kAW * 32) {
+            const float4 ma = __ldcg(ml + 4 * v), mb = __ldcg(ml + 4 * v + 1), la = __ldcg(ml + 4 * v + 2), lb = __ldcg(ml + 4 * v + 3);
+            const float mv[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w}, lv[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                // one CTA per thread unless the pair has more than 128 of them: then rescale what is held already
+                const float mn = fmaxf(m8[r], mv[r]);
+                if (mn != -INFINITY) l8[r] = l8[r] * fast_exp(m8[r] - mn) + lv[r] * fast_exp(mv[r] - mn);
+                m8[r] = mn;
+            }
+        }
+        float M8[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            float m = m8[r];
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+            if (lane == 0) cs->wm[wic][r] = m;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            float m = cs->wm[0][r];
+#pragma unroll
+            for (int w = 1; w < kAW; w++) m = fmaxf(m, cs->wm[w][r]);
+            M8[r] = m;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            float l = m8[r] != -INFINITY ? l8[r] * fast_exp(m8[r] - M8[r]) : 0.f;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) l += __shfl_xor_sync(0xffffffffu, l, d);
+            if (lane == 0) cs->wm[wic][r] = l;
+        }
+        __syncthreads();
+        if (threadIdx.x < 8) {
+            float L = 0.f;
+#pragma unroll
+            for (int w = 0; w < kAW; w++) L += cs->wm[w][threadIdx.x];
+            float M = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < 8; r++) if (r == (int)threadIdx.x) M = M8[r];
+            cs->gM[threadIdx.x] = M;
+            cs->gInvL[threadIdx.x] = L > 0.f ? 1.f / L : 0.f;
+        }
+        __syncthreads();
+    }
 
     // ============================================================================ phase 2: V tiles
     float o[8][4];
@@ -973,8 +1078,7 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
         }
     }
     __syncwarp();
-    if (__any_sync(0xffffffffu, bad_len) && lane == 0) atomicOr(a.flags, kFlagBadStream);
-    if (__any_sync(0xffffffffu, bad_zero) && lane == 0) atomicOr(a.flags, kFlagZeroRange);
+    report_flags();
 
     // ---- residual tiles, phase 2: probabilities x V ---------------------------------------------
     // The tile's 16 V rows are staged (padded to 272 bytes so that ldmatrix is conflict free) in the
@@ -1040,32 +1144,62 @@ __global__ void __launch_bounds__(kAW * 32, kMaxCtasPerSm) attn_decode_kernel(co
     cluster.sync();
     if (rank == 0) {
         const int d = threadIdx.x;
-        for (int hd = 0; hd < G; hd++) {
-            float v = 0.f;
-            for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
-            const T r = Tr<T>::from_float(v);
-            const int64_t idx = ((int64_t)(b * q_heads + h * G + hd)) * kD + d;
-            reinterpret_cast<T*>(a.out)[idx] = r;
-            // head-sharded decode: the same row goes into this rank's slice of every rank's gathered buffer
-            for (int p = 0; p < P.x.n_ranks; p++)
-                reinterpret_cast<T*>(P.x.gathered[p])[(int64_t)P.x.rank * a.batch * q_heads * kD + idx] = r;
-        }
-        if (P.x.n_ranks > 0) {
-            __threadfence_system();                    // the rows are visible to the other GPUs before the arrival is
+        bool deliver = true;
+        if constexpr (PASS == kValues) {
+            // this cluster's rows go to the scratch; the cluster that finds all the others' there adds them up
+            float* part = P.sc_part + ((int64_t)pair * P.nsplit + split) * 8 * kD;
+            for (int hd = 0; hd < G; hd++) {
+                float v = 0.f;
+                for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
+                __stcg(part + hd * kD + d, v);
+            }
+            __threadfence();
             __syncthreads();
-            if (d < P.x.n_ranks) atomicAdd_system(P.x.arrivals[d] + P.x.rank, 1u);
+            if (d == 0) cs->last = atomicAdd(P.sc_count + pair, 1u) == (unsigned)(P.nsplit - 1) ? 1u : 0u;
+            __syncthreads();
+            deliver = cs->last != 0;
+            if (deliver) __threadfence();
+        }
+        if (deliver) {
+            for (int hd = 0; hd < G; hd++) {
+                float v = 0.f;
+                if constexpr (PASS == kValues) {
+                    for (int sp = 0; sp < P.nsplit; sp++) v += __ldcg(P.sc_part + (((int64_t)pair * P.nsplit + sp) * 8 + hd) * kD + d);
+                } else {
+                    for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
+                }
+                const T r = Tr<T>::from_float(v);
+                const int64_t idx = ((int64_t)(b * q_heads + h * G + hd)) * kD + d;
+                reinterpret_cast<T*>(a.out)[idx] = r;
+                // head-sharded decode: the same row goes into this rank's slice of every rank's gathered buffer
+                for (int p = 0; p < P.x.n_ranks; p++)
+                    reinterpret_cast<T*>(P.x.gathered[p])[(int64_t)P.x.rank * a.batch * q_heads * kD + idx] = r;
+            }
+            if (PASS == kValues && d == 0) P.sc_count[pair] = 0u;   // ready for the next launch on this scratch
+            if (P.x.n_ranks > 0) {
+                __threadfence_system();                // the rows are visible to the other GPUs before the arrival is
+                __syncthreads();
+                if (d < P.x.n_ranks) atomicAdd_system(P.x.arrivals[d] + P.x.rank, 1u);
+            }
         }
     }
     cluster.sync();   // keep every CTA's shared memory alive until rank 0 has read it
+    }   // PASS != kScores
 }
 
 // =================================================================================================
 static int k_bound(int cb, int bits) { int r = cb / 16; return 2 * r + r * (16 * bits + 16 * len_field_bits(bits) + 256 * bits); }
 static int v_bound(int cb, int bits) { int n = cb == 128 ? 4 : 2; return 2 * n + n * (16 * bits + 16 * len_field_bits(bits) + 256 * bits); }
 
-template <typename T, int KM, bool HPV>
+// tuning overrides read once from the environment (0 = choose automatically)
+static int env_int(const char* name) {
+    const char* v = std::getenv(name);
+    return v ? std::atoi(v) : 0;
+}
+
+template <typename T, int KM, bool HPV, int PASS>
 static int launch_one(const AttnDev& P, dim3 grid, int smem, cudaStream_t st) {
-    auto kern = attn_decode_kernel<T, KM, HPV>;
+    auto kern = attn_decode_kernel<T, KM, HPV, PASS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kCudaError;
     if (P.cluster > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) return kCudaError;
     cudaLaunchConfig_t cfg = {};
@@ -1089,24 +1223,33 @@ static int launch_one(const AttnDev& P, dim3 grid, int smem, cudaStream_t st) {
     return cudaLaunchKernelEx(&cfg, kern, P) == cudaSuccess ? kOk : kCudaError;
 }
 
+template <typename T, int PASS>
+static int launch_pass(const AttnDev& P, dim3 grid, int smem, cudaStream_t st) {
+    const AttnArgs& a = P.a;
+    if (a.k_mode == kKChannel)
+        return a.high_precision_zero ? launch_one<T, kKChannel, true, PASS>(P, grid, smem, st) : launch_one<T, kKChannel, false, PASS>(P, grid, smem, st);
+    return a.high_precision_zero ? launch_one<T, kKToken, true, PASS>(P, grid, smem, st) : launch_one<T, kKToken, false, PASS>(P, grid, smem, st);
+}
+
 template <typename T>
 static int launch_typed(const AttnDev& P, dim3 grid, int smem, cudaStream_t st) {
-    const AttnArgs& a = P.a;
-    if (a.k_mode == kKChannel) return a.high_precision_zero ? launch_one<T, kKChannel, true>(P, grid, smem, st) : launch_one<T, kKChannel, false>(P, grid, smem, st);
-    return a.high_precision_zero ? launch_one<T, kKToken, true>(P, grid, smem, st) : launch_one<T, kKToken, false>(P, grid, smem, st);
+    if (P.nsplit == 1 && P.sc_count == nullptr) return launch_pass<T, kFused>(P, grid, smem, st);
+#ifdef PKV_DEBUG_PASS   // measurement builds: one of the two launches alone (the results are then meaningless)
+    static const int only = env_int("PKV_ATTN_ONLY_PASS");
+    if (only == 1) return launch_pass<T, kScores>(P, grid, smem, st);
+    if (only == 2) return launch_pass<T, kValues>(P, grid, smem, st);
+#endif
+    const int rc = launch_pass<T, kScores>(P, grid, smem, st);
+    return rc != kOk ? rc : launch_pass<T, kValues>(P, grid, smem, st);
 }
 
-// tuning overrides read once from the environment (0 = choose automatically)
-static int env_int(const char* name) {
-    const char* v = std::getenv(name);
-    return v ? std::atoi(v) : 0;
-}
 
 // shared memory of one CTA for a cluster of `cl` CTAs with `nslots` staging slots per warp; fills the layout fields
-static int plan_smem(AttnDev& P, int cl, int nslots, int slot) {
+static int plan_smem(AttnDev& P, int cl, int nsplit, int nslots, int slot) {
     const AttnArgs& a = P.a;
-    const int n_warps = kAW * cl;
+    const int n_warps = kAW * cl * nsplit;
     P.cluster = cl;
+    P.nsplit = nsplit;
     P.nslots = nslots;
     P.slot = slot;
     P.tpw = (P.tiles_total + n_warps - 1) / n_warps;
@@ -1130,8 +1273,23 @@ static int plan_smem(AttnDev& P, int cl, int nslots, int slot) {
     P.off_stile = off; off += P.tpw * P.rows * P.prow;
     P.off_rst = off; off += P.rtw * P.rows * 32;
     P.warp_smem = (off + 15) & ~15;
+    P.dump_bytes = P.warp_smem - P.off_stile;
     P.cta_off = kAW * P.warp_smem;
     return P.cta_off + (int)sizeof(CtaShared);
+}
+
+// partition of the caller's scratch for the two-launch form
+struct ScratchLayout { int64_t count, ml, part, scores, total; };
+static ScratchLayout scratch_layout(int64_t pairs, int cl, int nsplit, int dump_bytes) {
+    ScratchLayout L;
+    int64_t off = 0;
+    L.count = off; off += (pairs * 4 + 255) & ~(int64_t)255;
+    L.ml = off; off += pairs * cl * nsplit * 64;
+    L.part = off; off += pairs * nsplit * 8 * kD * 4;
+    off = (off + 255) & ~(int64_t)255;
+    L.scores = off; off += pairs * cl * nsplit * kAW * (int64_t)dump_bytes;
+    L.total = off;
+    return L;
 }
 
 // One warp polls this rank's arrival counters; see pkv_exchange_wait.
@@ -1157,7 +1315,9 @@ int launch_exchange_wait(const uint32_t* arrivals, int n_ranks, unsigned expecte
     return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
 }
 
-int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppend* ap, cudaStream_t st) {
+// plan_io: in: cluster / nsplit / launches to force (0 = choose); out: what was chosen.  dry_run: plan only.
+int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppend* ap, AttnPlan* plan_io, void* scratch, int64_t scratch_bytes,
+                     bool dry_run, cudaStream_t st) {
     if (a.batch <= 0 || a.kv_heads <= 0 || a.group < 1 || a.group > 8) return a.group > 8 ? kUnsupported : kBadArgument;
     if (a.n_comp < 0 || a.n_res < 0 || a.n_comp + a.n_res == 0) return kBadArgument;
     if (!a.q || !a.out || !a.flags) return kBadArgument;
@@ -1222,43 +1382,70 @@ int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppen
         const int vs = P.vpair ? 2 * ((vb + 48 + 15) & ~15) : (vb + 48 + 15) & ~15;
         slot = ((ks > vs ? ks : vs) + 31) & ~31;                // the halves of a slot are 16-byte aligned
     }
-    // Cluster size and staging depth: the (sequence, KV head) pairs times the cluster size should fill the
-    // 148 SMs' CTA slots in whole waves, every warp should have work, and a long sequence must fit its scores
-    // in shared memory.  Cost model: waves x work units per warp x (resident warps beyond 10 per SM share
-    // the issue slots).
+    // Cluster size, clusters per pair and staging depth: the (sequence, KV head) pairs times their CTAs should
+    // fill the 148 SMs' CTA slots in whole waves, every warp should have work, and a warp's scores must fit in
+    // shared memory.  Cost model: waves x (work units per warp + a fixed part) x (resident warps beyond about 9
+    // per SM share the issue slots).  Several clusters per pair need the scratch and two launches.
     static const int env_cl = env_int("PKV_ATTN_CLUSTER"), env_slots = env_int("PKV_ATTN_SLOTS");
+    const int want_cl = plan_io && plan_io->cluster > 0 ? plan_io->cluster : env_cl;
+    const int want_split = plan_io && plan_io->nsplit > 0 ? plan_io->nsplit : 0;
+    const int want_launches = plan_io ? plan_io->launches : 0;
+    if (want_cl < 0 || want_cl > 16 || want_launches < 0 || want_launches > 2) return kBadArgument;
+    if (scratch && ((reinterpret_cast<uintptr_t>(scratch) & 255) || scratch_bytes < 0)) return kBadArgument;
     const long pairs = (long)a.batch * a.kv_heads;
-    const int units = P.tiles_total * (P.tile / 64) * 4 + (a.n_res + 15) / 16;   // a residual tile is about a quarter of 64 compressed tokens
-    const int unit_tile = (P.tile / 64) * 4;
-    int best_cl = 0, best_ns = 1, best_smem = 0;
+    const int unit_tile = (P.tile / 64) * 4;                   // a residual tile is about a quarter of 64 compressed tokens
+    static const int kSplits[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
+    int best_cl = 0, best_ns = 1, best_split = 1, best_launches = 1;
     double best_cost = 1e300;
     for (int cl = 1; cl <= 16; cl++) {
-        if (env_cl && cl != env_cl) continue;
-        for (int ns = 2; ns >= 1; ns--) {
-            if (env_slots && ns != env_slots) continue;
-            AttnDev Q = P;
-            const int smem = plan_smem(Q, cl, ns, slot);
-            if (smem > 227 * 1024) continue;
-            int per_sm = (228 * 1024) / (smem + 1024);
-            if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
-            if (per_sm < 1) continue;
-            const long ctas = pairs * cl, slots = (long)kSmCount * per_sm;
-            const long waves = (ctas + slots - 1) / slots;
-            const double resident = (double)(ctas < slots ? ctas : slots) / kSmCount * kAW;   // warps per SM
-            const int n_warps = kAW * cl;
-            const int upw = ((P.tiles_total + n_warps - 1) / n_warps) * unit_tile + (((a.n_res + 15) / 16 + n_warps - 1) / n_warps);
-            // measured: an SM's throughput stops growing at about 10 resident warps (the kernel is bound by instruction issue)
-            double cost = (double)waves * (upw + 3.0 /* fixed part per CTA: exchange, reductions */) * (resident > 10.0 ? resident / 10.0 : 1.0);
-            if (ns == 1) cost *= 1.06;                          // the copy of the next block is not overlapped
-            if (cl > 8) cost *= 1.10;                           // non-portable cluster sizes schedule worse
-            if (cost < best_cost - 1e-9) { best_cost = cost; best_cl = cl; best_ns = ns; best_smem = smem; }
+        if (want_cl && cl != want_cl) continue;
+        for (int split : kSplits) {
+            if (want_split && split != want_split) continue;
+            if (cl * split > 128) continue;
+            for (int launches = 1; launches <= 2; launches++) {
+                if (want_launches && launches != want_launches) continue;
+                if (launches == 1 && split > 1) continue;
+                if (launches == 2 && split == 1 && want_launches != 2) continue;   // one cluster in two launches: only on request
+                for (int ns = 2; ns >= 1; ns--) {
+                    if (env_slots && ns != env_slots) continue;
+                    AttnDev Q = P;
+                    const int smem = plan_smem(Q, cl, split, ns, slot);
+                    if (smem > 227 * 1024) continue;
+                    if (launches == 2 && (!scratch || scratch_layout(pairs, cl, split, Q.dump_bytes).total > scratch_bytes)) continue;
+                    int per_sm = (228 * 1024) / (smem + 1024);
+                    if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
+                    if (per_sm < 1) continue;
+                    const long ctas = pairs * cl * split, slots = (long)kSmCount * per_sm;
+                    const long waves = (ctas + slots - 1) / slots;
+                    const double resident = (double)(ctas < slots ? ctas : slots) / kSmCount * kAW;   // warps per SM
+                    const int n_warps = kAW * cl * split;
+                    const int upw = ((P.tiles_total + n_warps - 1) / n_warps) * unit_tile + (((a.n_res + 15) / 16 + n_warps - 1) / n_warps);
+                    // Fixed part per CTA: exchange and reductions; in two launches also the hand-over, a second start
+                    // and one more row to add per cluster of the pair.  Measured: a warp alone does a unit in 2.3 us and
+                    // an SM's throughput stops growing at about 9 resident warps (the kernel is bound by instruction
+                    // issue); clusters above the portable size schedule badly once they fill more than half the GPU.
+                    const double fixed = launches == 2 ? 5.0 + 0.05 * split : 3.0;
+                    double cost = (double)waves * (upw + fixed) * (resident > 9.2 ? resident / 9.2 : 1.0);
+                    if (ns == 1) cost *= 1.06;                      // the copy of the next block is not overlapped
+                    if (cl > 8) cost *= 2 * ctas > slots ? 1.4 : 1.1;
+                    if (cost < best_cost - 1e-9) { best_cost = cost; best_cl = cl; best_ns = ns; best_split = split; best_launches = launches; }
+                }
+            }
         }
     }
-    (void)units;
     if (best_cl == 0) return kUnsupported;
-    const int smem = plan_smem(P, best_cl, best_ns, slot);
-    (void)best_smem;
-    dim3 grid(P.cluster, a.kv_heads, a.batch);
+    const int smem = plan_smem(P, best_cl, best_split, best_ns, slot);
+    if (best_launches == 2) {
+        const ScratchLayout L = scratch_layout(pairs, best_cl, best_split, P.dump_bytes);
+        uint8_t* base = static_cast<uint8_t*>(scratch);
+        P.sc_count = reinterpret_cast<unsigned*>(base + L.count);
+        P.sc_ml = reinterpret_cast<float*>(base + L.ml);
+        P.sc_part = reinterpret_cast<float*>(base + L.part);
+        P.sc_scores = base + L.scores;
+    }
+    if (plan_io) { plan_io->cluster = best_cl; plan_io->nsplit = best_split; plan_io->launches = best_launches; }
+    if (dry_run) return kOk;
+    dim3 grid(P.cluster * P.nsplit, a.kv_heads, a.batch);
     return a.is_bf16 ? launch_typed<__nv_bfloat16>(P, grid, smem, st) : launch_typed<__half>(P, grid, smem, st);
 }
 

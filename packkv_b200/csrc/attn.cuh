@@ -12,9 +12,12 @@ using AttnArgs = pkv_attn_args;
 
 using AttnExchange = pkv_attn_exchange;
 using AttnAppend = pkv_attn_append;
+using AttnPlan = pkv_attn_plan;
 
-// xch may be null (single GPU); ap may be null (the residual already holds every token)
-int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppend* ap, cudaStream_t st);
+// xch may be null (single GPU); ap may be null (the residual already holds every token); plan_io may be null
+// (choose everything); scratch may be null (single-launch form only); dry_run: fill plan_io, launch nothing
+int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppend* ap, AttnPlan* plan_io, void* scratch, int64_t scratch_bytes,
+                     bool dry_run, cudaStream_t st);
 int launch_exchange_wait(const uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, cudaStream_t st);
 
 }  // namespace pkv

@@ -149,18 +149,31 @@ int32_t pkv_dequantize(const uint8_t* codes, int64_t codes_seq_stride, const voi
 
 int32_t pkv_decode_attention(const pkv_attn_args* args_host, void* cuda_stream) {
     if (!args_host) return kBadArgument;
-    return launch_attention(*args_host, nullptr, nullptr, static_cast<cudaStream_t>(cuda_stream));
+    return launch_attention(*args_host, nullptr, nullptr, nullptr, nullptr, 0, false, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int32_t pkv_decode_attention_exchange(const pkv_attn_args* args_host, const pkv_attn_exchange* exchange_host, void* cuda_stream) {
     if (!args_host || !exchange_host) return kBadArgument;
-    return launch_attention(*args_host, exchange_host, nullptr, static_cast<cudaStream_t>(cuda_stream));
+    return launch_attention(*args_host, exchange_host, nullptr, nullptr, nullptr, 0, false, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int32_t pkv_decode_attention_append(const pkv_attn_args* args_host, const pkv_attn_append* append_host, const pkv_attn_exchange* exchange_host,
                                     void* cuda_stream) {
     if (!args_host || !append_host) return kBadArgument;
-    return launch_attention(*args_host, exchange_host, append_host, static_cast<cudaStream_t>(cuda_stream));
+    return launch_attention(*args_host, exchange_host, append_host, nullptr, nullptr, 0, false, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_decode_attention_split(const pkv_attn_args* args_host, const pkv_attn_append* append_host, const pkv_attn_exchange* exchange_host,
+                                   pkv_attn_plan* plan_io, void* scratch, int64_t scratch_bytes, void* cuda_stream) {
+    if (!args_host) return kBadArgument;
+    return launch_attention(*args_host, exchange_host, append_host, plan_io, scratch, scratch_bytes, false, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_attention_plan(const pkv_attn_args* args_host, pkv_attn_plan* plan_io, int64_t scratch_bytes) {
+    if (!args_host || !plan_io) return kBadArgument;
+    // the plan depends on sizes only: any non-null, aligned address stands for the scratch
+    return launch_attention(*args_host, nullptr, nullptr, plan_io, scratch_bytes > 0 ? reinterpret_cast<void*>(uintptr_t(256)) : nullptr, scratch_bytes,
+                            true, nullptr);
 }
 
 int32_t pkv_exchange_wait(const uint32_t* arrivals, int32_t n_ranks, uint32_t expected, uint32_t max_polls, uint32_t* dev_flags,

@@ -229,7 +229,8 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
                      v_res: Optional[torch.Tensor], n_res: int, *, scaling: Optional[float] = None,
                      out: Optional[torch.Tensor] = None,
                      flags: Optional[torch.Tensor] = None, kv_heads: Optional[int] = None,
-                     exchange: Optional["_lib.AttnExchange"] = None, append: Optional[tuple] = None) -> torch.Tensor:
+                     exchange: Optional["_lib.AttnExchange"] = None, append: Optional[tuple] = None,
+                     scratch: Optional[torch.Tensor] = None, plan: Optional[tuple] = None, plan_only: bool = False):
     """softmax(q K^T * scaling) V for one query token per sequence.
 
     q: (B, Hq, 128) fp16/bf16 (post-RoPE).  `layer` holds the compressed tokens, k_res/v_res
@@ -239,8 +240,11 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
     `append` = (k_new, v_new, cos, sin) with k_new / v_new (B, Hkv, 1, 128) and cos / sin (B or 1, 1, 128) or None:
     the launch writes the step's new token (K rotated like rope()) into residual row n_res - 1 before attending;
     n_res counts that token.
+    `scratch` (new_attention_scratch) lets the library split a launch with few (sequence, KV head) pairs over
+    several clusters per pair in two launches; `plan` = (cluster, nsplit, launches), 0 = choose, forces the split.
+    plan_only: nothing is launched and the plan (cluster, nsplit, launches) that would be used is returned.
     """
-    _require_cuda(q, k_res, v_res, out, flags)
+    _require_cuda(q, k_res, v_res, out, flags, scratch)
     if q.dim() != 3 or q.shape[2] != 128 or not q.is_contiguous():
         raise ValueError("q must be a contiguous (B, Hq, 128) tensor")
     if q.dtype not in (torch.float16, torch.bfloat16):
@@ -303,6 +307,22 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
                 raise ValueError("cos / sin must be contiguous (B or 1, 1, 128) tensors of q's dtype")
             ap.cos, ap.sin, ap.cs_stride_b = cos.data_ptr(), sin.data_ptr(), (0 if cos.shape[0] == 1 else 128)
         ap.res_capacity = k_res.shape[2]
+    else:
+        ap = None
+    if scratch is not None or plan is not None or plan_only:
+        pl = _lib.AttnPlan()
+        if plan is not None:
+            pl.cluster, pl.nsplit, pl.launches = plan
+        if scratch is not None and (scratch.dtype != torch.uint8 or not scratch.is_contiguous() or scratch.data_ptr() % 256):
+            raise ValueError("scratch must be a contiguous uint8 tensor aligned to 256 bytes (new_attention_scratch)")
+        sbytes = 0 if scratch is None else scratch.numel()
+        if plan_only:
+            _lib.check(_lib.lib().pkv_attention_plan(ctypes.byref(a), ctypes.byref(pl), sbytes), "attention_plan")
+            return (pl.cluster, pl.nsplit, pl.launches)
+        st = _lib.lib().pkv_decode_attention_split(ctypes.byref(a), ctypes.byref(ap) if ap is not None else None,
+                                                   ctypes.byref(exchange) if exchange is not None else None, ctypes.byref(pl),
+                                                   scratch.data_ptr() if scratch is not None else None, sbytes, _stream_ptr())
+    elif ap is not None:
         st = _lib.lib().pkv_decode_attention_append(ctypes.byref(a), ctypes.byref(ap), ctypes.byref(exchange) if exchange is not None else None,
                                                     _stream_ptr())
     elif exchange is None:
@@ -311,6 +331,12 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
         st = _lib.lib().pkv_decode_attention_exchange(ctypes.byref(a), ctypes.byref(exchange), _stream_ptr())
     _lib.check(st, "decode_attention")
     return out
+
+
+def new_attention_scratch(device, nbytes: int = 32 << 20) -> torch.Tensor:
+    """Zeroed scratch for decode_attention's two-launch form (scores, per-CTA maxima and sums, per-cluster rows and
+    arrival counters); launches that share one must be ordered on one stream."""
+    return torch.zeros(nbytes, dtype=torch.uint8, device=device)
 
 
 def exchange_wait(arrivals: torch.Tensor, n_ranks: int, expected: int, flags: torch.Tensor, max_polls: int = 2_000_000) -> None:

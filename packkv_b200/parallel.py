@@ -153,15 +153,17 @@ class HeadExchange:
 
 
 def check_against_full(w: dict, rank: int, world: int, device, dtype, shard_layer0, q_full0: torch.Tensor, n_comp: int, n_res: int,
-                       xchg: "HeadExchange", flags: torch.Tensor) -> dict:
+                       xchg: "HeadExchange", flags: torch.Tensor, scratch: Optional[torch.Tensor] = None, plan=None) -> dict:
     """Runs layer 0 of a head-sharded benchmark workload once more: every rank computes its heads and takes part
-    in the exchange; rank 0 also computes all heads on its own GPU from the same seeded K/V and compares."""
+    in the exchange; rank 0 also computes all heads on its own GPU from the same seeded K/V, with the same CTAs per
+    (sequence, KV head) as the sharded launch (the order of the fp32 sums depends on nothing else), and compares."""
     from . import encode, ops, synth
     from .config import QuantMode
     layer, k_res, v_res = shard_layer0
     Hq_l = q_full0.shape[1] // world
-    out = ops.decode_attention(q_full0[:, rank * Hq_l:(rank + 1) * Hq_l].contiguous(), layer, k_res, v_res, n_res, flags=flags,
-                               exchange=xchg.begin())
+    q_l = q_full0[:, rank * Hq_l:(rank + 1) * Hq_l].contiguous()
+    used = ops.decode_attention(q_l, layer, k_res, v_res, n_res, flags=flags, scratch=scratch, plan=plan, plan_only=True)
+    out = ops.decode_attention(q_l, layer, k_res, v_res, n_res, flags=flags, exchange=xchg.begin(), scratch=scratch, plan=plan)
     xchg.gather(out)
     torch.cuda.synchronize()
     got = xchg.full()
@@ -171,9 +173,11 @@ def check_against_full(w: dict, rank: int, world: int, device, dtype, shard_laye
     full = encode.compress_kv(k[:, :, :n_comp], v[:, :, :n_comp], block=w["block"], bits_k=w["bits_k"], bits_v=w["bits_v"],
                               k_rel=synth.rel_for_bits(w["bits_k"]), v_rel=synth.rel_for_bits(w["bits_v"]),
                               k_mode=QuantMode.TokenQuant if w.get("k_mode") == "token" else QuantMode.ChannelQuant, cbk=w["cbk"], cbv=w["cbv"])
-    ref = ops.decode_attention(q_full0, full, k[:, :, n_comp:].contiguous(), v[:, :, n_comp:].contiguous(), n_res, flags=flags)
+    big = ops.new_attention_scratch(device, 256 << 20) if used[2] == 2 else None
+    ref = ops.decode_attention(q_full0, full, k[:, :, n_comp:].contiguous(), v[:, :, n_comp:].contiguous(), n_res, flags=flags, scratch=big, plan=used)
     torch.cuda.synchronize()
-    return {"bit_identical_to_one_gpu": bool(torch.equal(got, ref)), "max_abs_diff": float((got.float() - ref.float()).abs().max())}
+    return {"bit_identical_to_one_gpu": bool(torch.equal(got, ref)), "max_abs_diff": float((got.float() - ref.float()).abs().max()),
+            "plan": {"cluster": used[0], "clusters_per_pair": used[1], "launches": used[2]}}
 
 
 def compress_kv_head_shard(k: torch.Tensor, v: torch.Tensor, rank: int, world: int, *, block: int, bits_k: int, bits_v: int,

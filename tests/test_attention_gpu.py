@@ -15,7 +15,8 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-3
 
 
-def _run_case(dev, dtype, B, Hkv, G, n_comp, n_res, *, block, cbk, cbv, bits_k, bits_v, k_mode, seed, hp=False, rope=True):
+def _run_case(dev, dtype, B, Hkv, G, n_comp, n_res, *, block, cbk, cbv, bits_k, bits_v, k_mode, seed, hp=False, rope=True, plan=None, scratch=None,
+              repeats=1):
     S = n_comp + n_res
     k, v = synth.synth_kv(B, Hkv, S, 128, seed=seed, dtype=dtype, apply_rope=rope)
     q = synth.synth_q(B, Hkv * G, 128, seed=seed, dtype=dtype)
@@ -30,7 +31,11 @@ def _run_case(dev, dtype, B, Hkv, G, n_comp, n_res, *, block, cbk, cbv, bits_k, 
     k_res = k[:, :, n_comp:].contiguous().to(dev) if n_res else None
     v_res = v[:, :, n_comp:].contiguous().to(dev) if n_res else None
     flags = ops.new_flags(dev)
-    out = ops.decode_attention(q[:, :, 0].contiguous().to(dev), layer, k_res, v_res, n_res, flags=flags, kv_heads=Hkv)
+    if plan is not None and scratch is None:
+        scratch = ops.new_attention_scratch(dev)
+    qd = q[:, :, 0].contiguous().to(dev)
+    for _ in range(repeats):                                 # the scratch's counters must come back to zero every time
+        out = ops.decode_attention(qd, layer, k_res, v_res, n_res, flags=flags, kv_heads=Hkv, plan=plan, scratch=scratch)
     torch.cuda.synchronize()
     assert int(flags.item()) == 0
     return _rel_err(out.float().cpu(), ref, dtype)
@@ -267,3 +272,104 @@ def test_random_shapes(cuda_device, it):
     err = _run_case(cuda_device, c["dtype"], c["B"], c["Hkv"], c["G"], c["n_comp"], c["n_res"], block=c["block"], cbk=c["cbk"], cbv=c["cbv"],
                     bits_k=c["bits_k"], bits_v=c["bits_v"], k_mode=c["k_mode"], seed=200 + it, hp=c["hp"])
     assert err <= TOL, (c, err)
+
+
+# ---- two-launch form: several clusters per (sequence, KV head), state handed over through the scratch ----------
+@pytest.mark.parametrize("plan", [(1, 1, 2), (2, 2, 2), (4, 3, 2), (8, 4, 2), (16, 2, 2), (1, 16, 2), (3, 6, 2)])
+@pytest.mark.parametrize("k_mode", ["channel", "token"])
+def test_split_plans_match_reference(cuda_device, plan, k_mode):
+    """(cluster, nsplit) from one cluster in two launches to more warps than tiles, both K modes, V blocks 64 and 128."""
+    err = _run_case(cuda_device, torch.bfloat16, 2, 2, 4, 1536, 150, block=64, cbk=64, cbv=128, bits_k=4, bits_v=4, k_mode=k_mode, seed=41, plan=plan,
+                    repeats=2)
+    assert err <= TOL, err
+    err = _run_case(cuda_device, torch.float16, 1, 3, 2, 1024, 129, block=64, cbk=64, cbv=64, bits_k=3, bits_v=2, k_mode=k_mode, seed=42, plan=plan)
+    assert err <= TOL, err
+
+
+def test_split_residual_only_and_high_precision(cuda_device):
+    err = _run_case(cuda_device, torch.float16, 2, 2, 4, 0, 191, block=64, cbk=64, cbv=64, bits_k=4, bits_v=4, k_mode="channel", seed=43, plan=(2, 3, 2))
+    assert err <= TOL, err
+    err = _run_case(cuda_device, torch.bfloat16, 1, 2, 8, 512, 0, block=128, cbk=128, cbv=128, bits_k=2, bits_v=4, k_mode="channel", seed=44, hp=True,
+                    plan=(4, 2, 2))
+    assert err <= TOL, err
+
+
+def test_split_chosen_for_one_long_sequence(cuda_device):
+    """Batch 1 at a long context: with a scratch the library splits the pairs over several clusters (and says so);
+    without one, or with one that is too small, it stays with the single launch; same numbers either way."""
+    dev, dtype = cuda_device, torch.bfloat16
+    B, Hkv, G, n_comp, n_res = 1, 2, 4, 16384, 130
+    k, v = synth.synth_kv(B, Hkv, n_comp + n_res, 128, seed=45, dtype=dtype, apply_rope=True)
+    q = synth.synth_q(B, Hkv * G, 128, seed=45, dtype=dtype)
+    layer, kd, vd = layer_from_oracle(k[:, :, :n_comp], v[:, :, :n_comp], block=64, bits_k=4, bits_v=4, k_mode="channel", cbk=64, cbv=128,
+                                      rel_k=synth.rel_for_bits(4), rel_v=synth.rel_for_bits(4), device=dev)
+    ref = Q.eager_attention(q, torch.cat([kd, k[:, :, n_comp:]], 2), torch.cat([vd, v[:, :, n_comp:]], 2))[:, 0].float()
+    qd, kr, vr = q[:, :, 0].contiguous().to(dev), k[:, :, n_comp:].contiguous().to(dev), v[:, :, n_comp:].contiguous().to(dev)
+    scratch = ops.new_attention_scratch(dev)
+    plan = ops.decode_attention(qd, layer, kr, vr, n_res, scratch=scratch, plan_only=True)
+    assert plan[2] == 2 and plan[1] > 1, plan
+    assert ops.decode_attention(qd, layer, kr, vr, n_res, plan_only=True)[1:] == (1, 1)
+    assert ops.decode_attention(qd, layer, kr, vr, n_res, scratch=scratch[:4096], plan_only=True)[1:] == (1, 1)
+    flags = ops.new_flags(dev)
+    out_split = ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags, scratch=scratch)
+    out_one = ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags)
+    torch.cuda.synchronize()
+    assert int(flags.item()) == 0
+    assert _rel_err(out_split.float().cpu(), ref, dtype) <= TOL
+    assert _rel_err(out_one.float().cpu(), ref, dtype) <= TOL
+    # the same plan on a launch with another batch size gives the same bits for the same sequence
+    import dataclasses
+    rep = lambda t: t.repeat(3, *([1] * (t.dim() - 1))).contiguous()
+    layer3 = dataclasses.replace(layer, **{f: rep(getattr(layer, f)) for f in
+                                           ("k_stream", "k_info", "k_bytes", "k_scale", "k_zero", "v_stream", "v_info", "v_bytes", "v_scale", "v_zero")})
+    out3 = ops.decode_attention(rep(qd), layer3, rep(kr), rep(vr), n_res, flags=flags, scratch=scratch, plan=plan)
+    torch.cuda.synchronize()
+    assert int(flags.item()) == 0
+    for b in range(3):
+        assert torch.equal(out3[b], out_split[0])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", [4, 3, 2])
+def test_mixed_pack_widths(cuda_device, dtype, bits):
+    """Data in which some channels barely move or hold their value for 32 tokens: packs of 0, 1, 2 bits next to
+    full ones in every round (the seeded random data of the other tests has packs of the top two widths only),
+    against the same reference, single launch and two launches."""
+    dev = cuda_device
+    B, Hkv, G, n_comp, n_res = 2, 2, 4, 768, 140
+    k, v = synth.synth_kv(B, Hkv, n_comp + n_res, 128, seed=51, dtype=dtype, apply_rope=False)
+    q = synth.synth_q(B, Hkv * G, 128, seed=51, dtype=dtype)
+    t = torch.arange(n_comp + n_res)
+    for x in (k, v):
+        xf = x.float()
+        xf[..., 1::4] = xf[..., 1::4].mean(dim=2, keepdim=True) + 0.02 * xf[..., 1::4]          # narrow channels
+        hold = (t // 32) * 32
+        xf[:, :, :, 2::8] = xf[:, :, hold][:, :, :, 2::8] + 0.05 * xf[:, :, :, 2::8]               # channels that hold their value for 32 tokens
+        x.copy_(xf.to(dtype))
+    for k_mode in ("channel", "token"):
+        layer, kd, vd = layer_from_oracle(k[:, :, :n_comp], v[:, :, :n_comp], block=64, bits_k=bits, bits_v=bits, k_mode=k_mode, cbk=64, cbv=128,
+                                          rel_k=synth.rel_for_bits(bits), rel_v=synth.rel_for_bits(bits), device=dev)
+        # empty, full and in-between widths must be present, or the test does not test what it says
+        widths = torch.bincount(layer_pack_widths(k[:, :, :n_comp], bits, k_mode), minlength=5)
+        assert widths[0] > 0 and widths[bits] > 0 and int((widths > 0).sum()) >= 3, widths
+        ref = Q.eager_attention(q, torch.cat([kd, k[:, :, n_comp:]], 2), torch.cat([vd, v[:, :, n_comp:]], 2))[:, 0].float()
+        qd, kr, vr = q[:, :, 0].contiguous().to(dev), k[:, :, n_comp:].contiguous().to(dev), v[:, :, n_comp:].contiguous().to(dev)
+        flags = ops.new_flags(dev)
+        out = ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags)
+        out2 = ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags, scratch=ops.new_attention_scratch(dev), plan=(2, 3, 2))
+        torch.cuda.synchronize()
+        assert int(flags.item()) == 0
+        assert _rel_err(out.float().cpu(), ref, dtype) <= TOL
+        assert _rel_err(out2.float().cpu(), ref, dtype) <= TOL
+
+
+def layer_pack_widths(k, bits, k_mode):
+    """Bit widths (0..4) of the K packs (16 tokens of one channel, minimum subtracted), from the oracle's codes."""
+    kc, _, _ = Q.quant_ints(k, 64, synth.rel_for_bits(bits), k_mode)
+    B, H, nb, blk, D = kc.shape
+    c = kc.reshape(B, H, nb * blk // 16, 16, D).int()
+    span = c.amax(3) - c.amin(3)
+    width = torch.zeros_like(span)
+    for b in range(1, 5):
+        width[span >= (1 << (b - 1))] = b
+    return width.flatten()

@@ -71,10 +71,12 @@ def test_head_sharded_attention_equals_single_gpu():
         assert len(results) == 8 and all(results.values()), dict(results)
 
 
-def test_exchange_rows_and_counters_on_one_gpu(cuda_device):
+@pytest.mark.parametrize("plan", [None, (2, 3, 2)])
+def test_exchange_rows_and_counters_on_one_gpu(cuda_device, plan):
     """Two ranks' launches run one after the other on one device, each with the exchange block that names both
     ranks' (local) gathered buffers: the buffers end up equal to the unsharded result and every counter has
-    grown by batch * local KV heads; the wait then passes without a poll running out."""
+    grown by batch * local KV heads; the wait then passes without a poll running out.  Also in the two-launch
+    form, where the pair's last cluster to finish delivers the rows."""
     from packkv_b200 import _lib, encode, ops, parallel, synth
     from packkv_b200.config import QuantMode
     dev, dtype = cuda_device, torch.float16
@@ -83,7 +85,8 @@ def test_exchange_rows_and_counters_on_one_gpu(cuda_device):
     q = synth.synth_q(B, H * G, 128, seed=5, dtype=dtype, device=dev)[:, :, 0].contiguous()
     args = dict(block=64, bits_k=4, bits_v=4, k_rel=1 / 14, v_rel=1 / 14, k_mode=QuantMode.ChannelQuant)
     full = encode.compress_kv(k[:, :, :S], v[:, :, :S], **args)
-    want = ops.decode_attention(q, full, k[:, :, S:].contiguous(), v[:, :, S:].contiguous(), R)
+    scratch = ops.new_attention_scratch(dev) if plan else None
+    want = ops.decode_attention(q, full, k[:, :, S:].contiguous(), v[:, :, S:].contiguous(), R, scratch=scratch, plan=plan)
     Hl, Hql = H // world, H * G // world
     gathered = [torch.zeros(world, B, Hql, 128, dtype=dtype, device=dev) for _ in range(world)]
     arrivals = [torch.zeros(world, dtype=torch.int32, device=dev) for _ in range(world)]
@@ -95,7 +98,7 @@ def test_exchange_rows_and_counters_on_one_gpu(cuda_device):
         for r in range(world):
             x.gathered[r], x.arrivals[r] = gathered[r].data_ptr(), arrivals[r].data_ptr()
         ops.decode_attention(q[:, lo * G:hi * G].contiguous(), layer, k[:, lo:hi, S:].contiguous(), v[:, lo:hi, S:].contiguous(), R,
-                             flags=flags, exchange=x)
+                             flags=flags, exchange=x, scratch=scratch, plan=plan)
     for r in range(world):
         ops.exchange_wait(arrivals[r], world, B * Hl, flags, max_polls=10)
     torch.cuda.synchronize()
