@@ -6,15 +6,23 @@
 // the separate quantise + pack kernels.
 //
 // The stream format lays blocks back to back, so a block's byte offset is the sum of all earlier
-// block sizes of its sequence.  Three launches, no device-side waiting:
-//   encode : one warp per block reads its fp16/bf16 tile, quantises on the fly and builds the
-//            block in shared memory, then stores it to a fixed-stride SLOT in scratch memory and
-//            its size to block_info[blk][1]
-//   scan   : the existing per-sequence exclusive scan (scan_sizes_kernel, pack.cu)
-//   compact: one warp per block copies its slot to its final offset in the stream
-// HBM traffic per element: 2 B read (the second read of a tile comes from L1/L2) + the block
-// bytes written, read and written once more (~0.56 B each at 4 bit) = ~3.7 B, against 5.6 B for
-// quantise -> codes -> sizes -> write.
+// block sizes of its sequence.  Two forms:
+//   direct : ONE launch.  A CTA builds its blocks (consecutive in the stream) in shared memory, then
+//            learns the offset of its first block from the CTAs before it in the sequence by a
+//            decoupled look-back over a small status array (every CTA publishes the bytes of its own
+//            blocks as soon as it knows them, so nobody waits for more than its neighbours' packing),
+//            and writes the blocks to their final place.  CTAs take their position from a ticket
+//            counter, so every CTA a look-back waits for has started; the wait is bounded all the same
+//            and a CTA that gives up raises the timeout flag and writes nothing.
+//            HBM traffic per element: 2 B read (the second read of a tile comes from L1/L2) + the
+//            block bytes written once (~0.56 B at 4 bit).
+//   slots  : three launches, no device-side waiting (more than 8 heads, or on request): encode into
+//            fixed-stride SLOTS in scratch memory with the size in block_info[blk][1]; per-sequence
+//            exclusive scan (scan_sizes_kernel, pack.cu); one warp per block copies its slot to its
+//            final offset.  The block bytes are written, read and written once more.
+#include <cstdlib>
+#include <string>
+
 #include "common.cuh"
 #include "launch.h"
 #include "pack_dev.cuh"
@@ -34,7 +42,134 @@ struct FusedArgs {
     unsigned* flags;
     const uint8_t* order;                   // optional (batch, tokens / order_block, order_block): source row of every stored row
     int order_block;                        // tokens per reorder block (divides cb)
+    // direct form (status != nullptr): blocks go straight to the stream
+    unsigned* ticket;                       // zero before the launch: CTAs take their place in (sequence, link) order from it
+    unsigned long long* status;             // [batch][links], zero before the launch: (state << 32) | bytes; state 1: this link's
+                                            // blocks, 2: everything up to and including this link
+    int links;                              // CTAs per sequence
+    uint8_t* stream; int64_t stream_seq_stride, capacity;
+    unsigned* stream_bytes;                 // per sequence: bytes in the stream before (in) and after (out) the call
 };
+
+#ifdef PKV_DEBUG_CHAIN
+__device__ unsigned long long g_chain_stats[4];   // look-back cycles, look-backs, CTA cycles, CTAs
+#endif
+constexpr unsigned kChainSpins = 1u << 24;  // polls of a look-back before it gives up (each sleeps ~50 ns and waits for a load)
+
+// The CTA's place in the launch: ticket t -> (sequence, link).  All threads call; one barrier.
+__device__ __forceinline__ void chain_place(const FusedArgs& a, unsigned* sh_word, int& b, int& link) {
+    if (threadIdx.x == 0) *sh_word = atomicAdd(a.ticket, 1u);
+    __syncthreads();
+    // sequences take turns: the links of one sequence that are in flight at the same time are few, so a look-back
+    // rarely meets a predecessor that is still packing
+    const unsigned t = *sh_word;
+    b = (int)(t % (unsigned)a.batch);
+    link = (int)(t / (unsigned)a.batch);
+}
+
+// Byte offset, in sequence b's stream, of the first block of link `link`, whose blocks hold `total` bytes in all.
+// Called by ONE warp.  Returns false if a predecessor never published (bounded wait ran out).
+__device__ __forceinline__ bool chain_offset(const FusedArgs& a, int b, int link, unsigned total, unsigned& offset) {
+    const int lane = lane_id();
+    unsigned long long* st = a.status + (int64_t)b * a.links;
+    const unsigned base0 = a.first_cb == 0 ? 0u : a.stream_bytes[b];
+    unsigned excl = 0;
+    bool ok = true;
+#ifdef PKV_DEBUG_CHAIN   // measurement builds: cycles and polls spent in look-backs
+    const long long t_begin = clock64();
+#endif
+    if (link == 0) {
+        excl = base0;
+    } else {
+        if (lane == 0) *reinterpret_cast<volatile unsigned long long*>(st + link) = (1ull << 32) | total;
+        int j = link - 1;
+        unsigned spins = 0;
+        while (true) {
+            const int idx = j - lane;
+            const unsigned long long v = idx >= 0 ? *reinterpret_cast<volatile unsigned long long*>(st + idx) : ((2ull << 32) | base0);
+            // the nearest link that knows everything before it ends the search; the links between it and this one
+            // must have published their own bytes
+            const unsigned done = __ballot_sync(0xffffffffu, (v >> 32) == 2);
+            const int k = done ? __ffs(done) - 1 : 31;
+            if (__any_sync(0xffffffffu, lane <= k && (v >> 32) == 0)) {
+                if (++spins > kChainSpins) { ok = false; break; }
+                __nanosleep(50);
+                continue;
+            }
+            unsigned part = lane <= k ? (unsigned)v : 0u;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(0xffffffffu, part, d);
+            excl += part;
+            if (done) break;
+            j -= 32;
+        }
+    }
+#ifdef PKV_DEBUG_CHAIN
+    if (lane == 0) {
+        atomicAdd(&g_chain_stats[0], (unsigned long long)(clock64() - t_begin));
+        atomicAdd(&g_chain_stats[1], 1ull);
+    }
+#endif
+    // successors must not hang on a link that gave up: it publishes its own bytes on top of what it has
+    if (lane == 0) {
+        *reinterpret_cast<volatile unsigned long long*>(st + link) = (2ull << 32) | (excl + total);
+        if (link == a.links - 1) a.stream_bytes[b] = excl + total;
+        if (!ok) atomicOr(a.flags, kFlagTimeout);
+    }
+    offset = excl;
+    return ok;
+}
+
+// One warp copies a finished block from shared memory (16-byte aligned) to its place in the stream (even address).
+__device__ __forceinline__ void store_block(uint8_t* dst, const uint8_t* stage, int size, int lane) {
+    const int phase = (int)(reinterpret_cast<uintptr_t>(dst) & 15);   // even
+    const int head = min((16 - phase) & 15, size);                    // bytes before the first aligned chunk
+    for (int j = 2 * lane; j < head; j += 64) *reinterpret_cast<uint16_t*>(dst + j) = *reinterpret_cast<const uint16_t*>(stage + j);
+    const int nfull = (size - head) >> 4;
+    const unsigned* s32 = reinterpret_cast<const unsigned*>(stage);
+    const int sw = head >> 2;                                          // first source word of the body
+    const unsigned sh = (unsigned)(head & 3) * 8;                      // 0 or 16: byte offset inside that word
+    for (int c = lane; c < nfull; c += 32) {
+        const unsigned* p = s32 + sw + 4 * c;                          // aligned 32-bit loads, realigned by funnel shifts
+        const unsigned w0 = p[0], w1 = p[1], w2 = p[2], w3 = p[3], w4 = sh ? p[4] : 0u;
+        *reinterpret_cast<uint4*>(dst + head + 16 * c) = make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh),
+                                                                    __funnelshift_r(w2, w3, sh), __funnelshift_r(w3, w4, sh));
+    }
+    for (int j = head + 16 * nfull + 2 * lane; j < size; j += 64)
+        *reinterpret_cast<uint16_t*>(dst + j) = *reinterpret_cast<const uint16_t*>(stage + j);
+}
+
+// Direct form, after every warp of the CTA has put the sizes of its blocks into sizes[0..n): warp 0 gets the
+// CTA's offset, then warp w stores the blocks w, w + nwarps, ... (block j at stage_of(j)) and their table entries.
+// info_first: table index of block 0 of this link.  All threads call.
+template <typename StageOf>
+__device__ __forceinline__ void chain_store(const FusedArgs& a, int b, int link, const unsigned* sizes, int n, unsigned* sh_word, int64_t info_first,
+                                            int nwarps, StageOf stage_of) {
+    const int lane = lane_id(), wic = threadIdx.x >> 5;
+    __syncthreads();
+    if (wic == 0) {
+        unsigned total = 0;
+        for (int j = 0; j < n; j++) total += sizes[j];
+        unsigned off;
+        const bool ok = chain_offset(a, b, link, total, off);
+        if (lane == 0) *sh_word = ok ? off : 0xFFFFFFFFu;
+    }
+    __syncthreads();
+    const unsigned base = *sh_word;
+    if (base == 0xFFFFFFFFu) return;
+    for (int j = wic; j < n; j += nwarps) {
+        unsigned off = base;
+        for (int i = 0; i < j; i++) off += sizes[i];
+        const unsigned size = sizes[j];
+        uint32_t* bi = a.info + ((int64_t)b * a.info_seq_stride + info_first + j) * 2;
+        if (lane == 0) { bi[0] = off; bi[1] = size; }
+        if ((int64_t)off + size > a.capacity) {
+            if (lane == 0) atomicOr(a.flags, kFlagStreamOverflow);
+            continue;
+        }
+        store_block(a.stream + (int64_t)b * a.stream_seq_stride + off, stage_of(j), (int)size, lane);
+    }
+}
 
 __device__ __forceinline__ void store_slot(uint8_t* slot, const uint8_t* stage, int size, int lane) {
     // slot and stage are 16-byte aligned; the slot has room for the rounded-up size
@@ -192,8 +327,12 @@ __device__ __forceinline__ int k_encode_rounds_packed(const T* x, int64_t ss, co
 // same ownership as the stream format, so per-channel statistics need no cross-lane step.
 // CONTIG: token rows are 128 elements apart (a contiguous (B, H, S, 128) tensor), so every load of a
 // round is the block pointer plus a constant
+#ifndef PKV_K_WARPS
+#define PKV_K_WARPS 4
+#endif
+constexpr int kKWarps = PKV_K_WARPS;   // warps (= consecutive blocks of a sequence's stream) per CTA of the channel-mode K kernel
 template <typename T, bool CONTIG, int BITS, bool ORDERED = false>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(FusedArgs a) {
+__global__ void __launch_bounds__(kKWarps * 32, 768 / (kKWarps * 32)) k_fused_encode_kernel(FusedArgs a) {
     constexpr bool HP = false;
     const int64_t ss = CONTIG ? 128 : a.ss;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -201,15 +340,29 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
     const int lane = lane_id(), wic = threadIdx.x >> 5;
     const int nctx = a.tokens / a.cb;
     const int64_t per_seq = (int64_t)nctx * a.heads;
-    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + wic;
-    if (warp >= per_seq * a.batch) return;
-    const int b = (int)(warp / per_seq);
-    const int rem = (int)(warp % per_seq);
-    const int cbi = rem / a.heads, h = rem % a.heads;
+    __shared__ unsigned sh_word, sh_sizes[kKWarps];
+    const bool direct = a.status != nullptr;
+    int b, rem, link = 0;
+    int64_t warp = 0;
+    if (direct) {
+        // the CTA's warps take kKWarps consecutive blocks of one sequence's stream
+        chain_place(a, &sh_word, b, link);
+        rem = link * kKWarps + wic;
+    } else {
+        warp = (int64_t)blockIdx.x * kKWarps + wic;
+        if (warp >= per_seq * a.batch) return;
+        b = (int)(warp / per_seq);
+        rem = (int)(warp % per_seq);
+    }
+    const bool active = rem < per_seq;
+    const int cbi = active ? rem / a.heads : 0, h = active ? rem % a.heads : 0;
     const KGeom g(a.cb, BITS);
     const int slot_smem = (g.head_bytes + g.rounds * (g.min_bytes + g.len_bytes + 128 * 2 * BITS) + 15) & ~15;
     uint8_t* stage = smem + wic * slot_smem;
     const T* x = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)h * a.sh + (int64_t)cbi * a.cb * ss + 4 * lane;
+    int pos = 0;
+    bool bad = false;
+    if (active) {
 
     // per-channel min / max over the block, two channels per instruction in the element type
     // (min/max of element-type values is exact, so the fp32 detour is not needed here)
@@ -232,9 +385,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
         *reinterpret_cast<uint2*>(reinterpret_cast<T*>(a.scale) + pi) = *reinterpret_cast<const uint2*>(sc);
         *reinterpret_cast<uint2*>(reinterpret_cast<T*>(a.zero) + pi) = *reinterpret_cast<const uint2*>(zr);
     }
-    bool bad = q0.degenerate() || q1.degenerate() || q2.degenerate() || q3.degenerate();
+    bad = q0.degenerate() || q1.degenerate() || q2.degenerate() || q3.degenerate();
     const bool packable = __all_sync(0xffffffffu, q0.packable() && q1.packable() && q2.packable() && q3.packable());
-    int pos;
     const bool half_ok = __all_sync(0xffffffffu, q0.half_domain() && q1.half_domain() && q2.half_domain() && q3.half_domain());
     // reordered blocks (order_block == cb here): the table of this block's rows
     const uint8_t* ordp = ORDERED ? a.order + ((int64_t)b * nctx + cbi) * a.cb : nullptr;
@@ -242,8 +394,16 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) k_fused_encode_kernel(Fused
     else if (!HP && packable) pos = k_encode_rounds_packed<T, BITS, false, ORDERED>(x, ss, ordp, q0, q1, q2, q3, g, stage, lane, bad);
     else pos = k_encode_rounds<T, HP, BITS, false, ORDERED>(x, ss, ordp, q0, q1, q2, q3, g, stage, lane, bad);
     __syncwarp();
-    store_slot(a.slots + (int64_t)warp * a.slot_stride, stage, pos, lane);
-    if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * a.heads + h) * 2 + 1] = (unsigned)pos;
+    }   // active
+    if (direct) {
+        if (lane == 0) sh_sizes[wic] = (unsigned)pos;
+        const int64_t left = per_seq - (int64_t)link * kKWarps;
+        chain_store(a, b, link, sh_sizes, (int)(left < kKWarps ? left : kKWarps), &sh_word,
+                    (int64_t)a.first_cb * a.heads + (int64_t)link * kKWarps, kKWarps, [&](int j) { return smem + j * slot_smem; });
+    } else {
+        store_slot(a.slots + (int64_t)warp * a.slot_stride, stage, pos, lane);
+        if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * a.heads + h) * 2 + 1] = (unsigned)pos;
+    }
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
 }
 
@@ -423,17 +583,20 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int LB = len_field_bits(BITS);
     const int lane = lane_id(), wic = threadIdx.x >> 5;
-    const int cbi = blockIdx.x, b = blockIdx.y;
     const int nctx = a.tokens / CB;
+    __shared__ unsigned sh_word, sh_sizes[16];
+    const bool direct = a.status != nullptr;                 // then a warp keeps both of its blocks until the offsets are known
+    int cbi = blockIdx.x, b = blockIdx.y;
+    if (direct) chain_place(a, &sh_word, b, cbi);
     constexpr int PPT = CB == 32 ? 2 : 4, RPW = CB == 128 ? 2 : 1;
     const VGeom g(CB, BITS);
     const int bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * PPT * 2 * BITS) + 15) & ~15;
+    const int wstride = CB * 64 + (direct ? 2 : 1) * bound16;
     float4* prm = reinterpret_cast<float4*>(smem);           // [cb] (scale, zero, 1/scale, fast)
-    uint8_t* wbase = smem + 32 * CB + wic * (CB * 64 + bound16);
+    uint8_t* wbase = smem + 32 * CB + wic * wstride;
     uint8_t* ctile = wbase;                                  // [cb][64] codes
-    uint8_t* stage = wbase + CB * 64;
     const T* xb = reinterpret_cast<const T*>(a.x) + (int64_t)b * a.sb + (int64_t)cbi * CB * a.ss;
-    uint8_t* ord = smem + 32 * CB + 8 * (CB * 64 + bound16);
+    uint8_t* ord = smem + 32 * CB + 8 * wstride;
     load_row_order<CB>(a, ord, b, cbi);
 
     // pass 1: per-token statistics across every head and channel
@@ -454,6 +617,7 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
     for (int vb = wic; vb < nvb; vb += 8) {
         const int h = vb >> 1, half = vb & 1;
         const T* src = xb + (int64_t)h * a.sh + 64 * half;
+        uint8_t* stage = wbase + CB * 64 + (direct ? (vb >> 3) * bound16 : 0);
         __syncwarp();
         seen |= all_half ? v_quantise_tile<T, CB, 2>(src, a.ss, prm, ord, ctile, lane)
                          : all_packed ? v_quantise_tile<T, CB, 1>(src, a.ss, prm, ord, ctile, lane) : v_quantise_tile<T, CB, 0>(src, a.ss, prm, ord, ctile, lane);
@@ -501,10 +665,17 @@ __global__ void __launch_bounds__(256, 3) v_fused_encode_kernel(FusedArgs a) {
             }
         }
         __syncwarp();
-        const int64_t blk = ((int64_t)b * nctx + cbi) * nvb + vb;
-        store_slot(a.slots + blk * a.slot_stride, stage, pos, lane);
-        if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * nvb + vb) * 2 + 1] = (unsigned)pos;
+        if (direct) {
+            if (lane == 0) sh_sizes[vb] = (unsigned)pos;
+        } else {
+            const int64_t blk = ((int64_t)b * nctx + cbi) * nvb + vb;
+            store_slot(a.slots + blk * a.slot_stride, stage, pos, lane);
+            if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * nvb + vb) * 2 + 1] = (unsigned)pos;
+        }
     }
+    if (direct)
+        chain_store(a, b, cbi, sh_sizes, nvb, &sh_word, (int64_t)(a.first_cb + cbi) * nvb, 8,
+                    [&](int j) { return smem + 32 * CB + (j & 7) * wstride + CB * 64 + (j >> 3) * bound16; });
     bad = bad || (seen & ~(((1u << BITS) - 1u) * 0x00010001u)) != 0;
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
 }
@@ -518,8 +689,11 @@ __global__ void __launch_bounds__(256, 2) kt_fused_encode_kernel(FusedArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int LB = len_field_bits(BITS);
     const int lane = lane_id(), wic = threadIdx.x >> 5;
-    const int cbi = blockIdx.x, b = blockIdx.y;
     const int nctx = a.tokens / CB;
+    __shared__ unsigned sh_word, sh_sizes[8];
+    const bool direct = a.status != nullptr;
+    int cbi = blockIdx.x, b = blockIdx.y;
+    if (direct) chain_place(a, &sh_word, b, cbi);
     const KGeom g(CB, BITS);
     const int bound16 = (g.head_bytes + g.rounds * (g.min_bytes + g.len_bytes + 128 * 2 * BITS) + 15) & ~15;
     float4* prm = reinterpret_cast<float4*>(smem);
@@ -592,10 +766,17 @@ __global__ void __launch_bounds__(256, 2) kt_fused_encode_kernel(FusedArgs a) {
             pos += round_size;
         }
         __syncwarp();
-        const int64_t blk = ((int64_t)b * nctx + cbi) * a.heads + h;
-        store_slot(a.slots + blk * a.slot_stride, stage, pos, lane);
-        if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * a.heads + h) * 2 + 1] = (unsigned)pos;
+        if (direct) {
+            if (lane == 0) sh_sizes[h] = (unsigned)pos;     // direct form: at most 8 heads, one block per warp
+        } else {
+            const int64_t blk = ((int64_t)b * nctx + cbi) * a.heads + h;
+            store_slot(a.slots + blk * a.slot_stride, stage, pos, lane);
+            if (lane == 0) a.info[((int64_t)b * a.info_seq_stride + (int64_t)(a.first_cb + cbi) * a.heads + h) * 2 + 1] = (unsigned)pos;
+        }
     }
+    if (direct)
+        chain_store(a, b, cbi, sh_sizes, a.heads, &sh_word, (int64_t)(a.first_cb + cbi) * a.heads, 8,
+                    [&](int j) { return smem + 32 * CB + j * (CB * 128 + bound16) + CB * 128; });
     bad = bad || (seen & ~(((1u << BITS) - 1u) * 0x00010001u)) != 0;
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(a.flags, kFlagCodeRange);
 }
@@ -755,16 +936,31 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, const uin
     a.batch = r.batch; a.heads = r.heads; a.tokens = r.tokens; a.cb = r.cb; a.bits = BITS; a.rel = r.rel; a.flags = r.flags;
     const int nctx = r.tokens / r.cb;
     int bound16, blocks_per_seq;
+    // Direct form: the scratch holds only the ticket and the status array of the look-back.  The slots form stays
+    // for more than 8 heads (a CTA of the per-token kernels would not hold all blocks of its token block), for a
+    // scratch too small for the status array, and on request (PKV_ENCODE_PATH=slots: measurements, tests).
+    static const bool env_slots = [] { const char* v = std::getenv("PKV_ENCODE_PATH"); return v && std::string(v) == "slots"; }();
+    const bool per_token_kernel = r.which == 1 || r.mode == 1;
+    const int links = per_token_kernel ? nctx : (nctx * r.heads + kKWarps - 1) / kKWarps;
+    const int64_t chain_bytes = 256 + (int64_t)r.batch * links * 8;
+    const bool direct = !env_slots && (!per_token_kernel || r.heads <= 8) && chain_bytes <= fused_encode_scratch_bytes(r) && r.stream_bytes != nullptr;
+    if (direct) {
+        a.ticket = reinterpret_cast<unsigned*>(slots);
+        a.status = reinterpret_cast<unsigned long long*>(slots + 256);
+        a.links = links;
+        a.stream = r.stream; a.stream_seq_stride = r.stream_seq_stride; a.capacity = r.capacity; a.stream_bytes = reinterpret_cast<unsigned*>(r.stream_bytes);
+        if (cudaMemsetAsync(slots, 0, (size_t)chain_bytes, st) != cudaSuccess) return kCudaError;
+    }
     if (r.which == 0) {
         const KGeom g(r.cb, BITS);
         bound16 = (g.head_bytes + g.rounds * (g.min_bytes + g.len_bytes + 128 * 2 * BITS) + 15) & ~15;
         a.slot_stride = bound16;
         blocks_per_seq = nctx * r.heads;
         const int64_t nwarps = (int64_t)blocks_per_seq * r.batch;
-        const int smem = kWarpsPerCta * bound16;
-        const unsigned grid = (unsigned)((nwarps + kWarpsPerCta - 1) / kWarpsPerCta);
+        const int smem = kKWarps * bound16 + 16;
+        const unsigned grid = direct ? (unsigned)links * r.batch : (unsigned)((nwarps + kKWarps - 1) / kKWarps);
         if (r.mode == 1) {                       // per-token parameters: CTA per (sequence, token block)
-            const int smem_t = 32 * r.cb + 8 * (r.cb * 128 + bound16) + r.cb;
+            const int smem_t = 32 * r.cb + 8 * (r.cb * 128 + bound16) + r.cb + 16;
             auto launch_kt = [&](auto kern) {
                 if (opt_in_smem(kern, smem_t)) return (int)kCudaError;
                 kern<<<dim3(nctx, r.batch), 256, smem_t, st>>>(a);
@@ -778,22 +974,22 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, const uin
         } else if (a.order) {
             auto kern = k_fused_encode_kernel<T, false, BITS, true>;
             if (opt_in_smem(kern, smem)) return kCudaError;
-            kern<<<grid, kWarpsPerCta * 32, smem, st>>>(a);
+            kern<<<grid, kKWarps * 32, smem, st>>>(a);
         } else if (r.stride_s == 128) {
             auto kern = k_fused_encode_kernel<T, true, BITS>;
             if (opt_in_smem(kern, smem)) return kCudaError;
-            kern<<<grid, kWarpsPerCta * 32, smem, st>>>(a);
+            kern<<<grid, kKWarps * 32, smem, st>>>(a);
         } else {
             auto kern = k_fused_encode_kernel<T, false, BITS>;
             if (opt_in_smem(kern, smem)) return kCudaError;
-            kern<<<grid, kWarpsPerCta * 32, smem, st>>>(a);
+            kern<<<grid, kKWarps * 32, smem, st>>>(a);
         }
     } else {
         const VGeom g(r.cb, BITS);
         bound16 = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * g.ppt * 2 * BITS) + 15) & ~15;
         a.slot_stride = bound16;
         blocks_per_seq = nctx * 2 * r.heads;
-        const int smem = 32 * r.cb + 8 * (r.cb * 64 + bound16) + r.cb;
+        const int smem = 32 * r.cb + 8 * (r.cb * 64 + (direct ? 2 : 1) * bound16) + r.cb + 16;
         auto launch_v = [&](auto kern) {
             if (opt_in_smem(kern, smem)) return (int)kCudaError;
             kern<<<dim3(nctx, r.batch), 256, smem, st>>>(a);
@@ -805,6 +1001,7 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, const uin
         else rc = launch_v(v_fused_encode_kernel<T, HP, BITS, 128>);
         if (rc != kOk) return rc;
     }
+    if (direct) return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
     // offsets: reuse the per-sequence scan of the two-pass encoder
     CodecShape sh{r.batch, r.tokens, r.heads * 128, r.cb, r.which == 0 ? 128 : 64, BITS, r.first_token / r.cb};
     CodecBuffers cbuf{nullptr, 0, r.stream, r.stream_seq_stride, r.capacity, r.block_info, r.info_seq_stride, r.stream_bytes, r.flags};
@@ -843,6 +1040,14 @@ int launch_fused_encode(const FusedEncodeRequest& r, uint8_t* slots, const uint8
     if ((reinterpret_cast<uintptr_t>(slots) & 15) || (reinterpret_cast<uintptr_t>(r.stream) & 1) || (r.stream_seq_stride & 1)) return kBadArgument;
     return r.is_bf16 ? launch_fused_b<__nv_bfloat16, false>(r, slots, order, order_block, st) : launch_fused_b<__half, false>(r, slots, order, order_block, st);
 }
+
+#ifdef PKV_DEBUG_CHAIN
+extern "C" int pkv_debug_chain_stats(unsigned long long* out4, int reset) {
+    if (cudaMemcpyFromSymbol(out4, g_chain_stats, 32) != cudaSuccess) return -1;
+    if (reset) { unsigned long long z[4] = {0, 0, 0, 0}; cudaMemcpyToSymbol(g_chain_stats, z, 32); }
+    return 0;
+}
+#endif
 
 int launch_value_median_order(const FusedEncodeRequest& r, uint8_t* order, int block, cudaStream_t st) {
     if (block != 64 || r.heads < 1 || r.heads > 8 || r.tokens % 64 || r.high_precision_zero) return kUnsupported;

@@ -110,3 +110,28 @@ def test_strided_inputs(cuda_device, layout, which, mode):
     assert int(a["flags"].item()) == 0 and int(b["flags"].item()) == 0
     for name in ("stream", "info", "stream_bytes", "scale", "zero"):
         assert torch.equal(a[name].view(torch.uint8), b[name].view(torch.uint8)), name
+
+
+@pytest.mark.parametrize("which,mode", [("k", ops.K_CHANNEL), ("v", ops.K_TOKEN), ("k", ops.K_TOKEN)])
+@pytest.mark.parametrize("H,S", [(3, 128), (12, 128), (1, 64), (2, 64 * 150)])
+def test_direct_and_slot_forms(cuda_device, which, mode, H, S):
+    """The encoder writes blocks straight to the stream after a look-back over the CTAs before it in the sequence;
+    with more than 8 heads the per-token kernels go through slots and a compaction pass instead.  Head counts
+    that leave the last CTA of a sequence partly empty (3), that take the slot form (12), the smallest input, and
+    a sequence long enough for look-backs of more than one 32-entry window (150 token blocks, 75 K CTAs of 4
+    blocks): all byte-exact against the oracle, three sequences so that chains of different sequences interleave."""
+    dev, dtype = cuda_device, torch.float16
+    B, block, bits = 3, 64, 4
+    k, v = synth.synth_kv(B, H, S, 128, seed=43, dtype=dtype, apply_rope=True)
+    x = k if which == "k" else v
+    want, z, s = _oracle(x, which, mode, block, bits, False)
+    bufs = _bufs(B, H, S, block, bits, which, mode, dtype, dev)
+    for _ in range(2):   # a second call on the same scratch-free interface must start from clean look-back state
+        ops.encode_tensor(which, x.to(dev), block, synth.rel_for_bits(bits), mode, bits, block, **bufs)
+    torch.cuda.synchronize()
+    assert int(bufs["flags"].item()) == 0
+    for b in range(B):
+        ws, wi = want[b]
+        assert int(bufs["stream_bytes"][b].item()) == ws.size
+        assert np.array_equal(bufs["stream"][b, : ws.size].cpu().numpy(), ws)
+        assert np.array_equal(bufs["info"][b].cpu().numpy().view(np.uint32), wi)
