@@ -54,10 +54,10 @@ RECENT = 192   # buffer_size of every reference script (128 + 64)
 MIN_TIMED_S = 1.0   # the timed region is repeated until it is at least this long
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch (attention) or one step (encoder) from the ncu
-# captures summarised under profiles/.  An entry is valid for one revision of the kernel only (the revision is
+# captures kept with the repository's profile summaries.  An entry is valid for one revision of the kernel only (the revision is
 # a constant of packkv_b200.ops that changes with the kernel): other revisions report null.
 NCU_TRAFFIC_BYTES = {
-    ("attn", 2, 16, 8192, 8, 4, 4, 64, 128): 161.3e6,      # profiles/attn_decode_kernel_llama8b.md
+    ("attn", 2, 16, 8192, 8, 4, 4, 64, 128): 161.3e6,
     ("encode", 1, 16, 4, 64): 1836e6,
 }
 
@@ -567,13 +567,37 @@ def phi3_e2e_leg(rank, world, device, *, seqs_per_gpu=8, prompt=4096, new_tokens
 ENCODE_REVISION = 1   # changes when the encoder kernels change (keys NCU_TRAFFIC_BYTES)
 
 
+def legacy_matvec_leg(device, *, ctx=65536, hidden=1024, bits=4, layers=32, repeats=20):
+    """The reference's two-kernel API on its own benchmark shape (scripts/throughput_config_test.py: hidden 1024,
+    one sequence, context 64 K, 4 bit; it reports the sum over 32 layers of the wv kernel's time): K blocks of 64
+    tokens x 128 channels through kq_mat_vec_mul, V blocks of 128 tokens x 64 channels through wv_mat_vec_mul,
+    each timed by the call itself (CUDA events inside the call, like the reference's), median of `repeats`."""
+    import packkv_cuda
+    from packkv_b200 import ops, synth
+    heads, dtype = hidden // 128, torch.float16
+    k, v = synth.synth_kv(1, heads, ctx, 128, seed=3, dtype=dtype, device=device, apply_rope=True)
+    out = {"shape": f"hidden {hidden}, context {ctx}, 1 sequence, {bits} bit", "layers": layers}
+    for name, x, cb, hb in (("kq", k, 64, 128), ("wv", v, 128, 64)):
+        flags = ops.new_flags(device)
+        qz = ops.quantize(x, 64, synth.rel_for_bits(bits), ops.K_TOKEN, bits=bits, flags=flags)
+        stream, info, nbytes, _ = ops.encode_codes("k" if name == "kq" else "v", qz.codes, cb, bits)
+        stream = stream[0, : (int(nbytes[0].item()) + 15) // 16 * 16].contiguous()
+        vec = torch.randn(heads, 128 if name == "kq" else ctx, dtype=dtype, device=device)
+        res = torch.zeros(heads, ctx, dtype=dtype, device=device) if name == "kq" else torch.zeros(heads, 128, dtype=torch.float32, device=device)
+        fn = packkv_cuda.kq_mat_vec_mul if name == "kq" else packkv_cuda.wv_mat_vec_mul
+        times = sorted(fn(stream, info[0].contiguous(), vec, res, ctx, hidden, cb, hb, bits) for _ in range(repeats + 3))
+        ms = times[len(times) // 2]
+        out[name] = {"ms_per_call": ms, "ms_sum_over_layers": ms * layers, "stream_gbs": stream.numel() / (ms * 1e-3) / 1e9}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS) + ["mistral7b-encode", "phi3-e2e"])
+    ap.add_argument("--workload", default="llama8b", choices=sorted(WORKLOADS) + ["mistral7b-encode", "phi3-e2e", "legacy-matvec"])
     ap.add_argument("--encode-batch", type=int, default=64, help="sequences in all (split over the ranks)")
     ap.add_argument("--encode-bits", type=int, default=4)
     ap.add_argument("--encode-block", type=int, default=64)
@@ -627,6 +651,12 @@ def main():
                         "e2e": leg.get("e2e"), "median_reorder": leg.get("median"), "append": leg.get("append"),
                         "source_fp16_gbs": p["source_fp16_gbs"], "compressed_over_fp16": p["compressed_over_fp16"], "gpu_launches": 7 * args.steps}
                 print(json.dumps(line), flush=True)
+            return
+        if args.workload == "legacy-matvec":
+            if rank == 0:
+                leg = legacy_matvec_leg(device)
+                print(json.dumps({"metric": "legacy two-kernel API, wv_mat_vec_mul summed over 32 layers", "value": leg["wv"]["ms_sum_over_layers"],
+                                  "unit": "ms", "n_gpus": 1, "higher_is_better": False, "data": "synthetic", "detail": leg}), flush=True)
             return
         if args.workload == "phi3-e2e":
             leg = phi3_e2e_leg(rank, world, device)

@@ -28,7 +28,8 @@ REF_SO = os.path.join(REF_DIR, "libpackkv_ref.so")
 
 
 def reference_root() -> str:
-    return os.environ.get("PACKKV_REFERENCE", "/root/reference")
+    """The reference checkout: $PACKKV_REFERENCE, else a directory `reference` beside this repository."""
+    return os.environ.get("PACKKV_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _newer(target: str, *sources: str) -> bool:

@@ -9,7 +9,7 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-# PACKKV_SM100_LIB points at another build of the same ABI (e.g. an instrumented one)
+# PACKKV_SM100_LIB: path of another build of the same ABI to load instead of the in-tree one
 LIB_PATH = os.environ.get("PACKKV_SM100_LIB") or os.path.join(_PKG, "libpackkv_sm100.so")
 
 PKV_OK, PKV_ERR_BAD_ARGUMENT, PKV_ERR_UNSUPPORTED, PKV_ERR_CUDA, PKV_ERR_TOO_LARGE = 0, 1, 2, 3, 4

@@ -6,8 +6,12 @@
 //   wv_mat_vec_mul  packkv_cuda_ext/src/kernels.cu:632-859
 //   fused_kq        packkv_cuda_ext/src/fused_kernels.cu:13-185
 //   fused_wv        packkv_cuda_ext/src/fused_kernels.cu:187-370
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "launch.h"
+
+namespace cg = cooperative_groups;
 
 namespace pkv {
 
@@ -101,14 +105,18 @@ __global__ void __launch_bounds__(128) kq_kernel(LegacyArgs a) {
     }
 }
 
-// out[hb*64 + c] += sum_n w[h, n] * code[n, hb*64 + c], h = hb*64/128.  One CTA per 64-channel
-// block column; its 8 warps stride over the token blocks and are summed in a fixed order.
+// out[hb*64 + c] += sum_n w[h, n] * code[n, hb*64 + c], h = hb*64/128.  One cluster of kWvSlices CTAs per
+// 64-channel block column: the CTAs' 8 warps each stride over the token blocks; warps, then CTAs (through
+// distributed shared memory, on the cluster's first CTA) are summed in a fixed order.
+constexpr int kWvSlices = 8;
 template <typename T>
 __global__ void __launch_bounds__(256) wv_kernel(LegacyArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ float part[8][64];
+    __shared__ float csum[64];
+    cg::cluster_group cluster = cg::this_cluster();
     const int lane = lane_id(), wic = threadIdx.x >> 5;
-    const int hbi = blockIdx.x;
+    const int hbi = blockIdx.x / kWvSlices, slice = (int)cluster.block_rank();
     const int nhid = a.hidden / 64, nctx = a.ctx_len / a.cb;
     const VGeom g(a.cb, a.bits);
     const int lb = len_field_bits(a.bits);
@@ -116,7 +124,7 @@ __global__ void __launch_bounds__(256) wv_kernel(LegacyArgs a) {
     const int slot = (bound + 48 + 15) & ~15;
     const T* wrow = reinterpret_cast<const T*>(a.vec) + (int64_t)(hbi * 64 / 128) * a.ctx_len;
     float acc0 = 0.f, acc1 = 0.f;   // channels lane and 32 + lane
-    for (int cbi = wic; cbi < nctx; cbi += 8) {
+    for (int cbi = slice * 8 + wic; cbi < nctx; cbi += 8 * kWvSlices) {
         const int64_t blk_id = (int64_t)cbi * nhid + hbi;
         const unsigned off = a.info[2 * blk_id], size = a.info[2 * blk_id + 1];
         if ((int64_t)off + size > a.stream_bytes || (int)size > bound || size < 4) {
@@ -161,8 +169,15 @@ __global__ void __launch_bounds__(256) wv_kernel(LegacyArgs a) {
     if (threadIdx.x < 64) {
         float s = 0.f;
         for (int w = 0; w < 8; w++) s += part[w][threadIdx.x];
+        csum[threadIdx.x] = s;
+    }
+    cluster.sync();
+    if (slice == 0 && threadIdx.x < 64) {
+        float s = 0.f;
+        for (int r = 0; r < kWvSlices; r++) s += cluster.map_shared_rank(csum, r)[threadIdx.x];
         reinterpret_cast<float*>(a.out)[hbi * 64 + threadIdx.x] += s;
     }
+    cluster.sync();   // the other CTAs' sums stay alive until the first one has read them
 }
 
 // our_kq[m, n] = (sum_d q[m, d] * zero[n] + t[m, n]) * scale[n]
@@ -214,8 +229,18 @@ int launch_legacy_matvec(bool is_k, const LegacyArgs& a, cudaStream_t st) {
         const VGeom g(a.cb, a.bits);
         const int slot = (g.head_bytes + g.nseg * (g.min_bytes + g.len_bytes + 32 * g.ppt * 2 * a.bits) + 48 + 15) & ~15;
         const int smem = 8 * slot;
-        if (a.is_bf16) wv_kernel<__nv_bfloat16><<<a.hidden / 64, 256, smem, st>>>(a);
-        else wv_kernel<__half><<<a.hidden / 64, 256, smem, st>>>(a);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(a.hidden / 64) * kWvSlices, 1, 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = kWvSlices; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = a.is_bf16 ? cudaLaunchKernelEx(&cfg, wv_kernel<__nv_bfloat16>, a) : cudaLaunchKernelEx(&cfg, wv_kernel<__half>, a);
+        if (e != cudaSuccess) { cudaGetLastError(); return kCudaError; }
     }
     return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
 }

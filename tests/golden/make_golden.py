@@ -1,6 +1,6 @@
 """Generates the committed golden fixtures from the REFERENCE itself.
 
-Needs the reference checkout (``PACKKV_REFERENCE``, default ``/root/reference``): its
+Needs the reference checkout (``PACKKV_REFERENCE``, default: a directory ``reference`` beside this repository): its
 ``utils/compute.py`` is imported for the quantiser / reorder / size model, and its CPU
 codec sources are compiled by ``oracle/build_oracle.py``.  Run from the repository root:
 
@@ -25,7 +25,7 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("PACKKV_REFERENCE", "/root/reference")
+REF = os.environ.get("PACKKV_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
 sys.path.insert(0, REF)
 
 from oracle import codec  # noqa: E402

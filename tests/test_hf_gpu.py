@@ -112,3 +112,52 @@ def test_generate_runs():
     out = model.generate(ids, attention_mask=torch.ones_like(ids), past_key_values=cache, max_new_tokens=6, do_sample=False)
     assert out.shape == (2, 266)
     assert cache.get_seq_length() == 265          # the last generated token is not fed back
+
+
+@pytest.mark.parametrize("family", ["llama", "phi3"])
+def test_every_decode_attention_against_oracle_on_the_dense_view(family):
+    """Inside a running transformers model: every fused decode attention call (both layers, steps that cross a
+    block boundary included) is compared at 2e-3 with the reference's eager attention (oracle, CPU) over the
+    cache's dense view, which the cache tests pin to the reference cache bit for bit."""
+    transformers = pytest.importorskip("transformers")
+    from oracle import quant as Q
+    from packkv_b200 import hf
+    from packkv_b200.cache import PackKVCacheConfigStatic
+    from packkv_b200.config import PackKVCacheConfig, QuantMethod, RepackMethod
+    dtype = torch.bfloat16
+    torch.manual_seed(3)
+    if family == "llama":
+        from transformers import LlamaConfig as Cfg, LlamaForCausalLM as Model
+        cfg = Cfg(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=2, intermediate_size=1024, vocab_size=2000,
+                  head_dim=128, max_position_embeddings=1024)
+    else:
+        from transformers import Phi3Config as Cfg, Phi3ForCausalLM as Model
+        cfg = Cfg(hidden_size=384, num_attention_heads=4, num_key_value_heads=4, num_hidden_layers=2, intermediate_size=768, vocab_size=1000,
+                  max_position_embeddings=1024, pad_token_id=0, bos_token_id=1, eos_token_id=2)
+    model = Model(cfg).to("cuda", dtype).eval()
+    hf.register()
+    model.set_attn_implementation(hf.ATTN_NAME)
+    PackKVCacheConfigStatic.config = PackKVCacheConfig(family, QuantMethod.KIVI, RepackMethod.NONE, False, 64, 192, 16, 1 / 14, 1 / 14)
+    B, prefill, steps = 2, 300, 40
+    ids = torch.randint(3, 1000, (B, prefill + steps), device="cuda")
+    cache = hf.make_cache(cfg, B)
+    inner, worst, calls = cache.attend, [0.0], [0]
+
+    def checked(query_states, layer_idx, scaling=None):
+        out = inner(query_states, layer_idx, scaling)                       # (B, 1, Hq, D)
+        kd, vd = cache.dense(layer_idx)
+        ref = Q.eager_attention(query_states.cpu(), kd.cpu(), vd.cpu(), scaling)   # (B, 1, Hq, D)
+        err = ((out.float().cpu() - ref.float()).abs().max() / ref.float().abs().max()).item()
+        worst[0], calls[0] = max(worst[0], err), calls[0] + 1
+        return out
+    cache.attend = checked
+    try:
+        with torch.no_grad():
+            model(ids[:, :prefill], past_key_values=cache, use_cache=True)
+            for t in range(prefill, prefill + steps):
+                model(ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+        cache.check_flags()
+    finally:
+        PackKVCacheConfigStatic.config = None
+    assert calls[0] == 2 * steps
+    assert worst[0] <= 2e-3, worst[0]

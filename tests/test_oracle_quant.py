@@ -14,7 +14,7 @@ from oracle import codec
 from oracle import quant as Q
 from packkv_b200 import synth
 
-REF = os.environ.get("PACKKV_REFERENCE", "/root/reference")
+REF = os.environ.get("PACKKV_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 def _sha(a):
