@@ -58,7 +58,8 @@ MIN_TIMED_S = 1.0   # the timed region is repeated until it is at least this lon
 # a constant of packkv_b200.ops that changes with the kernel): other revisions report null.
 NCU_TRAFFIC_BYTES = {
     ("attn", 2, 16, 8192, 8, 4, 4, 64, 128): 161.3e6,
-    ("encode", 1, 16, 4, 64): 1836e6,
+    ("encode", 2, 16, 4, 64): 1401e6,                      # K 576 + 151 MB, V 561 + 113 MB
+    ("encode", 2, 64, 4, 64): 4 * 1401e6,                  # the 16-sequence capture scaled by the sequences (traffic is per sequence)
 }
 
 
@@ -471,28 +472,49 @@ def encode_leg(steps, warmup, rank, world, device, *, total_seqs=64, bits=4, blo
                          "attend_only_us": ms_attend / 512 * 1e3, "separate_append_launch_us": ms_update / 512 * 1e3,
                          "sequences_per_gpu": B, "steps": 512, "token_appends_per_s": world * B / (max(1e-6, ms_both - ms_attend) / 512 * 1e-3)}
     if with_e2e:
-        # end to end: K and V start in pinned host memory, the streams and their byte counts go back to it
+        # End to end: K and V start in pinned host memory, the streams and their byte counts go back to it.  The
+        # sequences go through in groups on three streams (upload, encode, download), so that the uploads of one group
+        # overlap the encode and the downloads of the groups before it; the timed region ends after the last download.
         layer = encode.compress_kv(k, v, **kw)
+        groups = 4 if B % 4 == 0 and B >= 8 else 1
+        G = B // groups
         k_host, v_host = k.cpu().pin_memory(), v.cpu().pin_memory()
         ks_host = torch.empty(layer.k_stream.shape, dtype=torch.uint8).pin_memory()
         vs_host = torch.empty(layer.v_stream.shape, dtype=torch.uint8).pin_memory()
         nb_host = torch.empty(2, B, dtype=torch.int32).pin_memory()
         k_dev, v_dev = torch.empty_like(k), torch.empty_like(v)
+        s_in, s_out, s_cmp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+        ev_in = [torch.cuda.Event() for _ in range(groups)]
+        ev_cmp = [torch.cuda.Event() for _ in range(groups)]
 
         def step_e2e():
-            k_dev.copy_(k_host, non_blocking=True)
-            v_dev.copy_(v_host, non_blocking=True)
-            L = encode.compress_kv(k_dev, v_dev, **kw)
-            ks_host.copy_(L.k_stream, non_blocking=True)
-            vs_host.copy_(L.v_stream, non_blocking=True)
-            nb_host[0].copy_(L.k_bytes, non_blocking=True)
-            nb_host[1].copy_(L.v_bytes, non_blocking=True)
+            s_in.wait_stream(s_cmp)                               # the device buffers of the step before are free again
+            kept = []
+            for g in range(groups):
+                sl = slice(g * G, (g + 1) * G)
+                with torch.cuda.stream(s_in):
+                    k_dev[sl].copy_(k_host[sl], non_blocking=True)
+                    v_dev[sl].copy_(v_host[sl], non_blocking=True)
+                    ev_in[g].record(s_in)
+                s_cmp.wait_event(ev_in[g])
+                L = encode.compress_kv(k_dev[sl], v_dev[sl], **kw)
+                ev_cmp[g].record(s_cmp)
+                kept.append(L)                                    # its buffers stay alive until the downloads have run
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_cmp[g])
+                    ks_host[sl].copy_(L.k_stream, non_blocking=True)
+                    vs_host[sl].copy_(L.v_stream, non_blocking=True)
+                    nb_host[0, sl].copy_(L.k_bytes, non_blocking=True)
+                    nb_host[1, sl].copy_(L.v_bytes, non_blocking=True)
+            s_cmp.wait_stream(s_out)
+            return kept
         step_e2e()
+        torch.cuda.synchronize()
         ms_e2e, _, _ = timed_batches(step_e2e, 2, world, device, min_seconds=0.0, max_batches=1)
         ms_e2e /= 2
         alg = src_bytes + layer.stream_bytes()
         out["e2e"] = {"value": world * alg / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": src_bytes,
-                      "d2h_bytes_per_step": int(layer.k_stream.numel() + layer.v_stream.numel() + 8 * B)}
+                      "d2h_bytes_per_step": int(layer.k_stream.numel() + layer.v_stream.numel() + 8 * B), "sequence_groups": groups}
     return out if rank == 0 else None
 
 
@@ -564,7 +586,7 @@ def phi3_e2e_leg(rank, world, device, *, seqs_per_gpu=8, prompt=4096, new_tokens
         torch.cuda.empty_cache()
 
 
-ENCODE_REVISION = 1   # changes when the encoder kernels change (keys NCU_TRAFFIC_BYTES)
+ENCODE_REVISION = 2   # changes when the encoder kernels change (keys NCU_TRAFFIC_BYTES)
 
 
 def legacy_matvec_leg(device, *, ctx=65536, hidden=1024, bits=4, layers=32, repeats=20):
@@ -601,6 +623,7 @@ def main():
     ap.add_argument("--encode-batch", type=int, default=64, help="sequences in all (split over the ranks)")
     ap.add_argument("--encode-bits", type=int, default=4)
     ap.add_argument("--encode-block", type=int, default=64)
+    ap.add_argument("--encode-plain-only", action="store_true", help="encode workload: skip the median / append / end-to-end legs (sweeps)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="default workload: skip the v_block_64 / encode / head_sharded legs")
     ap.add_argument("--decode-bits-k", type=int, default=None, help="override the decode workload's K bit width (sweeps)")
@@ -641,15 +664,16 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=device)
     try:
         if args.workload == "mistral7b-encode":
+            rest = not args.encode_plain_only
             leg = encode_leg(args.steps, args.warmup, rank, world, device, total_seqs=args.encode_batch, bits=args.encode_bits,
-                             block=args.encode_block)
+                             block=args.encode_block, with_median=rest, with_e2e=rest, with_append=rest)
             if rank == 0:
                 p = leg["plain"]
                 line = {"metric": "KV encode throughput", "value": p["value"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
                         "warmup": max(args.warmup, 3), "ms_per_step": p["ms_per_step"], "higher_is_better": True, "scaling": "strong",
                         "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": leg["config"], "roofline": p["roofline"],
                         "e2e": leg.get("e2e"), "median_reorder": leg.get("median"), "append": leg.get("append"),
-                        "source_fp16_gbs": p["source_fp16_gbs"], "compressed_over_fp16": p["compressed_over_fp16"], "gpu_launches": 7 * args.steps}
+                        "source_fp16_gbs": p["source_fp16_gbs"], "compressed_over_fp16": p["compressed_over_fp16"], "gpu_launches": 2 * args.steps}
                 print(json.dumps(line), flush=True)
             return
         if args.workload == "legacy-matvec":

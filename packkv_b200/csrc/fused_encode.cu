@@ -937,13 +937,17 @@ static int launch_fused_t(const FusedEncodeRequest& r, uint8_t* slots, const uin
     const int nctx = r.tokens / r.cb;
     int bound16, blocks_per_seq;
     // Direct form: the scratch holds only the ticket and the status array of the look-back.  The slots form stays
-    // for more than 8 heads (a CTA of the per-token kernels would not hold all blocks of its token block), for a
-    // scratch too small for the status array, and on request (PKV_ENCODE_PATH=slots: measurements, tests).
+    // for more than 8 heads (a CTA of the per-token kernels would not hold all blocks of its token block), for
+    // 128-token blocks in those kernels, for a scratch too small for the status array, and on request
+    // (PKV_ENCODE_PATH=slots: measurements, tests).
     static const bool env_slots = [] { const char* v = std::getenv("PKV_ENCODE_PATH"); return v && std::string(v) == "slots"; }();
     const bool per_token_kernel = r.which == 1 || r.mode == 1;
     const int links = per_token_kernel ? nctx : (nctx * r.heads + kKWarps - 1) / kKWarps;
     const int64_t chain_bytes = 256 + (int64_t)r.batch * links * 8;
-    const bool direct = !env_slots && (!per_token_kernel || r.heads <= 8) && chain_bytes <= fused_encode_scratch_bytes(r) && r.stream_bytes != nullptr;
+    // (128-token blocks in the per-token kernels: a second staging buffer per warp would leave one CTA per SM; measured
+    // 2.55 ms against 2.28 ms for the slots form on the 4-bit sweep configuration)
+    const bool direct = !env_slots && (!per_token_kernel || (r.heads <= 8 && r.cb != 128)) && chain_bytes <= fused_encode_scratch_bytes(r) &&
+                        r.stream_bytes != nullptr;
     if (direct) {
         a.ticket = reinterpret_cast<unsigned*>(slots);
         a.status = reinterpret_cast<unsigned long long*>(slots + 256);
