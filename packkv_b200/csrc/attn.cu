@@ -931,13 +931,14 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
     // channel l's four packs in the stream (lengths, minima, offsets), while the mma wants lane (g, c) to hold
     // channels g, g+8, g+16, g+24 for the 16 tokens of quarter c: the owners publish their pack descriptors
     // and every lane fetches the four packs its fragment rows need.
-    auto v_block = [&](auto bits_tag, unsigned blk, int hh, int tok_blk, unsigned st_a) {
-        constexpr int BV = decltype(bits_tag)::value, LBV = len_field_bits(BV);
-        const int rpw_shift = a.cbv == 128 ? 1 : 0;
-        const int nseg = 2 << rpw_shift;
-        int pos = 2 * nseg;
-        for (int sgi = 0; sgi < nseg; sgi++) {
-            const int w = sgi >> rpw_shift, rr = sgi & ((1 << rpw_shift) - 1);
+    // hh (which 64-channel half of the head) and w (which 32 channels of it) are compile-time, so that the accumulator
+    // tiles a segment adds to are fixed registers and no branch selects them
+    auto v_block = [&](auto bits_tag, auto hh_tag, unsigned blk, int tok_blk, unsigned st_a) {
+        constexpr int BV = decltype(bits_tag)::value, LBV = len_field_bits(BV), HH = decltype(hh_tag)::value;
+        const int rpw = a.cbv == 128 ? 2 : 1;           // segments of 64 tokens per 32 channels
+        int pos = 4 * rpw;
+        auto segment = [&](auto w_tag, int rr) {
+            constexpr int W = decltype(w_tag)::value, SEL = 2 * HH + W;
             const int tok_seg = tok_blk + rr * 64;     // first token (in the tile) of the segment
             const unsigned hdr = blk + pos;
             unsigned lens4 = spread_const<LBV>(lane_word<4 * LBV>(hdr + 16 * BV, lane));   // byte q = length of pack q (tokens 16q..16q+15)
@@ -964,7 +965,6 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
             const unsigned prow_a = st_a + min(g, P.rows - 1) * P.prow + tok2;
             const uint4 p0 = lds128(prow_a), p1 = lds128(prow_a + 16);
             const unsigned pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-            const int sel = 2 * hh + w;
 #pragma unroll
             for (int mt = 0; mt < 2; mt++) {
                 unsigned x[2][8];                      // rows g (channel g + 16 mt) and g + 8 (channel g + 8 + 16 mt)
@@ -989,19 +989,19 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
                 }
                 // four steps of 16 token slots: step s takes the words 2s and 2s+1 of every quarter
 #pragma unroll
-                for (int idx = 0; idx < 4; idx++) {
-                    if (idx == sel) {
-#pragma unroll
-                        for (int s = 0; s < 4; s++) {
-                            const unsigned af[4] = {x[0][2 * s], x[1][2 * s], x[0][2 * s + 1], x[1][2 * s + 1]};
-                            Tr<T>::mma(o[2 * idx + mt], af, pw[2 * s], pw[2 * s + 1]);
-                        }
-                    }
+                for (int s = 0; s < 4; s++) {
+                    const unsigned af[4] = {x[0][2 * s], x[1][2 * s], x[0][2 * s + 1], x[1][2 * s + 1]};
+                    Tr<T>::mma(o[2 * SEL + mt], af, pw[2 * s], pw[2 * s + 1]);
                 }
             }
             __syncwarp();                              // descriptors are rewritten by the next segment
             pos += 16 * BV + 16 * LBV + 2 * (int)(t012 + (tot >> 24));
-        }
+        };
+        // (unrolling these two loops as well was measured slower: 122 against 117 us per layer)
+#pragma unroll 1
+        for (int rr = 0; rr < rpw; rr++) segment(std::integral_constant<int, 0>{}, rr);
+#pragma unroll 1
+        for (int rr = 0; rr < rpw; rr++) segment(std::integral_constant<int, 1>{}, rr);
     };
 
     for (int n = k_items; n < total_items; n++) {
@@ -1064,10 +1064,14 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
                 const unsigned blk = sbase + sub * half_slot + (pk & 15);
                 const int hh = P.vpair ? sub : vi;                       // which 64-channel half of the head
                 const int tok_blk = P.vpair ? (vi << 6) : 0;             // token offset of the block in the tile
+                auto by_half = [&](auto bits_tag) {
+                    if (hh) v_block(bits_tag, std::integral_constant<int, 1>{}, blk, tok_blk, st_a);
+                    else v_block(bits_tag, std::integral_constant<int, 0>{}, blk, tok_blk, st_a);
+                };
                 switch (a.bits_v) {
-                    case 4: v_block(std::integral_constant<int, 4>{}, blk, hh, tok_blk, st_a); break;
-                    case 3: v_block(std::integral_constant<int, 3>{}, blk, hh, tok_blk, st_a); break;
-                    default: v_block(std::integral_constant<int, 2>{}, blk, hh, tok_blk, st_a); break;
+                    case 4: by_half(std::integral_constant<int, 4>{}); break;
+                    case 3: by_half(std::integral_constant<int, 3>{}); break;
+                    default: by_half(std::integral_constant<int, 2>{}); break;
                 }
             }
         }
