@@ -222,7 +222,7 @@ def _check_layer_shapes(L: "CompressedLayer", batch: int) -> None:
 
 
 # changes whenever the attention kernel changes in a way that can change its DRAM traffic (keys recorded profiler figures)
-ATTN_KERNEL_REVISION = 2
+ATTN_KERNEL_REVISION = 3
 
 
 def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: Optional[torch.Tensor],
