@@ -33,9 +33,13 @@ extern "C" {
 #define PKV_FLAG_TIMEOUT 8u
 #define PKV_FLAG_ZERO_RANGE 16u   /* pkv_decode_attention: a zero-point too large for the exact in-kernel dequantisation */
 
-/* quantisation modes (the reference's QuantMode.ChannelQuant / QuantMode.TokenQuant) */
+/* quantisation modes (the reference's QuantMode, utils/compute.py:6-11).  ChannelQuant and TokenQuant are the modes of
+ * its two quantisation methods and the only ones the single-pass encoder and the attention kernel take; VectorQuant
+ * and BlockQuant are served by pkv_quantize / pkv_dequantize (and the codec entry points on the code matrix). */
 #define PKV_K_CHANNEL 0
 #define PKV_K_TOKEN 1
+#define PKV_Q_VECTOR 2
+#define PKV_Q_BLOCK 3
 
 /* Library / build identification: returns the ABI version (currently 1). */
 int32_t pkv_abi_version(void);
@@ -112,7 +116,10 @@ int32_t pkv_fused_wv(void* our_wv, const void* w, const void* zero, const void* 
  * element type after every op.  mode PKV_K_CHANNEL: parameters per (sequence, head, token
  * block, channel), written to (batch, heads, param_blocks, 128) starting at block first_block;
  * mode PKV_K_TOKEN: per (sequence, token) across all heads, written to (batch, param_tokens)
- * starting at token first_token.  x strides are in elements; rows of 128 channels are
+ * starting at token first_token; mode PKV_Q_VECTOR: per (sequence, head, token) across its 128 channels, written to
+ * (batch, heads, param_tokens) starting at token first_token; mode PKV_Q_BLOCK: per (sequence, token block) across
+ * heads and channels, written to (batch, param_blocks) starting at block first_block (the reduction sets of
+ * QUANT_DIM, utils/compute.py:405-410).  x strides are in elements; rows of 128 channels are
  * contiguous and 8-byte aligned.  bits > 0 enables the range check (PKV_FLAG_CODE_RANGE).
  */
 int32_t pkv_quantize(const void* x, int64_t stride_b, int64_t stride_h, int64_t stride_s, uint8_t* codes,

@@ -70,7 +70,9 @@ __global__ void __launch_bounds__(128) dequant_kernel(DequantArgs q) {
     const float code = (float)q.codes[(int64_t)b * q.codes_seq_stride + (int64_t)t * (q.heads * 128) + h * 128 + d];
     int64_t pi;
     if (q.mode == 0) pi = (((int64_t)b * q.heads + h) * q.param_blocks + (q.first_token + t) / q.block) * 128 + d;
-    else pi = (int64_t)b * q.param_tokens + q.first_token + t;
+    else if (q.mode == 1) pi = (int64_t)b * q.param_tokens + q.first_token + t;
+    else if (q.mode == 2) pi = ((int64_t)b * q.heads + h) * q.param_tokens + q.first_token + t;      // vector: per (head, token)
+    else pi = (int64_t)b * q.param_blocks + (q.first_token + t) / q.block;                           // block: per token block
     const float s = CT<T>::ld(reinterpret_cast<const T*>(q.scale) + pi), z = CT<T>::ld(reinterpret_cast<const T*>(q.zero) + pi);
     const float v = HP ? CT<T>::rnd(CT<T>::rnd(code * s) + z) : CT<T>::rnd(CT<T>::rnd(code + z) * s);
     reinterpret_cast<T*>(q.out)[(int64_t)b * q.o_stride_b + (int64_t)h * q.o_stride_h + (int64_t)t * q.o_stride_s + d] = CT<T>::cvt(v);
@@ -98,7 +100,7 @@ int launch_append(const AppendArgs& r, cudaStream_t st) {
 
 int launch_dequantize(const DequantArgs& q, cudaStream_t st) {
     if (q.batch < 0 || q.heads <= 0 || q.tokens < 0 || q.block <= 0) return kBadArgument;
-    if (q.mode != 0 && q.mode != 1) return kUnsupported;
+    if (q.mode < 0 || q.mode > 3) return kUnsupported;
     if ((int64_t)q.batch * q.tokens == 0) return kOk;
     if (!q.codes || !q.scale || !q.zero || !q.out) return kBadArgument;
     dim3 grid(q.tokens, q.heads, q.batch);

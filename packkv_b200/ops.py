@@ -111,13 +111,26 @@ def decode_codes(which: str, stream: torch.Tensor, info: torch.Tensor, ctx: int,
     return out, flags
 
 
-K_CHANNEL, K_TOKEN = 0, 1
+K_CHANNEL, K_TOKEN, Q_VECTOR, Q_BLOCK = 0, 1, 2, 3
+
+
+def _param_extents(scale: torch.Tensor, mode: int):
+    """(capacity in blocks, capacity in tokens) of a parameter tensor of the given mode; the extent the mode does not
+    use is 0."""
+    if mode == K_CHANNEL:
+        return scale.shape[2], 0
+    if mode == K_TOKEN:
+        return 0, scale.shape[1]
+    if mode == Q_VECTOR:
+        return 0, scale.shape[2]
+    return scale.shape[1], 0
 
 
 @dataclass
 class Quantised:
     codes: torch.Tensor     # (B, S, H*128) uint8, the encoders' input layout
-    scale: torch.Tensor     # channel: (B, H, capacity_blocks, 128); token: (B, capacity_tokens)
+    scale: torch.Tensor     # channel: (B, H, capacity_blocks, 128); token: (B, capacity_tokens); vector: (B, H, capacity_tokens);
+                            # block: (B, capacity_blocks)
     zero: torch.Tensor
 
 
@@ -127,7 +140,8 @@ def quantize(x: torch.Tensor, block: int, rel: float, mode, *, bits: int = 0, hi
              ) -> Quantised:
     """Block-quantises x (B, H, S, 128) fp16/bf16 like the reference's quant_ints.
 
-    `mode` is a QuantMode (ChannelQuant or TokenQuant) or the integers K_CHANNEL / K_TOKEN.
+    `mode` is a QuantMode or one of the integers K_CHANNEL / K_TOKEN / Q_VECTOR / Q_BLOCK (the last two are not
+    taken by the encoder's single pass or the attention kernel: their codes go through encode_codes).
     Passing existing scale/zero tensors with first_token > 0 writes the new parameters behind
     the ones already there (append path).
     """
@@ -135,8 +149,8 @@ def quantize(x: torch.Tensor, block: int, rel: float, mode, *, bits: int = 0, hi
     if x.dim() != 4 or x.shape[3] != 128 or x.stride(3) != 1 or x.dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("x must be (B, H, S, 128) fp16/bf16 with contiguous channels")
     m = getattr(mode, "value", mode)
-    m = {"ChannelQuant": K_CHANNEL, "TokenQuant": K_TOKEN}.get(m, m)
-    if m not in (K_CHANNEL, K_TOKEN):
+    m = {"ChannelQuant": K_CHANNEL, "TokenQuant": K_TOKEN, "VectorQuant": Q_VECTOR, "BlockQuant": Q_BLOCK}.get(m, m)
+    if m not in (K_CHANNEL, K_TOKEN, Q_VECTOR, Q_BLOCK):
         raise RuntimeError("not supported")
     B, H, S, D = x.shape
     if S % block:
@@ -147,11 +161,10 @@ def quantize(x: torch.Tensor, block: int, rel: float, mode, *, bits: int = 0, hi
         flags = new_flags(dev)
     codes = torch.empty(B, S, H * D, dtype=torch.uint8, device=dev)
     if scale is None:
-        shape = (B, H, cap // block, D) if m == K_CHANNEL else (B, cap)
+        shape = {K_CHANNEL: (B, H, cap // block, D), K_TOKEN: (B, cap), Q_VECTOR: (B, H, cap), Q_BLOCK: (B, cap // block)}[m]
         scale = torch.zeros(shape, dtype=x.dtype, device=dev)
         zero = torch.zeros(shape, dtype=x.dtype, device=dev)
-    pb = scale.shape[2] if m == K_CHANNEL else 0
-    pt = scale.shape[1] if m == K_TOKEN else 0
+    pb, pt = _param_extents(scale, m)
     st = _lib.lib().pkv_quantize(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2), codes.data_ptr(), codes.stride(0),
                                  scale.data_ptr(), zero.data_ptr(), pb, first_token // block, pt, first_token,
                                  B, H, S, block, float(rel), bits, m, int(high_precision_zero),
@@ -400,8 +413,7 @@ def dequantize(codes: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, hea
     B, T, _ = codes.shape
     if out is None:
         out = torch.empty(B, heads, T, 128, dtype=scale.dtype, device=codes.device)
-    pb = scale.shape[2] if mode == K_CHANNEL else 0
-    pt = scale.shape[1] if mode == K_TOKEN else 0
+    pb, pt = _param_extents(scale, mode)
     st = _lib.lib().pkv_dequantize(codes.data_ptr(), codes.stride(0), scale.data_ptr(), zero.data_ptr(), pb, pt, first_token,
                                    out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), B, heads, T, block, mode,
                                    int(high_precision_zero), int(scale.dtype == torch.bfloat16), _stream_ptr())

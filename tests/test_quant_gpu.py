@@ -12,7 +12,7 @@ from packkv_b200 import ops, synth
 from packkv_b200.config import QuantMode
 
 pytestmark = pytest.mark.gpu
-MODES = {"channel": QuantMode.ChannelQuant, "token": QuantMode.TokenQuant}
+MODES = {"channel": QuantMode.ChannelQuant, "token": QuantMode.TokenQuant, "vector": QuantMode.VectorQuant, "block": QuantMode.BlockQuant}
 
 
 def _bits16(t):
@@ -26,16 +26,19 @@ def _check(dev, x, block, rel, mode, hp):
     torch.cuda.synchronize()
     want_codes = c.flatten(2, 3).permute(0, 2, 1, 3).flatten(2, 3).contiguous().to(torch.uint8)
     assert torch.equal(got.codes.cpu(), want_codes)
-    if mode == "channel":
-        zs, ss = z.reshape(B, H, S // block, D), s.reshape(B, H, S // block, D)
-    else:
-        zs, ss = z.reshape(B, S), s.reshape(B, S)
+    shape = {"channel": (B, H, S // block, D), "token": (B, S), "vector": (B, H, S), "block": (B, S // block)}[mode]
+    zs, ss = z.reshape(shape), s.reshape(shape)
     assert torch.equal(_bits16(got.scale.cpu()), _bits16(ss))
     assert torch.equal(_bits16(got.zero.cpu()), _bits16(zs))
+    # and back: the dense tensor the reference's cache would hold
+    mode_int = {"channel": ops.K_CHANNEL, "token": ops.K_TOKEN, "vector": ops.Q_VECTOR, "block": ops.Q_BLOCK}[mode]
+    dense = ops.dequantize(got.codes, got.scale, got.zero, H, block, mode_int, high_precision_zero=hp)
+    torch.cuda.synchronize()
+    assert torch.equal(_bits16(dense.cpu()), _bits16(Q.dequant(c, z, s, hp)))
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("mode", ["channel", "token"])
+@pytest.mark.parametrize("mode", ["channel", "token", "vector", "block"])
 def test_bit_exact_against_oracle(cuda_device, dtype, mode):
     k, v = synth.synth_kv(2, 4, 256, 128, seed=21, dtype=dtype, apply_rope=True)
     for x in (k, v):
