@@ -179,7 +179,7 @@ def layer_bytes(layer, k_res, v_res, n_res, batch, q_heads):
     return n
 
 
-def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e2e=True, sample_clocks=True, exchange="nccl"):
+def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e2e=True, sample_clocks=True, exchange="nccl", graph=False):
     """Builds the workload's compressed layers on this rank and times decode steps.  Returns a dict of raw
     measurements (milliseconds are per step, max over ranks)."""
     from packkv_b200 import ops, parallel
@@ -212,6 +212,22 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
            "plan": {"cluster": used[0], "clusters_per_pair": used[1], "launches": used[2]}}
     for _ in range(max(warmup, 3)):
         step_resident()
+    step_eager = step_resident
+    graph = graph and len(layers) % 2 == 0 and (not by_heads or exchange == "peer")   # the exchange's two buffers alternate per layer
+    if graph:
+        # the whole layer loop (attention launches, exchange blocks, waits) as one CUDA graph: no host work per launch
+        torch.cuda.synchronize()
+        cuda_graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(cuda_graph, stream=side):
+                step_eager()
+        torch.cuda.current_stream().wait_stream(side)
+        step_resident = cuda_graph.replay
+        for _ in range(3):
+            step_resident()
+    res["cuda_graph"] = bool(graph)
     sampler = None
     if sample_clocks:
         sampler = ClockSampler(torch.cuda.current_device())
@@ -227,6 +243,16 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
         def step_local():
             for (L, kr, vr), q, o in zip(layers, q_dev, out_dev):
                 ops.decode_attention(q, L, kr, vr, n_res, out=o, flags=flags, scratch=scratch, plan=plan)
+        if graph:
+            torch.cuda.synchronize()
+            g_local = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g_local, stream=side):
+                    step_local()
+            torch.cuda.current_stream().wait_stream(side)
+            step_local = g_local.replay
         ms_l, _, _ = timed_batches(step_local, steps, world, device, min_seconds=0.3)
         res["exchange_ms_per_step"] = max(0.0, ms / steps - ms_l / steps)
         res["check"] = parallel.check_against_full(w, rank, world, device, dtype, layers[0], q_full[0], n_comp, n_res, xchg, flags, scratch=scratch,
@@ -733,14 +759,14 @@ def main():
             if world > 1:
                 wq = dict(WORKLOADS["qwen8b-long"], layers=6)
                 mh = time_decode(wq, max(5, args.steps), args.warmup, rank, world, device, by_heads=True, with_e2e=False, sample_clocks=False,
-                                 exchange=args.exchange)
-                m1 = time_decode(wq, max(5, args.steps), args.warmup, rank, 1, device, with_e2e=False, sample_clocks=False) if rank == 0 else None
+                                 exchange=args.exchange, graph=True)
+                m1 = time_decode(wq, max(5, args.steps), args.warmup, rank, 1, device, with_e2e=False, sample_clocks=False, graph=True) if rank == 0 else None
                 torch.distributed.barrier()
                 if rank == 0:
                     us_n = mh["ms_per_step"] / mh["layers"] * 1e3
                     us_1 = m1["ms_per_step"] / m1["layers"] * 1e3
                     line["head_sharded"] = {
-                        "workload": wq["name"], "layers_timed": mh["layers"], "exchange": args.exchange,
+                        "workload": wq["name"], "layers_timed": mh["layers"], "exchange": args.exchange, "cuda_graph": mh["cuda_graph"],
                         "tok_s_at_36_layers": wq["batch"] / (us_n * 1e-6 * 36), "us_per_layer": us_n,
                         "exchange_us_per_layer": mh["exchange_ms_per_step"] / mh["layers"] * 1e3,
                         "one_gpu_us_per_layer": us_1, "speedup": us_1 / us_n, "efficiency": us_1 / us_n / world, "check": mh["check"]}

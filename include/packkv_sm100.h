@@ -326,8 +326,8 @@ int32_t pkv_decode_attention(const pkv_attn_args* args_host, void* cuda_stream);
  * args.out still receives the local rows.
  *
  * pkv_exchange_wait makes the stream wait until every arrivals[r] (this rank's own counters) has reached
- * `expected` (compared modulo 2^32): one warp polls with acquire loads for at most `max_polls` rounds of about
- * a microsecond each and then gives up, setting PKV_FLAG_TIMEOUT in dev_flags (the kernel always returns, so a
+ * `expected` (compared modulo 2^32): one warp polls with acquire loads for at most `max_polls` rounds a quarter
+ * of a microsecond apart and then gives up, setting PKV_FLAG_TIMEOUT in dev_flags (the kernel always returns, so a
  * rank that never arrives costs the others a bounded wait, not a hang).  Kernels after it on the stream see the
  * gathered rows.  A rank must not start step s+2 into the same gathered buffer before it has waited for step
  * s+1: alternate two buffers per layer or wait every step.
@@ -342,6 +342,16 @@ int32_t pkv_decode_attention_exchange(const pkv_attn_args* args_host, const pkv_
                                       void* cuda_stream);
 int32_t pkv_exchange_wait(const uint32_t* arrivals, int32_t n_ranks, uint32_t expected, uint32_t max_polls,
                           uint32_t* dev_flags, void* cuda_stream);
+/*
+ * The same wait, but once every counter has reached per_step (the arrivals of ONE step: batch * local KV heads) that
+ * many are taken off it again.  The call is then identical for every step, so a CUDA graph that holds the layer loop
+ * (attention launches with their exchange blocks and these waits) can be replayed step after step.  With two
+ * alternating buffer / counter sets a peer's arrivals for step s + 2 cannot reach a counter before this rank has
+ * taken step s off it: the peer starts s + 2 only after it has seen this rank's step s + 1, which this rank's stream
+ * launches after this wait.
+ */
+int32_t pkv_exchange_wait_consume(uint32_t* arrivals, int32_t n_ranks, uint32_t per_step, uint32_t max_polls,
+                                  uint32_t* dev_flags, void* cuda_stream);
 /*
  * Decode step with the append folded in: the launch first writes the step's new token (K after RoPE with the
  * arithmetic of pkv_rope, V as is) into row n_res-1 of the residual buffers and then attends over all n_res

@@ -1296,8 +1296,10 @@ static ScratchLayout scratch_layout(int64_t pairs, int cl, int nsplit, int dump_
     return L;
 }
 
-// One warp polls this rank's arrival counters; see pkv_exchange_wait.
-__global__ void exchange_wait_kernel(const uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags) {
+// One warp polls this rank's arrival counters; see pkv_exchange_wait.  consume: once every counter has reached
+// `expected`, that many arrivals are taken off it again, so that the same launch (same `expected`) serves every step:
+// what a CUDA graph over the layer loop needs.
+__global__ void exchange_wait_kernel(uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, int consume) {
     const int lane = threadIdx.x;
     bool ok = lane >= n_ranks;
     for (unsigned it = 0; it <= max_polls; it++) {
@@ -1307,15 +1309,17 @@ __global__ void exchange_wait_kernel(const uint32_t* arrivals, int n_ranks, unsi
             ok = (int)(v - expected) >= 0;
         }
         if (__all_sync(0xffffffffu, ok)) break;
-        __nanosleep(1000);
+        __nanosleep(250);
     }
-    if (!__all_sync(0xffffffffu, ok) && lane == 0) atomicOr(flags, kFlagTimeout);
+    const bool all = __all_sync(0xffffffffu, ok);
+    if (!all && lane == 0) atomicOr(flags, kFlagTimeout);
+    if (all && consume && lane < n_ranks) atomicSub(arrivals + lane, expected);   // resolved where the peers' additions are: this GPU's L2
     __threadfence_system();
 }
 
-int launch_exchange_wait(const uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, cudaStream_t st) {
+int launch_exchange_wait(uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, bool consume, cudaStream_t st) {
     if (!arrivals || !flags || n_ranks < 1 || n_ranks > 8) return kBadArgument;
-    exchange_wait_kernel<<<1, 32, 0, st>>>(arrivals, n_ranks, expected, max_polls, flags);
+    exchange_wait_kernel<<<1, 32, 0, st>>>(arrivals, n_ranks, expected, max_polls, flags, consume ? 1 : 0);
     return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
 }
 

@@ -18,6 +18,6 @@ using AttnPlan = pkv_attn_plan;
 // (choose everything); scratch may be null (single-launch form only); dry_run: fill plan_io, launch nothing
 int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppend* ap, AttnPlan* plan_io, void* scratch, int64_t scratch_bytes,
                      bool dry_run, cudaStream_t st);
-int launch_exchange_wait(const uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, cudaStream_t st);
+int launch_exchange_wait(uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, bool consume, cudaStream_t st);
 
 }  // namespace pkv

@@ -178,7 +178,12 @@ int32_t pkv_attention_plan(const pkv_attn_args* args_host, pkv_attn_plan* plan_i
 
 int32_t pkv_exchange_wait(const uint32_t* arrivals, int32_t n_ranks, uint32_t expected, uint32_t max_polls, uint32_t* dev_flags,
                           void* cuda_stream) {
-    return launch_exchange_wait(arrivals, n_ranks, expected, max_polls, dev_flags, static_cast<cudaStream_t>(cuda_stream));
+    return launch_exchange_wait(const_cast<uint32_t*>(arrivals), n_ranks, expected, max_polls, dev_flags, false, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int32_t pkv_exchange_wait_consume(uint32_t* arrivals, int32_t n_ranks, uint32_t per_step, uint32_t max_polls, uint32_t* dev_flags,
+                                  void* cuda_stream) {
+    return launch_exchange_wait(arrivals, n_ranks, per_step, max_polls, dev_flags, true, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int32_t pkv_exchange_alloc(int64_t bytes, void** ptr_host, uint8_t* handle64_host) {

@@ -352,11 +352,15 @@ def new_attention_scratch(device, nbytes: int = 32 << 20) -> torch.Tensor:
     return torch.zeros(nbytes, dtype=torch.uint8, device=device)
 
 
-def exchange_wait(arrivals: torch.Tensor, n_ranks: int, expected: int, flags: torch.Tensor, max_polls: int = 2_000_000) -> None:
+def exchange_wait(arrivals: torch.Tensor, n_ranks: int, expected: int, flags: torch.Tensor, max_polls: int = 2_000_000,
+                  consume: bool = False) -> None:
     """Makes the current stream wait until this rank's n_ranks arrival counters have reached `expected`
-    (modulo 2^32); after max_polls polls of about a microsecond the wait gives up and sets FLAG_TIMEOUT."""
+    (modulo 2^32); after max_polls polls (a quarter of a microsecond apart) the wait gives up and sets FLAG_TIMEOUT.
+    consume: `expected` is the arrivals of one step and is taken off the counters again once they are all there, so
+    that the same call serves every step (CUDA graphs)."""
     _require_cuda(arrivals, flags)
-    st = _lib.lib().pkv_exchange_wait(arrivals.data_ptr(), n_ranks, expected & 0xFFFFFFFF, max_polls, flags.data_ptr(), _stream_ptr())
+    fn = _lib.lib().pkv_exchange_wait_consume if consume else _lib.lib().pkv_exchange_wait
+    st = fn(arrivals.data_ptr(), n_ranks, expected & 0xFFFFFFFF, max_polls, flags.data_ptr(), _stream_ptr())
     _lib.check(st, "exchange_wait")
 
 

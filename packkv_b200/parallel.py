@@ -62,7 +62,8 @@ class HeadExchange:
     mode "nccl": one all-gather per layer after the attention launch (the checked baseline).
     mode "peer": the attention launch itself stores its rows into every rank's buffer (buffers and arrival
     counters are shared between the processes of the node through CUDA IPC handles) and a one-warp kernel makes
-    the stream wait for the other ranks' rows; two buffers alternate, so a rank may run one step ahead of the
+    the stream wait for the other ranks' rows (and takes the step's arrivals off the counters again, so that a CUDA
+    graph over the layer loop can be replayed); two buffers alternate, so a rank may run one step ahead of the
     slowest one.  Use: ``o = ops.decode_attention(..., exchange=x.begin()); x.gather(o)``.
     """
 
@@ -142,7 +143,8 @@ class HeadExchange:
         from . import ops
         i = self.step & 1
         self.step += 1
-        ops.exchange_wait(self._arrivals[i], self.world, ((self.step + 1) // 2) * self.per_step, self.flags, self.max_polls)
+        # consuming wait: the same launch every step, so the layer loop can live in a CUDA graph
+        ops.exchange_wait(self._arrivals[i], self.world, self.per_step, self.flags, self.max_polls, consume=True)
         self.buffer = self.buffers[i]
         return self.buffer
 

@@ -124,3 +124,21 @@ def test_exchange_wait_gives_up(cuda_device):
     ops.exchange_wait(arrivals, 4, 7, flags, max_polls=50)
     torch.cuda.synchronize()
     assert int(flags.item()) == 0
+
+
+def test_consuming_wait_serves_every_step(cuda_device):
+    """The wait that takes a step's arrivals off the counters again: three steps with the same call, the counters end
+    at zero; a step whose arrivals are missing gives up with the flag and takes nothing."""
+    from packkv_b200 import _lib, ops
+    dev = cuda_device
+    arrivals = torch.zeros(4, dtype=torch.int32, device=dev)
+    flags = ops.new_flags(dev)
+    for _ in range(3):
+        arrivals += 6                       # what four ranks' launches would have added
+        ops.exchange_wait(arrivals, 4, 6, flags, max_polls=50, consume=True)
+    torch.cuda.synchronize()
+    assert int(flags.item()) == 0 and arrivals.tolist() == [0, 0, 0, 0]
+    arrivals[:3] = 6
+    ops.exchange_wait(arrivals, 4, 6, flags, max_polls=50, consume=True)
+    torch.cuda.synchronize()
+    assert int(flags.item()) == _lib.FLAG_TIMEOUT and arrivals.tolist() == [6, 6, 6, 0]
