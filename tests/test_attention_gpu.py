@@ -373,3 +373,39 @@ def layer_pack_widths(k, bits, k_mode):
     for b in range(1, 5):
         width[span >= (1 << (b - 1))] = b
     return width.flatten()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_shapes_single_launch_and_split_agree_with_reference(cuda_device, seed):
+    """Seeded random shapes, formats and work splits: the two-launch form with a random (cluster, clusters per pair)
+    and the single launch both stay within the bar of the reference path, and the library's own choice with a
+    scratch does too."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    pick = lambda xs: xs[int(torch.randint(len(xs), (1,), generator=g))]
+    dtype = pick([torch.float16, torch.bfloat16])
+    B, Hkv, G = pick([1, 2, 3]), pick([1, 2, 4]), pick([1, 2, 4, 7, 8])
+    cbk, cbv = pick([(64, 64), (64, 128), (128, 128)])
+    k_mode = pick(["channel", "token"])
+    block = cbk if k_mode == "channel" else 64
+    bits_k, bits_v = pick([2, 3, 4]), pick([2, 3, 4])
+    tiles = pick([1, 2, 5, 9, 17])
+    n_comp = tiles * max(cbk, cbv)
+    n_res = pick([0, 1, 17, 128, 191]) if n_comp else 128
+    plan = (pick([1, 2, 4, 8, 16]), pick([1, 2, 3, 6]), 2)
+    dev = cuda_device
+    k, v = synth.synth_kv(B, Hkv, n_comp + n_res, 128, seed=2000 + seed, dtype=dtype, apply_rope=True)
+    q = synth.synth_q(B, Hkv * G, 128, seed=2000 + seed, dtype=dtype)
+    layer, kd, vd = layer_from_oracle(k[:, :, :n_comp], v[:, :, :n_comp], block=block, bits_k=bits_k, bits_v=bits_v, k_mode=k_mode, cbk=cbk, cbv=cbv,
+                                      rel_k=synth.rel_for_bits(bits_k), rel_v=synth.rel_for_bits(bits_v), device=dev)
+    ref = Q.eager_attention(q, torch.cat([kd, k[:, :, n_comp:]], 2), torch.cat([vd, v[:, :, n_comp:]], 2))[:, 0].float()
+    qd = q[:, :, 0].contiguous().to(dev)
+    kr = k[:, :, n_comp:].contiguous().to(dev) if n_res else None
+    vr = v[:, :, n_comp:].contiguous().to(dev) if n_res else None
+    flags, scratch = ops.new_flags(dev), ops.new_attention_scratch(dev)
+    outs = [ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags, kv_heads=Hkv),
+            ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags, kv_heads=Hkv, scratch=scratch, plan=plan),
+            ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags, kv_heads=Hkv, scratch=scratch)]
+    torch.cuda.synchronize()
+    assert int(flags.item()) == 0
+    for o in outs:
+        assert _rel_err(o.float().cpu(), ref, dtype) <= TOL, (seed, plan)
