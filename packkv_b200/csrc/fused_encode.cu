@@ -801,49 +801,88 @@ __global__ void __launch_bounds__(256) value_median_order_kernel(FusedArgs a, ui
     token_params_pass<T, CB, false>(a, xb, prm, ident, b, cbi, lane, wic);
     __syncthreads();
     const int need = (a.heads * 128 + 1) / 2;
+    const int n_slots = 16 * 64;                       // 16 lanes x 16 words x 4 codes per token; missing heads are filled with large codes
+    const unsigned half_mask = 0xFFFFu << (lane & 16);
     for (int t = 2 * wic + (lane >> 4); t < CB; t += 16) {
         const float4 pr = prm[t];
-        Quantiser<T, false> qz;
-        qz.scale = pr.x; qz.zero = pr.y;
-        qz.prepare();
-        const int zi = (int)pr.y;
+        const uint4 ph = reinterpret_cast<const uint4*>(prm + CB)[t];
         const T* xt = xb + (int64_t)t * a.ss + 8 * (lane & 15);
         unsigned cw[16];
+        // The token's codes, four per word.  Parameters inside the checked domain of the element-type quotient: two
+        // codes per instruction, as in the encoder; otherwise (or if a code does not fit a byte) one by one in fp32.
+        bool wide = ph.w == 0u, small = false;         // small: every code of this lane is known to be at most 15
+        if (!wide) {
+            HalfQuotient<T> hq;
+            hq.r = *reinterpret_cast<const typename QT<T>::T2*>(&ph.x);
+            hq.nsp = *reinterpret_cast<const typename QT<T>::T2*>(&ph.y);
+            hq.rp = *reinterpret_cast<const typename QT<T>::T2*>(&ph.z);
+            hq.kab = ph.w;
+            hq.magic = QT<T>::dup((float)(QT<T>::kIntBits == 0x6600u ? 1536 : 192));
+            hq.pre = QT<T>::dup(QT<T>::kPre);
+            unsigned seen = 0;
 #pragma unroll
-        for (int h = 0; h < 8; h++) {
-            cw[2 * h] = 0x7F7F7F7Fu; cw[2 * h + 1] = 0x7F7F7F7Fu;       // heads that do not exist count as large codes
-            if (h < a.heads) {
-                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xt + (int64_t)h * a.sh));
-                const unsigned rw[4] = {raw.x, raw.y, raw.z, raw.w};
-                unsigned c[8];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float2 f = QT<T>::to_float2(rw[i]);
-                    c[2 * i] = min(qz.fast ? qz.template code_u8<true>(f.x, zi) : qz.template code_u8<false>(f.x, zi), 127u);
-                    c[2 * i + 1] = min(qz.fast ? qz.template code_u8<true>(f.y, zi) : qz.template code_u8<false>(f.y, zi), 127u);
+            for (int h = 0; h < 8; h++) {
+                cw[2 * h] = 0x7F7F7F7Fu; cw[2 * h + 1] = 0x7F7F7F7Fu;
+                if (h < a.heads) {
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xt + (int64_t)h * a.sh));
+                    const unsigned c0 = hq.codes(raw.x), c1 = hq.codes(raw.y), c2 = hq.codes(raw.z), c3 = hq.codes(raw.w);
+                    seen |= c0 | c1 | c2 | c3;
+                    cw[2 * h] = __byte_perm(c0, c1, 0x6420);
+                    cw[2 * h + 1] = __byte_perm(c2, c3, 0x6420);
                 }
-                cw[2 * h] = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
-                cw[2 * h + 1] = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+            }
+            wide = (seen & 0xFF80FF80u) != 0u;
+            small = (seen & 0xFFF0FFF0u) == 0u;
+        }
+        if (__ballot_sync(0xffffffffu, wide) & half_mask) {          // the 16 lanes of a token decide together
+            Quantiser<T, false> qz;
+            qz.scale = pr.x; qz.zero = pr.y;
+            qz.prepare();
+            const int zi = (int)pr.y;
+#pragma unroll
+            for (int h = 0; h < 8; h++) {
+                cw[2 * h] = 0x7F7F7F7Fu; cw[2 * h + 1] = 0x7F7F7F7Fu;       // heads that do not exist count as large codes
+                if (h < a.heads) {
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xt + (int64_t)h * a.sh));
+                    const unsigned rw[4] = {raw.x, raw.y, raw.z, raw.w};
+                    unsigned c[8];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f = QT<T>::to_float2(rw[i]);
+                        c[2 * i] = min(qz.fast ? qz.template code_u8<true>(f.x, zi) : qz.template code_u8<false>(f.x, zi), 127u);
+                        c[2 * i + 1] = min(qz.fast ? qz.template code_u8<true>(f.y, zi) : qz.template code_u8<false>(f.y, zi), 127u);
+                    }
+                    cw[2 * h] = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+                    cw[2 * h + 1] = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+                }
             }
         }
-        // count(code <= m) over the token = n_slots - count(code > m); bit 7 of (code + 127 - m) is set iff code > m
+        // count(code <= m) over the token = slots - count(code > m); bit 7 of (code + 127 - m) is set iff code > m
+        // (codes are at most 127); the flags of 16 words add up in four byte counters
         auto count_le = [&](int m) {
-            unsigned over = 0;
+            const unsigned add = 0x01010101u * (unsigned)(127 - m);
+            unsigned acc = 0;
 #pragma unroll
-            for (int i = 0; i < 16; i++) over += __popc((cw[i] + 0x01010101u * (unsigned)(127 - m)) & 0x80808080u);
+            for (int i = 0; i < 16; i++) acc += ((cw[i] + add) >> 7) & 0x01010101u;
+            unsigned over = (acc * 0x01010101u) >> 24;               // sum of the four byte counters (each at most 16)
 #pragma unroll
             for (int s = 8; s > 0; s >>= 1) over += __shfl_xor_sync(0xffffffffu, over, s);
-            return 16 * 64 - (int)over;
+            return n_slots - (int)over;
         };
         int med = 16;                                  // codes above 15 are not expected (bits <= 4)
-        if (count_le(15) >= need) {
+        // all of the token's codes at most 15: count_le(15) is the number of real codes, which is at least `need`
+        // (decided for the warp's two tokens together: count_le shuffles over the whole warp)
+        const bool all_small = __ballot_sync(0xffffffffu, !small) == 0u;
+        const bool in_range = all_small || count_le(15) >= need;
+        {
+            // every lane runs every step (the counts shuffle over the whole warp, whose halves hold different tokens)
             int lo = 0, hi = 15;                       // smallest m in [lo, hi] with count_le(m) >= need
 #pragma unroll
             for (int step = 0; step < 4; step++) {
                 const int mid = (lo + hi) >> 1;
                 if (count_le(mid) >= need) hi = mid; else lo = mid + 1;
             }
-            med = hi;
+            if (in_range) med = hi;
         }
         if ((lane & 15) == 0) key[t] = (uint8_t)med;
     }
