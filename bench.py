@@ -748,28 +748,39 @@ def main():
                 torch.cuda.empty_cache()
             if rank == 0:
                 line["low_batch"] = low
-            leg = encode_leg(args.steps, args.warmup, rank, world, device)
+            # a leg that fails must not take the line with it: its key then holds the error
+            try:
+                leg = encode_leg(args.steps, args.warmup, rank, world, device)
+            except Exception as e:                      # noqa: BLE001
+                leg = {"error": repr(e)[:300]}
             if rank == 0:
                 line["encode"] = leg
             torch.cuda.empty_cache()
-            leg = phi3_e2e_leg(rank, world, device)
+            try:
+                leg = phi3_e2e_leg(rank, world, device)
+            except Exception as e:                      # noqa: BLE001
+                leg = {"error": repr(e)[:300]}
             if rank == 0:
                 line["phi3_e2e"] = leg
             torch.cuda.empty_cache()
             if world > 1:
-                wq = dict(WORKLOADS["qwen8b-long"], layers=6)
-                mh = time_decode(wq, max(5, args.steps), args.warmup, rank, world, device, by_heads=True, with_e2e=False, sample_clocks=False,
-                                 exchange=args.exchange, graph=True)
-                m1 = time_decode(wq, max(5, args.steps), args.warmup, rank, 1, device, with_e2e=False, sample_clocks=False, graph=True) if rank == 0 else None
-                torch.distributed.barrier()
-                if rank == 0:
-                    us_n = mh["ms_per_step"] / mh["layers"] * 1e3
-                    us_1 = m1["ms_per_step"] / m1["layers"] * 1e3
-                    line["head_sharded"] = {
-                        "workload": wq["name"], "layers_timed": mh["layers"], "exchange": args.exchange, "cuda_graph": mh["cuda_graph"],
-                        "tok_s_at_36_layers": wq["batch"] / (us_n * 1e-6 * 36), "us_per_layer": us_n,
-                        "exchange_us_per_layer": mh["exchange_ms_per_step"] / mh["layers"] * 1e3,
-                        "one_gpu_us_per_layer": us_1, "speedup": us_1 / us_n, "efficiency": us_1 / us_n / world, "check": mh["check"]}
+                try:
+                    wq = dict(WORKLOADS["qwen8b-long"], layers=6)
+                    mh = time_decode(wq, max(5, args.steps), args.warmup, rank, world, device, by_heads=True, with_e2e=False, sample_clocks=False,
+                                     exchange=args.exchange, graph=True)
+                    m1 = time_decode(wq, max(5, args.steps), args.warmup, rank, 1, device, with_e2e=False, sample_clocks=False, graph=True) if rank == 0 else None
+                    torch.distributed.barrier()
+                    if rank == 0:
+                        us_n = mh["ms_per_step"] / mh["layers"] * 1e3
+                        us_1 = m1["ms_per_step"] / m1["layers"] * 1e3
+                        line["head_sharded"] = {
+                            "workload": wq["name"], "layers_timed": mh["layers"], "exchange": args.exchange, "cuda_graph": mh["cuda_graph"],
+                            "tok_s_at_36_layers": wq["batch"] / (us_n * 1e-6 * 36), "us_per_layer": us_n,
+                            "exchange_us_per_layer": mh["exchange_ms_per_step"] / mh["layers"] * 1e3,
+                            "one_gpu_us_per_layer": us_1, "speedup": us_1 / us_n, "efficiency": us_1 / us_n / world, "check": mh["check"]}
+                except Exception as e:                # noqa: BLE001
+                    if rank == 0:
+                        line["head_sharded"] = {"error": repr(e)[:300]}
         if rank == 0:
             if not args.no_cpu_baseline and world == 1:
                 t0 = time.perf_counter()
