@@ -847,6 +847,8 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
     }
     if constexpr (PASS == kScores) {
         // ---- first launch ends here: this CTA's max and sum and every warp's score region go to the scratch ----
+        // (the second launch may be set up from here on; it waits for this grid's completion before it reads anything)
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         __syncthreads();
         if (threadIdx.x < 16)
             P.sc_ml[((int64_t)pair * n_vctas + vrank) * 16 + threadIdx.x] = threadIdx.x < 8 ? cs->cl_m[threadIdx.x] : cs->cl_l[threadIdx.x - 8];
@@ -860,6 +862,9 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
     } else {
     if constexpr (PASS == kValues) {
         // ---- second launch starts here: the warp's score region comes back; global max and sum from all CTAs' ----
+        // Launched with programmatic stream serialisation: everything above (barrier set-up, the copy of the first V
+        // block) may overlap the first launch's tail; its results (scratch, the appended residual row) are read below.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         {
             const uint4* src = reinterpret_cast<const uint4*>(P.sc_scores + ((int64_t)pair * n_warps + gw) * P.dump_bytes);
             uint4* dst = reinterpret_cast<uint4*>(wbase + P.off_stile);
@@ -1211,13 +1216,19 @@ static int launch_one(const AttnDev& P, dim3 grid, int smem, cudaStream_t st) {
     cfg.blockDim = dim3(kAW * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = P.cluster;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (PASS == kValues) {
+        // the second launch may start while the first one drains; it waits for it on the device (griddepcontrol.wait)
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
     if (P.cluster > 8) {
         // a non-portable cluster size with this much shared memory may not be schedulable at all: say so
         int clusters = 0;
@@ -1434,7 +1445,7 @@ int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppen
                     // issue); clusters above the portable size schedule badly once they fill more than half the GPU.
                     const double fixed = launches == 2 ? 5.0 + 0.05 * split : 3.0;
                     double cost = (double)waves * (upw + fixed) * (resident > 9.2 ? resident / 9.2 : 1.0);
-                    if (ns == 1) cost *= 1.06;                      // the copy of the next block is not overlapped
+                    if (ns == 1) cost *= 1.02;                      // the copy of the next block is not overlapped (it comes from L2)
                     if (cl > 8) cost *= 2 * ctas > slots ? 1.4 : 1.1;
                     if (cost < best_cost - 1e-9) { best_cost = cost; best_cl = cl; best_ns = ns; best_split = split; best_launches = launches; }
                 }
