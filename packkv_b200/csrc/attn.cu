@@ -1129,6 +1129,8 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
         }
     }
     __syncwarp();
+    // a launch that follows under programmatic stream serialisation (the exchange's wait) may be set up from here on
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- warp accumulators -> this warp's shared region: red[head][channel] --------------------
     float* red = reinterpret_cast<float*>(wbase);
 #pragma unroll
@@ -1330,8 +1332,23 @@ __global__ void exchange_wait_kernel(uint32_t* arrivals, int n_ranks, unsigned e
 
 int launch_exchange_wait(uint32_t* arrivals, int n_ranks, unsigned expected, unsigned max_polls, unsigned* flags, bool consume, cudaStream_t st) {
     if (!arrivals || !flags || n_ranks < 1 || n_ranks > 8) return kBadArgument;
-    exchange_wait_kernel<<<1, 32, 0, st>>>(arrivals, n_ranks, expected, max_polls, flags, consume ? 1 : 0);
-    return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
+    // The wait needs nothing from the launch before it but this rank's own arrivals, which are counted like the
+    // others': it may start while that launch drains (programmatic stream serialisation, no device-side wait) and
+    // ends when the last rank has arrived.  Launches after it are ordered behind both.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, 1);
+    cfg.blockDim = dim3(32, 1, 1);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, exchange_wait_kernel, arrivals, n_ranks, expected, max_polls, flags, consume ? 1 : 0) != cudaSuccess) {
+        cudaGetLastError();
+        return kCudaError;
+    }
+    return kOk;
 }
 
 // plan_io: in: cluster / nsplit / launches to force (0 = choose); out: what was chosen.  dry_run: plan only.
