@@ -45,9 +45,12 @@ namespace cg = cooperative_groups;
 
 namespace pkv {
 
-constexpr int kAW = 4;            // warps per CTA
+#ifndef PKV_ATTN_WARPS
+#define PKV_ATTN_WARPS 4
+#endif
+constexpr int kAW = PKV_ATTN_WARPS;   // warps per CTA (1, 2 or 4)
 #ifndef PKV_ATTN_CTAS
-#define PKV_ATTN_CTAS 4
+#define PKV_ATTN_CTAS (16 / PKV_ATTN_WARPS)
 #endif
 constexpr int kMaxCtasPerSm = PKV_ATTN_CTAS;  // register budget: 65536 / (128 * 4) -> 128 per thread, 96 for 5
 constexpr int kD = 128;           // head dimension
@@ -284,11 +287,12 @@ struct CtaShared {
     unsigned long long mbar[kAW][2];
 };
 // The CTA's reduced accumulators out[head][channel] (read by rank 0 through distributed shared
-// memory) live in the warps' regions, which are idle by then: head hd -> warp hd & 3,
-// float offset (hd >> 2) * kD.
+// memory) live in the warps' regions, which are idle by then: head hd -> warp hd % kAW,
+// float offset (hd / kAW) * kD (at most 8 / kAW rows of 512 bytes per warp: the 2 KB behind out_off hold them).
 __device__ __forceinline__ float* cta_out_row(uint8_t* smem, int warp_smem, int out_off, int hd) {
-    return reinterpret_cast<float*>(smem + (hd & 3) * warp_smem + out_off) + (hd >> 2) * kD;
+    return reinterpret_cast<float*>(smem + (hd & (kAW - 1)) * warp_smem + out_off) + (hd / kAW) * kD;
 }
+static_assert(kAW == 1 || kAW == 2 || kAW == 4, "the reduced rows of a CTA must fit the warps' 2 KB regions");
 
 // dequantise one register of two biased codes.  NORMAL: (code + zero) * scale with zadd = zero - bias (+ pack minimum);
 // HP: code * scale + min, the product rounded before the addition as in the reference (_rn keeps the compiler
@@ -1143,8 +1147,8 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
     __syncwarp();
     __syncthreads();
     // ---- CTA reduce, then cluster reduce on rank 0 ---------------------------------------------
-    {
-        const int d = threadIdx.x;
+    constexpr int kThreads = kAW * 32;
+    for (int d = threadIdx.x; d < kD; d += kThreads) {
         for (int hd = 0; hd < G; hd++) {
             float v = 0.f;
 #pragma unroll
@@ -1154,43 +1158,46 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
     }
     cluster.sync();
     if (rank == 0) {
-        const int d = threadIdx.x;
         bool deliver = true;
         if constexpr (PASS == kValues) {
             // this cluster's rows go to the scratch; the cluster that finds all the others' there adds them up
             float* part = P.sc_part + ((int64_t)pair * P.nsplit + split) * 8 * kD;
-            for (int hd = 0; hd < G; hd++) {
-                float v = 0.f;
-                for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
-                __stcg(part + hd * kD + d, v);
+            for (int d = threadIdx.x; d < kD; d += kThreads) {
+                for (int hd = 0; hd < G; hd++) {
+                    float v = 0.f;
+                    for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
+                    __stcg(part + hd * kD + d, v);
+                }
             }
             __threadfence();
             __syncthreads();
-            if (d == 0) cs->last = atomicAdd(P.sc_count + pair, 1u) == (unsigned)(P.nsplit - 1) ? 1u : 0u;
+            if (threadIdx.x == 0) cs->last = atomicAdd(P.sc_count + pair, 1u) == (unsigned)(P.nsplit - 1) ? 1u : 0u;
             __syncthreads();
             deliver = cs->last != 0;
             if (deliver) __threadfence();
         }
         if (deliver) {
-            for (int hd = 0; hd < G; hd++) {
-                float v = 0.f;
-                if constexpr (PASS == kValues) {
-                    for (int sp = 0; sp < P.nsplit; sp++) v += __ldcg(P.sc_part + (((int64_t)pair * P.nsplit + sp) * 8 + hd) * kD + d);
-                } else {
-                    for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
+            for (int d = threadIdx.x; d < kD; d += kThreads) {
+                for (int hd = 0; hd < G; hd++) {
+                    float v = 0.f;
+                    if constexpr (PASS == kValues) {
+                        for (int sp = 0; sp < P.nsplit; sp++) v += __ldcg(P.sc_part + (((int64_t)pair * P.nsplit + sp) * 8 + hd) * kD + d);
+                    } else {
+                        for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
+                    }
+                    const T r = Tr<T>::from_float(v);
+                    const int64_t idx = ((int64_t)(b * q_heads + h * G + hd)) * kD + d;
+                    reinterpret_cast<T*>(a.out)[idx] = r;
+                    // head-sharded decode: the same row goes into this rank's slice of every rank's gathered buffer
+                    for (int p = 0; p < P.x.n_ranks; p++)
+                        reinterpret_cast<T*>(P.x.gathered[p])[(int64_t)P.x.rank * a.batch * q_heads * kD + idx] = r;
                 }
-                const T r = Tr<T>::from_float(v);
-                const int64_t idx = ((int64_t)(b * q_heads + h * G + hd)) * kD + d;
-                reinterpret_cast<T*>(a.out)[idx] = r;
-                // head-sharded decode: the same row goes into this rank's slice of every rank's gathered buffer
-                for (int p = 0; p < P.x.n_ranks; p++)
-                    reinterpret_cast<T*>(P.x.gathered[p])[(int64_t)P.x.rank * a.batch * q_heads * kD + idx] = r;
             }
-            if (PASS == kValues && d == 0) P.sc_count[pair] = 0u;   // ready for the next launch on this scratch
+            if (PASS == kValues && threadIdx.x == 0) P.sc_count[pair] = 0u;   // ready for the next launch on this scratch
             if (P.x.n_ranks > 0) {
                 __threadfence_system();                // the rows are visible to the other GPUs before the arrival is
                 __syncthreads();
-                if (d < P.x.n_ranks) atomicAdd_system(P.x.arrivals[d] + P.x.rank, 1u);
+                if ((int)threadIdx.x < P.x.n_ranks) atomicAdd_system(P.x.arrivals[threadIdx.x] + P.x.rank, 1u);
             }
         }
     }
