@@ -1467,7 +1467,7 @@ int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppen
                     // and one more row to add per cluster of the pair.  Measured: a warp alone does a unit in 2.3 us and
                     // an SM's throughput stops growing at about 9 resident warps (the kernel is bound by instruction
                     // issue); clusters above the portable size schedule badly once they fill more than half the GPU.
-                    const double fixed = launches == 2 ? 5.0 + 0.05 * split : 3.0;
+                    const double fixed = launches == 2 ? 4.0 + 0.05 * split : 3.0;
                     double cost = (double)waves * (upw + fixed) * (resident > 9.2 ? resident / 9.2 : 1.0);
                     if (ns == 1) cost *= 1.02;                      // the copy of the next block is not overlapped (it comes from L2)
                     if (cl > 8) cost *= 2 * ctas > slots ? 1.4 : 1.1;
