@@ -651,7 +651,7 @@ def main():
     ap.add_argument("--encode-block", type=int, default=64)
     ap.add_argument("--encode-plain-only", action="store_true", help="encode workload: skip the median / append / end-to-end legs (sweeps)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-extras", action="store_true", help="default workload: skip the v_block_64 / encode / head_sharded legs")
+    ap.add_argument("--no-extras", action="store_true", help="default workload: skip the v_block_64 / low_batch / long_context / encode / phi3_e2e / head_sharded legs")
     ap.add_argument("--decode-bits-k", type=int, default=None, help="override the decode workload's K bit width (sweeps)")
     ap.add_argument("--decode-bits-v", type=int, default=None, help="override the decode workload's V bit width (sweeps)")
     ap.add_argument("--decode-cbv", type=int, default=None, choices=[64, 128], help="override the V token block (sweeps)")
@@ -748,6 +748,17 @@ def main():
                 torch.cuda.empty_cache()
             if rank == 0:
                 line["low_batch"] = low
+            if world == 1:
+                # the long-context configuration on one GPU (at several GPUs the head_sharded leg below measures it)
+                wq = dict(WORKLOADS["qwen8b-long"], layers=6)
+                mq = time_decode(wq, max(5, args.steps // 2), args.warmup, rank, world, device, with_e2e=False, sample_clocks=False)
+                peak, _ = measured_peak_gbs()
+                us = mq["ms_per_step"] / mq["layers"] * 1e3
+                gbs = mq["alg_bytes"] / mq["layers"] / (us * 1e-6) / 1e9
+                line["long_context"] = {"workload": wq["name"], "layers_timed": mq["layers"], "us_per_layer": us,
+                                        "tok_s_at_36_layers": wq["batch"] / (us * 1e-6 * 36), "compressed_kv_gbs": gbs, "roofline_frac": gbs / peak,
+                                        "plan": mq["plan"]}
+                torch.cuda.empty_cache()
             # a leg that fails must not take the line with it: its key then holds the error
             try:
                 leg = encode_leg(args.steps, args.warmup, rank, world, device)
