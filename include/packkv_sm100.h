@@ -380,8 +380,9 @@ int32_t pkv_decode_attention_append(const pkv_attn_args* args_host, const pkv_at
  * of all tokens (K phase) and leaves them, with every CTA's maximum and sum, in the scratch; the second
  * normalises with the global maximum and sum, rounds the probabilities, contracts V, and the pair's last
  * cluster to finish adds the clusters' rows in a fixed order.  Rounding points are those of the single launch.
- *   plan_io   in: cluster (CTAs per cluster, 1..16), nsplit (clusters per pair), launches (1 or 2) to force,
- *             0 = let the library choose; out: what was used.  May be NULL.  Two launches of the same tensors with
+ *   plan_io   in: cluster (CTAs per cluster, 1..16), nsplit (clusters per pair), launches (1 or 2), extra to force,
+ *             0 = let the library choose; out: what was used.  May be NULL.  Without an exchange block the library may
+ *             give the pairs unequal numbers of CTAs (`extra` > 0) when that fills the GPU better.  Two launches of the same tensors with
  *             the same cluster * nsplit give bit-identical results whatever the batch and head counts.
  *   scratch   device memory, 256-byte aligned, ZERO before its first use (the library leaves its counters at
  *             zero after every call); launches that share it must be ordered on one stream.  NULL: single launch.
@@ -392,6 +393,8 @@ typedef struct pkv_attn_plan {
     int32_t cluster;
     int32_t nsplit;
     int32_t launches;
+    int32_t extra;      /* two launches with cluster 1: the first `extra` pairs get nsplit + 1 CTAs, the others nsplit,
+                           so that all pairs' CTAs together fill the GPU's CTA slots exactly; 0 = the same for all */
 } pkv_attn_plan;
 int32_t pkv_decode_attention_split(const pkv_attn_args* args_host, const pkv_attn_append* append_host,
                                    const pkv_attn_exchange* exchange_host, pkv_attn_plan* plan_io,

@@ -51,7 +51,7 @@ class AttnAppend(ctypes.Structure):
 
 class AttnPlan(ctypes.Structure):
     """Mirror of pkv_attn_plan (include/packkv_sm100.h)."""
-    _fields_ = [("cluster", _i32), ("nsplit", _i32), ("launches", _i32)]
+    _fields_ = [("cluster", _i32), ("nsplit", _i32), ("launches", _i32), ("extra", _i32)]
 
 
 class EncodeArgs(ctypes.Structure):

@@ -268,6 +268,8 @@ struct AttnDev {
     AttnAppend ap;       // the step's new token, written into residual row n_res - 1 by this launch (new_k = null: none)
     // two-launch form: `nsplit` clusters per (sequence, KV head), state handed over through caller scratch
     int nsplit;          // clusters per (sequence, KV head); 1 in the single-launch form
+    int extra;           // two-launch form with cluster 1: the first `extra` pairs have nsplit + 1 CTAs, so that the CTAs of
+                         // all pairs together fill the GPU's CTA slots exactly (grid = (total CTAs, 1, 1)); -1 = uniform
     int dump_bytes;      // bytes of a warp's score region (compressed + residual tiles), a multiple of 16
     unsigned* sc_count;  // [pairs] arrivals of the pair's clusters in the second launch (zero between launches)
     float* sc_ml;        // [pairs][cluster * nsplit][16] per-CTA max (8 rows) and sum (8 rows)
@@ -320,14 +322,25 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
     const AttnArgs& a = P.a;
     const int lane = lane_id(), wic = threadIdx.x >> 5;
     const int g = lane >> 2, c = lane & 3;
-    const int vrank = blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // vrank: CTA index among all clusters of the pair
+    // vrank: CTA index among all CTAs of the pair; n_vctas: how many the pair has; part_stride: rows of its scratch arrays
+    int vrank = blockIdx.x, h = blockIdx.y, b = blockIdx.z, n_vctas = P.cluster * P.nsplit, part_stride = P.nsplit;
+    if (PASS != kFused && P.extra >= 0) {
+        // uneven form (cluster 1, one-dimensional grid): pairs 0 .. extra-1 have nsplit + 1 CTAs, the others nsplit
+        const int c = blockIdx.x, big = P.extra * (P.nsplit + 1);
+        int pr;
+        if (c < big) { pr = c / (P.nsplit + 1); vrank = c - pr * (P.nsplit + 1); n_vctas = P.nsplit + 1; }
+        else { const int c2 = c - big; pr = P.extra + c2 / P.nsplit; vrank = c2 % P.nsplit; n_vctas = P.nsplit; }
+        b = pr / a.kv_heads; h = pr - b * a.kv_heads;
+        part_stride = P.nsplit + 1;
+    }
     const int rank = PASS == kFused ? vrank : vrank % P.cluster, split = PASS == kFused ? 0 : vrank / P.cluster;
+    const int n_splits = n_vctas / P.cluster;          // clusters of this pair
     const int G = a.group;
     const int q_heads = a.kv_heads * G;
-    const int n_vctas = P.cluster * P.nsplit;
     const int n_warps = kAW * n_vctas;
     const int gw = vrank * kAW + wic;                  // warp index among all warps of the pair
     const int pair = b * a.kv_heads + h;
+    const int ml_stride = P.cluster * part_stride;     // CTAs a pair's scratch rows are laid out for
 
     uint8_t* wbase = smem + wic * P.warp_smem;
     CtaShared* cs = reinterpret_cast<CtaShared*>(smem + P.cta_off);
@@ -855,9 +868,9 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         __syncthreads();
         if (threadIdx.x < 16)
-            P.sc_ml[((int64_t)pair * n_vctas + vrank) * 16 + threadIdx.x] = threadIdx.x < 8 ? cs->cl_m[threadIdx.x] : cs->cl_l[threadIdx.x - 8];
+            P.sc_ml[((int64_t)pair * ml_stride + vrank) * 16 + threadIdx.x] = threadIdx.x < 8 ? cs->cl_m[threadIdx.x] : cs->cl_l[threadIdx.x - 8];
         {
-            uint4* dst = reinterpret_cast<uint4*>(P.sc_scores + ((int64_t)pair * n_warps + gw) * P.dump_bytes);
+            uint4* dst = reinterpret_cast<uint4*>(P.sc_scores + ((int64_t)pair * ml_stride * kAW + gw) * P.dump_bytes);
             const uint4* src = reinterpret_cast<const uint4*>(wbase + P.off_stile);
             for (int i = lane; i < (P.dump_bytes >> 4); i += 32) dst[i] = src[i];
         }
@@ -870,7 +883,7 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
         // block) may overlap the first launch's tail; its results (scratch, the appended residual row) are read below.
         asm volatile("griddepcontrol.wait;" ::: "memory");
         {
-            const uint4* src = reinterpret_cast<const uint4*>(P.sc_scores + ((int64_t)pair * n_warps + gw) * P.dump_bytes);
+            const uint4* src = reinterpret_cast<const uint4*>(P.sc_scores + ((int64_t)pair * ml_stride * kAW + gw) * P.dump_bytes);
             uint4* dst = reinterpret_cast<uint4*>(wbase + P.off_stile);
             for (int i = lane; i < (P.dump_bytes >> 4); i += 32) dst[i] = __ldcg(src + i);
         }
@@ -879,7 +892,7 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
         float m8[8], l8[8];
 #pragma unroll
         for (int r = 0; r < 8; r++) { m8[r] = -INFINITY; l8[r] = 0.f; }
-        const float4* ml = reinterpret_cast<const float4*>(P.sc_ml + (int64_t)pair * n_vctas * 16);
+        const float4* ml = reinterpret_cast<const float4*>(P.sc_ml + (int64_t)pair * ml_stride * 16);
         for (int v = threadIdx.x; v < n_vctas; v += kAW * 32) {
             const float4 ma = __ldcg(ml + 4 * v), mb = __ldcg(ml + 4 * v + 1), la = __ldcg(ml + 4 * v + 2), lb = __ldcg(ml + 4 * v + 3);
             const float mv[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w}, lv[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
@@ -1161,7 +1174,7 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
         bool deliver = true;
         if constexpr (PASS == kValues) {
             // this cluster's rows go to the scratch; the cluster that finds all the others' there adds them up
-            float* part = P.sc_part + ((int64_t)pair * P.nsplit + split) * 8 * kD;
+            float* part = P.sc_part + ((int64_t)pair * part_stride + split) * 8 * kD;
             for (int d = threadIdx.x; d < kD; d += kThreads) {
                 for (int hd = 0; hd < G; hd++) {
                     float v = 0.f;
@@ -1171,7 +1184,7 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
             }
             __threadfence();
             __syncthreads();
-            if (threadIdx.x == 0) cs->last = atomicAdd(P.sc_count + pair, 1u) == (unsigned)(P.nsplit - 1) ? 1u : 0u;
+            if (threadIdx.x == 0) cs->last = atomicAdd(P.sc_count + pair, 1u) == (unsigned)(n_splits - 1) ? 1u : 0u;
             __syncthreads();
             deliver = cs->last != 0;
             if (deliver) __threadfence();
@@ -1181,7 +1194,7 @@ __global__ void __launch_bounds__(kAW * 32, PASS == 1 ? PKV_ATTN_CTAS_SCORES : P
                 for (int hd = 0; hd < G; hd++) {
                     float v = 0.f;
                     if constexpr (PASS == kValues) {
-                        for (int sp = 0; sp < P.nsplit; sp++) v += __ldcg(P.sc_part + (((int64_t)pair * P.nsplit + sp) * 8 + hd) * kD + d);
+                        for (int sp = 0; sp < n_splits; sp++) v += __ldcg(P.sc_part + (((int64_t)pair * part_stride + sp) * 8 + hd) * kD + d);
                     } else {
                         for (int r = 0; r < P.cluster; r++) v += cluster.map_shared_rank(cta_out_row(smem, P.warp_smem, P.out_off, hd), r)[d];
                     }
@@ -1304,7 +1317,7 @@ static int plan_smem(AttnDev& P, int cl, int nsplit, int nslots, int slot) {
 
 // partition of the caller's scratch for the two-launch form
 struct ScratchLayout { int64_t count, ml, part, scores, total; };
-static ScratchLayout scratch_layout(int64_t pairs, int cl, int nsplit, int dump_bytes) {
+static ScratchLayout scratch_layout(int64_t pairs, int cl, int nsplit, int dump_bytes) {   // nsplit: the largest of any pair
     ScratchLayout L;
     int64_t off = 0;
     L.count = off; off += (pairs * 4 + 255) & ~(int64_t)255;
@@ -1387,6 +1400,7 @@ int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppen
     if (reinterpret_cast<uintptr_t>(a.q) & 15) return kBadArgument;
 
     AttnDev P{};
+    P.extra = -1;
     P.a = a;
     if (ap) {
         if (!ap->new_k || !ap->new_v || a.n_res < 1 || a.n_res > ap->res_capacity || ((ap->cos == nullptr) != (ap->sin == nullptr))) return kBadArgument;
@@ -1433,14 +1447,41 @@ int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppen
     const int want_cl = plan_io && plan_io->cluster > 0 ? plan_io->cluster : env_cl;
     const int want_split = plan_io && plan_io->nsplit > 0 ? plan_io->nsplit : 0;
     const int want_launches = plan_io ? plan_io->launches : 0;
-    if (want_cl < 0 || want_cl > 16 || want_launches < 0 || want_launches > 2) return kBadArgument;
+    const int want_extra = plan_io ? plan_io->extra : 0;
+    if (want_cl < 0 || want_cl > 16 || want_launches < 0 || want_launches > 2 || want_extra < 0) return kBadArgument;
     if (scratch && ((reinterpret_cast<uintptr_t>(scratch) & 255) || scratch_bytes < 0)) return kBadArgument;
     const long pairs = (long)a.batch * a.kv_heads;
     const int unit_tile = (P.tile / 64) * 4;                   // a residual tile is about a quarter of 64 compressed tokens
+    const int n_rt = (a.n_res + 15) / 16;
+    const double pair_units = (double)P.tiles_total * unit_tile + n_rt;
+    // Cost of a plan, in units of 16 tokens of one warp.  An SM's throughput stops growing at about 13 resident warps
+    // (the kernel is bound by instruction issue), so the time of a launch follows the work of its busiest SM:
+    // (warps on it) x (average units per warp + a fixed part) / min(warps, 13), and never less than the longest warp.
+    // Fixed part: exchange and reductions; in two launches also the hand-over, a second start and one more row to add
+    // per cluster of the pair.  Clusters are placed inside one GPC: about 7 % of the slots stay unusable for them
+    // (136 clusters of 4 fit at once, 144 do not), and clusters above the portable size schedule badly once they
+    // fill more than half the GPU.
+    auto plan_cost = [&](long ctas, int cl, int per_sm, double avg_upw, int upw_max, double fixed, int ns) {
+        long slots = (long)kSmCount * per_sm;
+        if (cl > 1) slots = (long)((double)slots * 0.93 / cl) * cl;
+        if (slots < cl) slots = cl;
+        const long waves = (ctas + slots - 1) / slots;
+        const long on_gpu = ctas < slots ? ctas : slots;
+        const int sm_warps = (int)((on_gpu + kSmCount - 1) / kSmCount) * kAW;
+        // (a launch ends with its longest warps running alone, below the saturated rate: three quarters of the
+        // difference between the longest and the average warp count as if every warp had them)
+        const double eff_upw = avg_upw + 0.75 * (upw_max - avg_upw);
+        const double thr = sm_warps * (eff_upw + fixed) / (sm_warps < 13 ? sm_warps : 13);
+        const double lat = upw_max + fixed;
+        double cost = (double)waves * (thr > lat ? thr : lat);
+        if (ns == 1) cost *= 1.02;                              // the copy of the next block is not overlapped (it comes from L2)
+        if (cl > 8) cost *= 2 * ctas > slots ? 1.4 : 1.1;
+        return cost;
+    };
     static const int kSplits[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
-    int best_cl = 0, best_ns = 1, best_split = 1, best_launches = 1;
+    int best_cl = 0, best_ns = 1, best_split = 1, best_launches = 1, best_extra = -1;
     double best_cost = 1e300;
-    for (int cl = 1; cl <= 16; cl++) {
+    for (int cl = 1; cl <= 16 && want_extra == 0; cl++) {
         if (want_cl && cl != want_cl) continue;
         for (int split : kSplits) {
             if (want_split && split != want_split) continue;
@@ -1458,37 +1499,65 @@ int launch_attention(const AttnArgs& a, const AttnExchange* xch, const AttnAppen
                     int per_sm = (228 * 1024) / (smem + 1024);
                     if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
                     if (per_sm < 1) continue;
-                    const long ctas = pairs * cl * split, slots = (long)kSmCount * per_sm;
-                    const long waves = (ctas + slots - 1) / slots;
-                    const double resident = (double)(ctas < slots ? ctas : slots) / kSmCount * kAW;   // warps per SM
                     const int n_warps = kAW * cl * split;
-                    const int upw = ((P.tiles_total + n_warps - 1) / n_warps) * unit_tile + (((a.n_res + 15) / 16 + n_warps - 1) / n_warps);
-                    // Fixed part per CTA: exchange and reductions; in two launches also the hand-over, a second start
-                    // and one more row to add per cluster of the pair.  Measured: a warp alone does a unit in 2.3 us and
-                    // an SM's throughput stops growing at about 9 resident warps (the kernel is bound by instruction
-                    // issue); clusters above the portable size schedule badly once they fill more than half the GPU.
+                    const int upw = ((P.tiles_total + n_warps - 1) / n_warps) * unit_tile + ((n_rt + n_warps - 1) / n_warps);
                     const double fixed = launches == 2 ? 4.0 + 0.05 * split : 3.0;
-                    double cost = (double)waves * (upw + fixed) * (resident > 9.2 ? resident / 9.2 : 1.0);
-                    if (ns == 1) cost *= 1.02;                      // the copy of the next block is not overlapped (it comes from L2)
-                    if (cl > 8) cost *= 2 * ctas > slots ? 1.4 : 1.1;
-                    if (cost < best_cost - 1e-9) { best_cost = cost; best_cl = cl; best_ns = ns; best_split = split; best_launches = launches; }
+                    const double cost = plan_cost(pairs * cl * split, cl, per_sm, pair_units / n_warps, upw, fixed, ns);
+                    if (cost < best_cost - 1e-9) { best_cost = cost; best_cl = cl; best_ns = ns; best_split = split; best_launches = launches; best_extra = -1; }
                 }
             }
         }
     }
+    // Uneven form: independent CTAs (cluster 1), as many as the GPU holds at once, nsplit or nsplit + 1 of them per pair.
+    // Not with an exchange (the ranks' launches and a single-GPU launch of the same tensors must be able to share a plan)
+    // and not when the caller forces a uniform plan.
+    const bool forced_uniform = want_extra == 0 && (want_cl || want_split || want_launches);
+    if (scratch && !xch && !forced_uniform && P.tiles_total > 0 && (want_launches == 0 || want_launches == 2)) {
+        for (int per_sm = kMaxCtasPerSm; per_sm >= 1; per_sm--) {
+            const long T = (long)kSmCount * per_sm;
+            int base = (int)(T / pairs), extra = (int)(T % pairs);
+            if (want_extra > 0) { base = want_split; extra = want_extra; }
+            if (base < 1 || base + 1 > 128 || extra >= pairs) { if (want_extra > 0) break; continue; }
+            if (extra == 0 && want_extra == 0) continue;      // a uniform plan: covered above
+            bool found = false;
+            for (int ns = 2; ns >= 1; ns--) {
+                if (env_slots && ns != env_slots) continue;
+                AttnDev Q = P;
+                const int smem = plan_smem(Q, 1, base, ns, slot);
+                if (smem > 227 * 1024) continue;
+                if (scratch_layout(pairs, 1, base + 1, Q.dump_bytes).total > scratch_bytes) continue;
+                int fit = (228 * 1024) / (smem + 1024);
+                if (fit > kMaxCtasPerSm) fit = kMaxCtasPerSm;
+                if (fit < per_sm && want_extra == 0) continue;
+                const long ctas = pairs * base + extra;
+                const int n_warps = kAW * base;
+                const int upw = ((P.tiles_total + n_warps - 1) / n_warps) * unit_tile + ((n_rt + n_warps - 1) / n_warps);
+                const double cost = plan_cost(ctas, 1, fit, pair_units * pairs / ((double)ctas * kAW), upw, 4.0 + 0.05 * (base + 1), ns);
+                if (cost < best_cost - 1e-9 || want_extra > 0) {
+                    best_cost = cost; best_cl = 1; best_ns = ns; best_split = base; best_launches = 2; best_extra = extra;
+                    found = true;
+                    if (want_extra > 0) break;
+                }
+            }
+            if (found || want_extra > 0) break;               // the fullest GPU that fits is the candidate
+        }
+    }
     if (best_cl == 0) return kUnsupported;
     const int smem = plan_smem(P, best_cl, best_split, best_ns, slot);
+    P.extra = best_extra;
     if (best_launches == 2) {
-        const ScratchLayout L = scratch_layout(pairs, best_cl, best_split, P.dump_bytes);
+        const ScratchLayout L = scratch_layout(pairs, best_cl, best_extra >= 0 ? best_split + 1 : best_split, P.dump_bytes);
+        if (!scratch || L.total > scratch_bytes) return kBadArgument;
         uint8_t* base = static_cast<uint8_t*>(scratch);
         P.sc_count = reinterpret_cast<unsigned*>(base + L.count);
         P.sc_ml = reinterpret_cast<float*>(base + L.ml);
         P.sc_part = reinterpret_cast<float*>(base + L.part);
         P.sc_scores = base + L.scores;
     }
-    if (plan_io) { plan_io->cluster = best_cl; plan_io->nsplit = best_split; plan_io->launches = best_launches; }
+    if (plan_io) { plan_io->cluster = best_cl; plan_io->nsplit = best_split; plan_io->launches = best_launches; plan_io->extra = best_extra > 0 ? best_extra : 0; }
     if (dry_run) return kOk;
     dim3 grid(P.cluster * P.nsplit, a.kv_heads, a.batch);
+    if (best_extra >= 0) grid = dim3((unsigned)(pairs * best_split + best_extra), 1, 1);
     return a.is_bf16 ? launch_typed<__nv_bfloat16>(P, grid, smem, st) : launch_typed<__half>(P, grid, smem, st);
 }
 

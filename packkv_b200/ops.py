@@ -254,8 +254,9 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
     the launch writes the step's new token (K rotated like rope()) into residual row n_res - 1 before attending;
     n_res counts that token.
     `scratch` (new_attention_scratch) lets the library split a launch with few (sequence, KV head) pairs over
-    several clusters per pair in two launches; `plan` = (cluster, nsplit, launches), 0 = choose, forces the split.
-    plan_only: nothing is launched and the plan (cluster, nsplit, launches) that would be used is returned.
+    several clusters per pair in two launches; `plan` = (cluster, nsplit, launches[, extra]), 0 = choose, forces the split
+    (extra > 0 with cluster 1: the first `extra` pairs get nsplit + 1 CTAs).
+    plan_only: nothing is launched and the plan (cluster, nsplit, launches, extra) that would be used is returned.
     """
     _require_cuda(q, k_res, v_res, out, flags, scratch)
     if q.dim() != 3 or q.shape[2] != 128 or not q.is_contiguous():
@@ -325,13 +326,14 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
     if scratch is not None or plan is not None or plan_only:
         pl = _lib.AttnPlan()
         if plan is not None:
-            pl.cluster, pl.nsplit, pl.launches = plan
+            pl.cluster, pl.nsplit, pl.launches = plan[:3]
+            pl.extra = plan[3] if len(plan) > 3 else 0
         if scratch is not None and (scratch.dtype != torch.uint8 or not scratch.is_contiguous() or scratch.data_ptr() % 256):
             raise ValueError("scratch must be a contiguous uint8 tensor aligned to 256 bytes (new_attention_scratch)")
         sbytes = 0 if scratch is None else scratch.numel()
         if plan_only:
             _lib.check(_lib.lib().pkv_attention_plan(ctypes.byref(a), ctypes.byref(pl), sbytes), "attention_plan")
-            return (pl.cluster, pl.nsplit, pl.launches)
+            return (pl.cluster, pl.nsplit, pl.launches, pl.extra)
         st = _lib.lib().pkv_decode_attention_split(ctypes.byref(a), ctypes.byref(ap) if ap is not None else None,
                                                    ctypes.byref(exchange) if exchange is not None else None, ctypes.byref(pl),
                                                    scratch.data_ptr() if scratch is not None else None, sbytes, _stream_ptr())

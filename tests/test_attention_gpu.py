@@ -308,8 +308,8 @@ def test_split_chosen_for_one_long_sequence(cuda_device):
     scratch = ops.new_attention_scratch(dev)
     plan = ops.decode_attention(qd, layer, kr, vr, n_res, scratch=scratch, plan_only=True)
     assert plan[2] == 2 and plan[1] > 1, plan
-    assert ops.decode_attention(qd, layer, kr, vr, n_res, plan_only=True)[1:] == (1, 1)
-    assert ops.decode_attention(qd, layer, kr, vr, n_res, scratch=scratch[:4096], plan_only=True)[1:] == (1, 1)
+    assert ops.decode_attention(qd, layer, kr, vr, n_res, plan_only=True)[1:] == (1, 1, 0)
+    assert ops.decode_attention(qd, layer, kr, vr, n_res, scratch=scratch[:4096], plan_only=True)[1:] == (1, 1, 0)
     flags = ops.new_flags(dev)
     out_split = ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags, scratch=scratch)
     out_one = ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags)
@@ -409,3 +409,27 @@ def test_random_shapes_single_launch_and_split_agree_with_reference(cuda_device,
     assert int(flags.item()) == 0
     for o in outs:
         assert _rel_err(o.float().cpu(), ref, dtype) <= TOL, (seed, plan)
+
+
+@pytest.mark.parametrize("k_mode", ["channel", "token"])
+def test_uneven_ctas_per_pair(cuda_device, k_mode):
+    """Two launches of independent CTAs with the pairs getting nsplit or nsplit + 1 of them (the form the library
+    chooses when that fills the GPU exactly): forced with small numbers, against the reference; the same plan twice
+    gives the same bits, and so does a CUDA-graph-free second call on the same scratch."""
+    dev, dtype = cuda_device, torch.bfloat16
+    B, Hkv, G, n_comp, n_res = 3, 2, 4, 1920, 150
+    k, v = synth.synth_kv(B, Hkv, n_comp + n_res, 128, seed=61, dtype=dtype, apply_rope=True)
+    q = synth.synth_q(B, Hkv * G, 128, seed=61, dtype=dtype)
+    layer, kd, vd = layer_from_oracle(k[:, :, :n_comp], v[:, :, :n_comp], block=64, bits_k=4, bits_v=3, k_mode=k_mode, cbk=64, cbv=128,
+                                      rel_k=synth.rel_for_bits(4), rel_v=synth.rel_for_bits(3), device=dev)
+    ref = Q.eager_attention(q, torch.cat([kd, k[:, :, n_comp:]], 2), torch.cat([vd, v[:, :, n_comp:]], 2))[:, 0].float()
+    qd, kr, vr = q[:, :, 0].contiguous().to(dev), k[:, :, n_comp:].contiguous().to(dev), v[:, :, n_comp:].contiguous().to(dev)
+    flags, scratch = ops.new_flags(dev), ops.new_attention_scratch(dev)
+    outs = []
+    for plan in [(1, 2, 2, 1), (1, 2, 2, 5), (1, 1, 2, 3), (1, 5, 2, 4), (1, 2, 2, 5)]:
+        outs.append(ops.decode_attention(qd, layer, kr, vr, n_res, flags=flags, scratch=scratch, plan=plan))
+        torch.cuda.synchronize()
+        assert int(flags.item()) == 0
+        assert _rel_err(outs[-1].float().cpu(), ref, dtype) <= TOL, plan
+        assert ops.decode_attention(qd, layer, kr, vr, n_res, scratch=scratch, plan=plan, plan_only=True) == plan
+    assert torch.equal(outs[1], outs[4])
