@@ -209,7 +209,7 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
                 xchg.gather(o)
 
     res = {"n_comp": n_comp, "n_res": n_res, "layers": len(layers), "batch": B, "q_heads_local": Hq, "alg_bytes": alg_bytes,
-           "plan": {"cluster": used[0], "clusters_per_pair": used[1], "launches": used[2]}}
+           "plan": {"cluster": used[0], "clusters_per_pair": used[1], "launches": used[2], "pairs_with_one_more_cta": used[3]}}
     for _ in range(max(warmup, 3)):
         step_resident()
     step_eager = step_resident

@@ -179,7 +179,7 @@ def check_against_full(w: dict, rank: int, world: int, device, dtype, shard_laye
     ref = ops.decode_attention(q_full0, full, k[:, :, n_comp:].contiguous(), v[:, :, n_comp:].contiguous(), n_res, flags=flags, scratch=big, plan=used)
     torch.cuda.synchronize()
     return {"bit_identical_to_one_gpu": bool(torch.equal(got, ref)), "max_abs_diff": float((got.float() - ref.float()).abs().max()),
-            "plan": {"cluster": used[0], "clusters_per_pair": used[1], "launches": used[2]}}
+            "plan": {"cluster": used[0], "clusters_per_pair": used[1], "launches": used[2], "pairs_with_one_more_cta": used[3]}}
 
 
 def compress_kv_head_shard(k: torch.Tensor, v: torch.Tensor, rank: int, world: int, *, block: int, bits_k: int, bits_v: int,
