@@ -200,7 +200,8 @@ def time_decode(w, steps, warmup, rank, world, device, *, by_heads=False, with_e
     scratch = ops.new_attention_scratch(device, 64 << 20) if w.get("split", True) else None
     plan = w.get("plan")
     L0, kr0, vr0 = layers[0]
-    used = ops.decode_attention(q_dev[0], L0, kr0, vr0, n_res, flags=flags, scratch=scratch, plan=plan, plan_only=True)
+    used = ops.decode_attention(q_dev[0], L0, kr0, vr0, n_res, flags=flags, scratch=scratch, plan=plan, plan_only=True,
+                                exchange=xchg.begin() if by_heads and xchg.mode == "peer" else None)
 
     def step_resident():
         for (L, kr, vr), q, o in zip(layers, q_dev, out_dev):

@@ -386,7 +386,8 @@ int32_t pkv_decode_attention_append(const pkv_attn_args* args_host, const pkv_at
  *             the same cluster * nsplit give bit-identical results whatever the batch and head counts.
  *   scratch   device memory, 256-byte aligned, ZERO before its first use (the library leaves its counters at
  *             zero after every call); launches that share it must be ordered on one stream.  NULL: single launch.
- * pkv_attention_plan fills plan_io the same way and launches nothing (scratch_bytes alone decides what fits).
+ * pkv_attention_plan fills plan_io the same way and launches nothing (scratch_bytes alone decides what fits;
+ * with_exchange != 0: plan as for a launch with an exchange block).
  * append_host and exchange_host may be NULL.
  */
 typedef struct pkv_attn_plan {
@@ -399,7 +400,8 @@ typedef struct pkv_attn_plan {
 int32_t pkv_decode_attention_split(const pkv_attn_args* args_host, const pkv_attn_append* append_host,
                                    const pkv_attn_exchange* exchange_host, pkv_attn_plan* plan_io,
                                    void* scratch, int64_t scratch_bytes, void* cuda_stream);
-int32_t pkv_attention_plan(const pkv_attn_args* args_host, pkv_attn_plan* plan_io, int64_t scratch_bytes);
+int32_t pkv_attention_plan(const pkv_attn_args* args_host, pkv_attn_plan* plan_io, int64_t scratch_bytes,
+                           int32_t with_exchange);
 
 /*
  * Set-up helpers of the exchange; the only entry points that allocate or touch address-space mappings (they

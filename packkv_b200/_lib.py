@@ -89,7 +89,7 @@ SIGNATURES = {
     "pkv_decode_attention_append": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnAppend), ctypes.POINTER(AttnExchange), _p]),
     "pkv_decode_attention_split": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnAppend), ctypes.POINTER(AttnExchange), ctypes.POINTER(AttnPlan),
                                           _p, _i64, _p]),
-    "pkv_attention_plan": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnPlan), _i64]),
+    "pkv_attention_plan": (_i32, [ctypes.POINTER(AttnArgs), ctypes.POINTER(AttnPlan), _i64, _i32]),
     "pkv_exchange_wait": (_i32, [_p, _i32, ctypes.c_uint32, ctypes.c_uint32, _p, _p]),
     "pkv_exchange_wait_consume": (_i32, [_p, _i32, ctypes.c_uint32, ctypes.c_uint32, _p, _p]),
     "pkv_exchange_alloc": (_i32, [_i64, ctypes.POINTER(ctypes.c_void_p), _p]),

@@ -169,11 +169,16 @@ int32_t pkv_decode_attention_split(const pkv_attn_args* args_host, const pkv_att
     return launch_attention(*args_host, exchange_host, append_host, plan_io, scratch, scratch_bytes, false, static_cast<cudaStream_t>(cuda_stream));
 }
 
-int32_t pkv_attention_plan(const pkv_attn_args* args_host, pkv_attn_plan* plan_io, int64_t scratch_bytes) {
+int32_t pkv_attention_plan(const pkv_attn_args* args_host, pkv_attn_plan* plan_io, int64_t scratch_bytes, int32_t with_exchange) {
     if (!args_host || !plan_io) return kBadArgument;
-    // the plan depends on sizes only: any non-null, aligned address stands for the scratch
-    return launch_attention(*args_host, nullptr, nullptr, plan_io, scratch_bytes > 0 ? reinterpret_cast<void*>(uintptr_t(256)) : nullptr, scratch_bytes,
-                            true, nullptr);
+    // the plan depends on sizes only: any non-null, aligned address stands for the scratch, and a block that is never
+    // dereferenced (nothing is launched) for the exchange
+    pkv_attn_exchange x{};
+    x.n_ranks = 1;
+    uint32_t dummy_counter = 0;
+    x.gathered[0] = &dummy_counter; x.arrivals[0] = &dummy_counter;
+    return launch_attention(*args_host, with_exchange ? &x : nullptr, nullptr, plan_io, scratch_bytes > 0 ? reinterpret_cast<void*>(uintptr_t(256)) : nullptr,
+                            scratch_bytes, true, nullptr);
 }
 
 int32_t pkv_exchange_wait(const uint32_t* arrivals, int32_t n_ranks, uint32_t expected, uint32_t max_polls, uint32_t* dev_flags,

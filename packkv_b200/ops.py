@@ -332,7 +332,7 @@ def decode_attention(q: torch.Tensor, layer: Optional[CompressedLayer], k_res: O
             raise ValueError("scratch must be a contiguous uint8 tensor aligned to 256 bytes (new_attention_scratch)")
         sbytes = 0 if scratch is None else scratch.numel()
         if plan_only:
-            _lib.check(_lib.lib().pkv_attention_plan(ctypes.byref(a), ctypes.byref(pl), sbytes), "attention_plan")
+            _lib.check(_lib.lib().pkv_attention_plan(ctypes.byref(a), ctypes.byref(pl), sbytes, int(exchange is not None)), "attention_plan")
             return (pl.cluster, pl.nsplit, pl.launches, pl.extra)
         st = _lib.lib().pkv_decode_attention_split(ctypes.byref(a), ctypes.byref(ap) if ap is not None else None,
                                                    ctypes.byref(exchange) if exchange is not None else None, ctypes.byref(pl),

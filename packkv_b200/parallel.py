@@ -164,8 +164,9 @@ def check_against_full(w: dict, rank: int, world: int, device, dtype, shard_laye
     layer, k_res, v_res = shard_layer0
     Hq_l = q_full0.shape[1] // world
     q_l = q_full0[:, rank * Hq_l:(rank + 1) * Hq_l].contiguous()
-    used = ops.decode_attention(q_l, layer, k_res, v_res, n_res, flags=flags, scratch=scratch, plan=plan, plan_only=True)
-    out = ops.decode_attention(q_l, layer, k_res, v_res, n_res, flags=flags, exchange=xchg.begin(), scratch=scratch, plan=plan)
+    x = xchg.begin()
+    used = ops.decode_attention(q_l, layer, k_res, v_res, n_res, flags=flags, scratch=scratch, plan=plan, plan_only=True, exchange=x)
+    out = ops.decode_attention(q_l, layer, k_res, v_res, n_res, flags=flags, exchange=x, scratch=scratch, plan=plan)
     xchg.gather(out)
     torch.cuda.synchronize()
     got = xchg.full()
