@@ -5,7 +5,8 @@
 // (evaluation/evaluation.py:1040-1049), wv_mat_vec_mul + fused_wv (kernels.cu:632-765,
 // fused_kernels.cu:187-261) and, for numerics, the model path's dequantise-then-attend
 // (models/cache/packkv_quant.py:45-85 + models/llama.py:177-212).  Decompressed K/V never go
-// to HBM, and neither do scores or partial results.
+// to HBM, and in the single launch neither do scores or partial results (the two-launch form for
+// launches whose pairs do not fill the GPU hands scores and per-cluster rows over through a scratch).
 //
 // Numerics follow the reference's rounding points so the result can be compared with its
 // decompress-then-attend path: every K and V element is dequantised to the element type
